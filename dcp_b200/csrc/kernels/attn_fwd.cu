@@ -1,0 +1,393 @@
+// Blockwise range-masked attention forward for sm_100a.
+//
+// One CTA = one 128-query tile of one head.  Warp roles:
+//   warps 0-3  softmax: one thread per query row, S read from TMEM with tcgen05.ld,
+//              online-softmax state in registers, P written back (TMEM or smem),
+//              O rescaled in TMEM only when a row maximum moved, epilogue.
+//   warp 4     TMA producer: Q once, then a 2-deep ring of K tiles and of V tiles.
+//   warp 5     UMMA issuer: S_j = Q K_j^T (SS), O += P_j V_j (TS or SS), software
+//              pipelined so S_{j+1} is in flight while softmax works on S_j.
+// TMEM (512 columns): S0 [0,128) S1 [128,256) O [256,384); P_j aliases the first 64
+// columns of S_j as packed bf16 pairs.
+//
+// The partial (out, lse) of a tile is stored straight to its destination arena, which
+// may be a peer GPU's memory (plain st.global over the NVLink mapping).
+//
+// Reference behaviour covered: the varlen forward with block tables and per-query KV
+// ranges that dcp/runtime/flash_attention/executor.py:884-913 calls.
+#include <limits.h>
+#include <math.h>
+
+#include "attn_common.cuh"
+#include "ptx.cuh"
+#include "tmap.cuh"
+
+namespace dcpk {
+
+static constexpr int kFwdThreads = 192;
+static constexpr int kHalfBytes = 128 * 64 * 2;      // one [128 x 64] bf16 swizzled half tile
+static constexpr int kTileBytes = 2 * kHalfBytes;    // [128 x 128] bf16
+
+struct __align__(1024) FwdSmem {
+  uint8_t q[kTileBytes];
+  uint8_t k[2][kTileBytes];
+  uint8_t v[2][kTileBytes];
+  uint8_t p[kTileBytes];  // only touched by the smem-P variant
+  uint64_t q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], p_ready[2], o_done;
+  uint32_t tmem_base;
+  int abort_word;
+  int red[4][8];
+};
+
+__device__ __forceinline__ TileBounds combine_bounds(const int (*red)[8]) {
+  TileBounds b;
+  b.u0s = min(min(red[0][0], red[1][0]), min(red[2][0], red[3][0]));
+  b.u0e = max(max(red[0][1], red[1][1]), max(red[2][1], red[3][1]));
+  b.u1s = min(min(red[0][2], red[1][2]), min(red[2][2], red[3][2]));
+  b.u1e = max(max(red[0][3], red[1][3]), max(red[2][3], red[3][3]));
+  b.i0s = max(max(red[0][4], red[1][4]), max(red[2][4], red[3][4]));
+  b.i0e = min(min(red[0][5], red[1][5]), min(red[2][5], red[3][5]));
+  b.i1s = max(max(red[0][6], red[1][6]), max(red[2][6], red[3][6]));
+  b.i1e = min(min(red[0][7], red[1][7]), min(red[2][7], red[3][7]));
+  return b;
+}
+
+// each of the first 128 threads owns one query row; reduce its ranges over the warp
+__device__ __forceinline__ void reduce_row_ranges(int (*red)[8], int warp, int lane, bool valid, int s0,
+                                                  int e0, int s1, int e1) {
+  bool has0 = valid && e0 > s0, has1 = valid && e1 > s1;
+  int v[8];
+  v[0] = has0 ? s0 : INT_MAX;  v[1] = has0 ? e0 : INT_MIN;
+  v[2] = has1 ? s1 : INT_MAX;  v[3] = has1 ? e1 : INT_MIN;
+  v[4] = valid ? s0 : INT_MIN; v[5] = valid ? e0 : INT_MAX;
+  v[6] = valid ? s1 : INT_MIN; v[7] = valid ? e1 : INT_MAX;
+  v[0] = __reduce_min_sync(0xffffffffu, v[0]);
+  v[1] = __reduce_max_sync(0xffffffffu, v[1]);
+  v[2] = __reduce_min_sync(0xffffffffu, v[2]);
+  v[3] = __reduce_max_sync(0xffffffffu, v[3]);
+  v[4] = __reduce_max_sync(0xffffffffu, v[4]);
+  v[5] = __reduce_min_sync(0xffffffffu, v[5]);
+  v[6] = __reduce_max_sync(0xffffffffu, v[6]);
+  v[7] = __reduce_min_sync(0xffffffffu, v[7]);
+  if (lane == 0) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) red[warp][i] = v[i];
+  }
+}
+
+template <bool kPSmem>
+__global__ void __launch_bounds__(kFwdThreads, 1)
+attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_kv,
+                const AttnTile* __restrict__ tiles, const KvEntry* __restrict__ kv_entries,
+                const int4* __restrict__ masks, PeerPtrs ptrs, int hq, int hkv, int lse_stride,
+                int block_size, float scale, int* __restrict__ status) {
+  extern __shared__ uint8_t smem_raw[];
+  FwdSmem& sm = *reinterpret_cast<FwdSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const AttnTile tile = tiles[blockIdx.x];
+  const int kv_head = tile.head / (hq / hkv);
+
+  if (threadIdx.x == 128) {
+    tma_prefetch_desc(&tm_q);
+    tma_prefetch_desc(&tm_kv);
+    mbar_init(&sm.q_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&sm.k_full[i], 1);  mbar_init(&sm.k_empty[i], 1);
+      mbar_init(&sm.v_full[i], 1);  mbar_init(&sm.v_empty[i], 1);
+      mbar_init(&sm.s_full[i], 1);  mbar_init(&sm.p_ready[i], 128);
+    }
+    mbar_init(&sm.o_done, 1);
+    sm.abort_word = 0;
+    mbar_fence_init();
+  }
+  if (warp == 5) {
+    tmem_alloc(&sm.tmem_base, 512);
+    tmem_relinquish();
+  }
+  int s0 = 0, e0 = 0, s1 = 0, e1 = 0;
+  if (warp < 4) {
+    const int r = threadIdx.x;
+    const bool valid = r < tile.n_rows;
+    if (valid) {
+      int4 m = masks[tile.mask_row + r];
+      s0 = m.x; e0 = max(m.y, m.x); s1 = m.z; e1 = max(m.w, m.z);
+    }
+    reduce_row_ranges(sm.red, warp, lane, valid, s0, e0, s1, e1);
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const TileBounds bounds = combine_bounds(sm.red);
+  const uint32_t tmem = sm.tmem_base;
+  volatile int* abort_word = &sm.abort_word;
+  KvTileIter it;
+  it.init(kv_entries + tile.kv_off, tile.n_kv, block_size, bounds);
+
+  if (warp == 4) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      mbar_expect_tx(&sm.q_full, kTileBytes);
+      tma_load_3d(sm.q, &tm_q, &sm.q_full, 0, tile.head, tile.q_row);
+      tma_load_3d(sm.q + kHalfBytes, &tm_q, &sm.q_full, 64, tile.head, tile.q_row);
+      int j = 0;
+      bool ok = true;
+      int k_pending[2] = {-1, -1}, v_pending[2] = {-1, -1};  // parity of the last armed phase
+      while (ok && it.next()) {
+        const int st = j & 1, u = j >> 1;
+        ok = mbar_wait(&sm.k_empty[st], (u & 1) ^ 1, abort_word);
+        if (!ok) break;
+        mbar_expect_tx(&sm.k_full[st], kTileBytes);
+        tma_load_3d(sm.k[st], &tm_kv, &sm.k_full[st], 0, kv_head, it.row);
+        tma_load_3d(sm.k[st] + kHalfBytes, &tm_kv, &sm.k_full[st], 64, kv_head, it.row);
+        k_pending[st] = u & 1;
+        ok = mbar_wait(&sm.v_empty[st], (u & 1) ^ 1, abort_word);
+        if (!ok) break;
+        mbar_expect_tx(&sm.v_full[st], kTileBytes);
+        tma_load_3d(sm.v[st], &tm_kv, &sm.v_full[st], 0, hkv + kv_head, it.row);
+        tma_load_3d(sm.v[st] + kHalfBytes, &tm_kv, &sm.v_full[st], 64, hkv + kv_head, it.row);
+        v_pending[st] = u & 1;
+        ++j;
+      }
+      if (!ok) {
+        // give copies already in flight a bounded chance to land before the CTA retires
+        for (int st = 0; st < 2; ++st) {
+          if (k_pending[st] >= 0)
+            for (int spin = 0; spin < 200000 && !mbar_try_wait(&sm.k_full[st], k_pending[st]); ++spin) {}
+          if (v_pending[st] >= 0)
+            for (int spin = 0; spin < 200000 && !mbar_try_wait(&sm.v_full[st], v_pending[st]); ++spin) {}
+        }
+      }
+    }
+  } else if (warp == 5) {
+    // ------------------------------------------------------------ UMMA issuer
+    constexpr uint32_t idesc_qk = make_idesc_bf16(128, 128, 0, 0);
+    constexpr uint32_t idesc_pv = make_idesc_bf16(128, 128, 0, 1);  // B = V is MN-major
+    const uint32_t q_addr = smem_u32(sm.q), p_addr = smem_u32(sm.p);
+    bool ok = mbar_wait(&sm.q_full, 0, abort_word);
+    int j = 0;
+    auto issue_pv = [&](int i) -> bool {
+      const int st = i & 1, u = i >> 1;
+      if (!mbar_wait(&sm.p_ready[st], u & 1, abort_word)) return false;
+      if (!mbar_wait(&sm.v_full[st], u & 1, abort_word)) return false;
+      tc_fence_after();
+      if (lane == 0) {
+        const uint32_t v_addr = smem_u32(sm.v[st]);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          // 16 key rows per UMMA; V rows are 128 B apart inside a 64-wide half, halves 16 KB apart
+          uint64_t bdesc = make_sdesc_sw128(v_addr + k * 2048, kHalfBytes, 1024);
+          if (kPSmem) {
+            uint64_t adesc = make_sdesc_sw128(p_addr + (k >> 2) * kHalfBytes + (k & 3) * 32, 16, 1024);
+            umma_ss(tmem + 256, adesc, bdesc, idesc_pv, (i > 0 || k > 0) ? 1u : 0u);
+          } else {
+            umma_ts(tmem + 256, tmem + st * 128 + k * 8, bdesc, idesc_pv, (i > 0 || k > 0) ? 1u : 0u);
+          }
+        }
+        umma_commit(&sm.o_done);
+        umma_commit(&sm.v_empty[st]);
+      }
+      __syncwarp();
+      return true;
+    };
+    while (ok && it.next()) {
+      const int st = j & 1, u = j >> 1;
+      ok = mbar_wait(&sm.k_full[st], u & 1, abort_word);
+      if (!ok) break;
+      tc_fence_after();
+      if (lane == 0) {
+        const uint32_t k_addr = smem_u32(sm.k[st]);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          uint64_t adesc = make_sdesc_sw128(q_addr + (k >> 2) * kHalfBytes + (k & 3) * 32, 16, 1024);
+          uint64_t bdesc = make_sdesc_sw128(k_addr + (k >> 2) * kHalfBytes + (k & 3) * 32, 16, 1024);
+          umma_ss(tmem + st * 128, adesc, bdesc, idesc_qk, k > 0 ? 1u : 0u);
+        }
+        umma_commit(&sm.s_full[st]);
+        umma_commit(&sm.k_empty[st]);
+      }
+      __syncwarp();
+      if (j > 0) ok = issue_pv(j - 1);
+      ++j;
+    }
+    if (ok && j > 0) ok = issue_pv(j - 1);
+    if (ok && j > 0) {
+      // keep TMEM alive until the last accumulate retired (the epilogue also waits on it)
+      mbar_wait(&sm.o_done, (j - 1) & 1, abort_word);
+    }
+  } else {
+    // ------------------------------------------------------------ softmax + epilogue
+    const int r = threadIdx.x;
+    const uint32_t lane_base = uint32_t(warp * 32) << 16;
+    const float sl2 = scale * 1.4426950408889634f;
+    const int len0 = e0 - s0, len1 = e1 - s1;
+    float m_run = -INFINITY, l_run = 0.f;
+    int j = 0;
+    bool ok = true;
+    while (ok && it.next()) {
+      const int st = j & 1, u = j >> 1;
+      ok = mbar_wait(&sm.s_full[st], u & 1, abort_word);
+      if (!ok) break;
+      tc_fence_after();
+      uint32_t sreg[128];
+      const uint32_t s_addr = tmem + lane_base + st * 128;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) tmem_ld32(s_addr + c * 32, sreg + c * 32);
+      tmem_wait_ld();
+      float mx = -INFINITY;
+      if (it.full) {
+#pragma unroll
+        for (int c = 0; c < 128; ++c) mx = fmaxf(mx, __uint_as_float(sreg[c]));
+      } else {
+        const int rel0 = it.pos0 - s0, rel1 = it.pos0 - s1;
+#pragma unroll
+        for (int c = 0; c < 128; ++c) {
+          bool allow = (unsigned(rel0 + c) < unsigned(len0)) || (unsigned(rel1 + c) < unsigned(len1));
+          allow = allow && (c < it.n_valid);
+          float sv = allow ? __uint_as_float(sreg[c]) : -INFINITY;
+          sreg[c] = __float_as_uint(sv);
+          mx = fmaxf(mx, sv);
+        }
+      }
+      const float m_new = fmaxf(m_run, mx);
+      const float m_sub = (m_new == -INFINITY) ? 0.f : m_new * sl2;
+      const float alpha = (m_new == -INFINITY) ? 1.f : fast_exp2(m_run * sl2 - m_sub);
+      float psum = 0.f;
+      uint32_t preg[64];
+#pragma unroll
+      for (int c = 0; c < 64; ++c) {
+        float p0 = fast_exp2(fmaf(__uint_as_float(sreg[2 * c]), sl2, -m_sub));
+        float p1 = fast_exp2(fmaf(__uint_as_float(sreg[2 * c + 1]), sl2, -m_sub));
+        psum += p0 + p1;
+        preg[c] = pack_bf16x2(p0, p1);
+      }
+      l_run = l_run * alpha + psum;
+      m_run = m_new;
+      if (kPSmem) {
+        // the single P buffer is free once the previous accumulate retired
+        if (j > 0) {
+          ok = mbar_wait(&sm.o_done, (j - 1) & 1, abort_word);
+          if (!ok) break;
+          tc_fence_after();
+        }
+#pragma unroll
+        for (int ch = 0; ch < 16; ++ch) {
+          uint4 val = make_uint4(preg[4 * ch], preg[4 * ch + 1], preg[4 * ch + 2], preg[4 * ch + 3]);
+          const int half = ch >> 3, cc = ch & 7;
+          *reinterpret_cast<uint4*>(sm.p + half * kHalfBytes + r * 128 + ((cc ^ (r & 7)) << 4)) = val;
+        }
+        fence_proxy_async_smem();
+      } else {
+        tmem_st32(s_addr, preg);
+        tmem_st32(s_addr + 32, preg + 32);
+        if (j > 0) {
+          ok = mbar_wait(&sm.o_done, (j - 1) & 1, abort_word);
+          if (!ok) break;
+          tc_fence_after();
+        }
+      }
+      if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
+        const uint32_t o_addr = tmem + lane_base + 256;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint32_t oreg[32];
+          tmem_ld32(o_addr + c * 32, oreg);
+          tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) oreg[i] = __float_as_uint(__uint_as_float(oreg[i]) * alpha);
+          tmem_st32(o_addr + c * 32, oreg);
+        }
+      }
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(&sm.p_ready[st]);
+      ++j;
+    }
+    // epilogue
+    if (ok && j > 0) {
+      ok = mbar_wait(&sm.o_done, (j - 1) & 1, abort_word);
+      tc_fence_after();
+    }
+    ok = __all_sync(0xffffffffu, ok);
+    if (ok) {
+      const bool store = r < tile.n_rows;
+      const float inv_l = l_run > 0.f ? 1.f / l_run : 0.f;
+      __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(ptrs.out[tile.out_dev]) +
+                           (size_t(tile.out_row + r) * hq + tile.head) * kHeadDim;
+      if (store)
+        ptrs.lse[tile.out_dev][size_t(tile.head) * lse_stride + tile.out_row + r] =
+            l_run > 0.f ? m_run * scale + logf(l_run) : -INFINITY;
+      const uint32_t o_addr = tmem + lane_base + 256;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t oreg[32];
+        if (j > 0) {  // warp-uniform: the TMEM load is a warp-collective instruction
+          tmem_ld32(o_addr + c * 32, oreg);
+          tmem_wait_ld();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) oreg[i] = 0;
+        }
+        if (store) {
+          uint32_t packed[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i)
+            packed[i] = pack_bf16x2(__uint_as_float(oreg[2 * i]) * inv_l, __uint_as_float(oreg[2 * i + 1]) * inv_l);
+          uint4* dst = reinterpret_cast<uint4*>(out + c * 32);
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+            dst[i] = make_uint4(packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 5) {
+    tc_fence_after();
+    tmem_dealloc(tmem, 512);
+  }
+  if (threadIdx.x == 0 && sm.abort_word) atomicExch(status, kStatusBarrierTimeout);
+}
+
+static int g_fwd_attr_set[2] = {0, 0};
+
+}  // namespace dcpk
+
+using namespace dcpk;
+
+// Launches the forward kernel over `n_tiles` tiles.  `variant` 0 keeps P in TMEM (TS
+// UMMA), 1 stages P through shared memory (SS UMMA).  Returns 0 or a negative error.
+extern "C" int dcpk_attn_fwd(const void* q_arena, long q_rows, const void* kv_arena, long kv_rows, int hq,
+                             int hkv, const void* tiles, int n_tiles, const void* kv_entries,
+                             const void* masks, void* const* out_ptrs, float* const* lse_ptrs, int n_dst,
+                             int lse_stride, int block_size, float scale, int* status, int variant,
+                             void* stream) {
+  if (n_tiles <= 0) return 0;
+  if (n_dst > kMaxPeers || hq % hkv != 0) return -3;
+  CUtensorMap tm_q, tm_kv;
+  if (encode_arena_map(&tm_q, q_arena, uint64_t(q_rows), uint32_t(hq), kHeadDim, 128)) return -1;
+  if (encode_arena_map(&tm_kv, kv_arena, uint64_t(kv_rows), uint32_t(2 * hkv), kHeadDim, 128)) return -1;
+  PeerPtrs pp;
+  for (int i = 0; i < kMaxPeers; ++i) {
+    pp.out[i] = i < n_dst ? out_ptrs[i] : nullptr;
+    pp.lse[i] = i < n_dst ? lse_ptrs[i] : nullptr;
+  }
+  const int smem = int(sizeof(FwdSmem)) + 1024;
+  const int v = variant ? 1 : 0;
+  if (!g_fwd_attr_set[v]) {
+    cudaError_t e = v ? cudaFuncSetAttribute(attn_fwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)
+                      : cudaFuncSetAttribute(attn_fwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return -4;
+    g_fwd_attr_set[v] = 1;
+  }
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (v)
+    attn_fwd_kernel<true><<<n_tiles, kFwdThreads, smem, s>>>(
+        tm_q, tm_kv, static_cast<const AttnTile*>(tiles), static_cast<const KvEntry*>(kv_entries),
+        static_cast<const int4*>(masks), pp, hq, hkv, lse_stride, block_size, scale, status);
+  else
+    attn_fwd_kernel<false><<<n_tiles, kFwdThreads, smem, s>>>(
+        tm_q, tm_kv, static_cast<const AttnTile*>(tiles), static_cast<const KvEntry*>(kv_entries),
+        static_cast<const int4*>(masks), pp, hq, hkv, lse_stride, block_size, scale, status);
+  return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}

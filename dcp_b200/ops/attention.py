@@ -1,0 +1,144 @@
+"""Blockwise range-masked attention: host-side table building, kernel launch, fp32 reference.
+
+The kernels (``csrc/kernels/attn_fwd.cu``, ``attn_bwd.cu``) consume flat int32 tables that
+describe 128-query tiles, the KV blocks each tile attends to, and two half-open key ranges per
+query.  ``AttnRow`` is the Python-side unit: one Q block of one plan stage (what one row of the
+reference's AttnInstr block tables describes, dcp/core/instructions.py:479-626).
+"""
+from __future__ import annotations
+
+import ctypes
+from dataclasses import dataclass, field
+from typing import List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+
+from . import _lib
+
+TILE_M = 128
+TILE_N = 128
+HEAD_DIM = 128
+
+
+@dataclass
+class AttnRow:
+    """One Q block and the KV blocks it attends to within one stage.
+
+    q_row/out_row are arena rows; ``kv`` lists (arena_row, n_tokens) per KV block in position
+    order; ``ranges`` is int32 [n_tokens, 4] = (s0, e0, s1, e1) in concatenated-KV positions
+    where KV block i covers positions [i*block_size, (i+1)*block_size).
+    """
+
+    q_row: int
+    n_tokens: int
+    heads: Sequence[int]
+    kv: List[Tuple[int, int]]
+    ranges: np.ndarray
+    out_dev: int = 0
+    out_row: int = 0
+    # backward only: destination of dQ / per-KV-block destination of dKV
+    dq_dev: int = 0
+    dq_row: int = 0
+    dkv: List[Tuple[int, int]] = field(default_factory=list)  # (dev, row) per KV block
+
+
+@dataclass
+class FwdTables:
+    tiles: torch.Tensor       # int32 [n_tiles, 8]
+    kv_entries: torch.Tensor  # int32 [n_entries, 2]
+    masks: torch.Tensor       # int32 [n_mask_rows, 4]
+    n_tiles: int
+    block_size: int
+    flops: float = 0.0
+
+
+def _pair_count(ranges: np.ndarray) -> float:
+    """Number of (query, key) pairs allowed by a [n,4] range table (ranges assumed disjoint)."""
+    r = ranges.astype(np.int64)
+    return float(np.maximum(r[:, 1] - r[:, 0], 0).sum() + np.maximum(r[:, 3] - r[:, 2], 0).sum())
+
+
+def build_fwd_tables(rows: Sequence[AttnRow], block_size: int, device) -> FwdTables:
+    tiles, entries, masks = [], [], []
+    mask_row = 0
+    pairs = 0.0
+    for row in rows:
+        kv_off = len(entries)
+        entries.extend((int(r), int(n)) for r, n in row.kv)
+        rng = np.ascontiguousarray(row.ranges, dtype=np.int32).reshape(-1, 4)
+        assert rng.shape[0] == row.n_tokens
+        masks.append(rng)
+        pairs += _pair_count(rng) * len(row.heads)
+        n_sub = (row.n_tokens + TILE_M - 1) // TILE_M
+        for t in range(n_sub):
+            n_rows = min(TILE_M, row.n_tokens - t * TILE_M)
+            for h in row.heads:
+                tiles.append((row.q_row + t * TILE_M, n_rows, int(h), kv_off, len(row.kv),
+                              mask_row + t * TILE_M, row.out_dev, row.out_row + t * TILE_M))
+        mask_row += row.n_tokens
+    # longest tiles first: the grid is scheduled in index order, so this is LPT packing
+    tiles.sort(key=lambda x: -x[4])
+    t_np = np.asarray(tiles, dtype=np.int32).reshape(-1, 8)
+    e_np = np.asarray(entries, dtype=np.int32).reshape(-1, 2)
+    m_np = np.concatenate(masks, axis=0) if masks else np.zeros((0, 4), np.int32)
+    to = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(device, non_blocking=True)
+    return FwdTables(to(t_np), to(e_np), to(m_np), len(tiles), block_size, flops=4.0 * pairs * HEAD_DIM)
+
+
+def _ptr_array(tensors) -> ctypes.Array:
+    arr = (ctypes.c_void_p * len(tensors))()
+    for i, t in enumerate(tensors):
+        arr[i] = t if isinstance(t, int) else t.data_ptr()
+    return arr
+
+
+def attn_fwd(q_arena: torch.Tensor, kv_arena: torch.Tensor, tables: FwdTables, out_dsts, lse_dsts,
+             scale: float, status: torch.Tensor, variant: int = 0):
+    """Run the forward kernel.
+
+    q_arena: bf16 [rows, hq, 128]; kv_arena: bf16 [rows, 2, hkv, 128]; out_dsts / lse_dsts: lists of
+    destination arenas (tensors or raw device addresses; index 0 = this rank), every out arena
+    bf16 [rows_o, hq, 128] with its lse fp32 [hq, rows_o].
+    """
+    lib = _lib.load()
+    assert q_arena.dtype == torch.bfloat16 and kv_arena.dtype == torch.bfloat16
+    assert q_arena.is_contiguous() and kv_arena.is_contiguous()
+    assert q_arena.shape[-1] == HEAD_DIM and kv_arena.shape[-1] == HEAD_DIM
+    hq, hkv = q_arena.shape[1], kv_arena.shape[2]
+    lse0 = lse_dsts[0]
+    lse_stride = lse0.shape[1] if not isinstance(lse0, int) else int(out_dsts[0].shape[0])
+    rc = lib.dcpk_attn_fwd(
+        _lib.ptr(q_arena), ctypes.c_long(q_arena.shape[0]), _lib.ptr(kv_arena), ctypes.c_long(kv_arena.shape[0]),
+        ctypes.c_int(hq), ctypes.c_int(hkv), _lib.ptr(tables.tiles), ctypes.c_int(tables.n_tiles),
+        _lib.ptr(tables.kv_entries), _lib.ptr(tables.masks), _ptr_array(out_dsts), _ptr_array(lse_dsts),
+        ctypes.c_int(len(out_dsts)), ctypes.c_int(lse_stride), ctypes.c_int(tables.block_size),
+        ctypes.c_float(scale), _lib.ptr(status), ctypes.c_int(variant), _lib.stream_handle())
+    _lib.check(rc, "dcpk_attn_fwd")
+
+
+# ----------------------------------------------------------------------------- reference
+def ranges_to_dense(ranges: np.ndarray, n_kv: int) -> torch.Tensor:
+    """[n_q, 4] ranges -> bool [n_q, n_kv] mask."""
+    r = torch.as_tensor(np.asarray(ranges)).long().reshape(-1, 4)
+    pos = torch.arange(n_kv)[None, :]
+    return ((pos >= r[:, 0:1]) & (pos < r[:, 1:2])) | ((pos >= r[:, 2:3]) & (pos < r[:, 3:4]))
+
+
+def attention_reference(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, mask: torch.Tensor, scale: float):
+    """fp32 dense masked attention. q [nq, hq, d], k/v [nk, hkv, d], mask bool [nq, nk].
+
+    Returns (out [nq, hq, d] fp32, lse [hq, nq] fp32); fully masked rows give out 0, lse -inf.
+    """
+    hq, hkv = q.shape[1], k.shape[1]
+    g = hq // hkv
+    qf = q.float().permute(1, 0, 2)
+    kf = k.float().permute(1, 0, 2).repeat_interleave(g, dim=0)
+    vf = v.float().permute(1, 0, 2).repeat_interleave(g, dim=0)
+    s = torch.einsum("hqd,hkd->hqk", qf, kf) * scale
+    s = s.masked_fill(~mask.to(s.device)[None], float("-inf"))
+    lse = torch.logsumexp(s, dim=-1)
+    p = torch.exp(s - torch.where(torch.isinf(lse), torch.zeros_like(lse), lse)[..., None])
+    p = torch.where(torch.isinf(lse)[..., None], torch.zeros_like(p), p)
+    out = torch.einsum("hqk,hkd->hqd", p, vf).permute(1, 0, 2)
+    return out, lse
