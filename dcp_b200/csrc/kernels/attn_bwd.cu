@@ -1,0 +1,416 @@
+// Blockwise range-masked attention backward for sm_100a.
+//
+// One CTA owns one 128-row KV tile of one KV head and walks a host-built list of
+// (64-query tile, query head) items that attend to it.  Everything is computed in the
+// transposed orientation so that the probability and score-gradient tiles land in TMEM
+// with lane = key row, ready to be the A operand of the accumulating UMMAs:
+//   S^T  = K  Q^T          (SS, M=128 keys, N=64 queries, K=d)
+//   dP^T = V  dO^T         (SS)
+//   P^T  = exp2(S^T*c - lse),  dS^T = P^T o (dP^T - delta) * scale      (threads, TMEM)
+//   dV  += P^T  dO         (TS, M=128, N=d, K=64 queries)
+//   dK  += dS^T Q          (TS)
+//   dQ^T = K^T dS^T        (SS, M=d, N=64 queries, K=128 keys; dS^T staged in smem)
+// dQ^T is read back with lane = d, so each warp adds 128 contiguous bytes per query row
+// with red.global.add.f32 into the fp32 dQ accumulator of the destination (which may be
+// a peer GPU's memory).  dK/dV stay in TMEM for the CTA's lifetime and are added once,
+// at the end, into the fp32 dKV accumulator of their owner.
+// TMEM columns: S^T [0,64) dP^T [64,128) P^T [128,160) dS^T [160,192) dQ^T [192,256)
+//               dK [256,384) dV [384,512).
+//
+// Reference behaviour covered: the varlen backward the executor calls at
+// dcp/runtime/flash_attention/executor.py:1058-1115, plus the blockwise partial sums
+// that follow it (dcp/ops/fused_ops.py:1087-1360), which the atomics make unnecessary.
+#include <limits.h>
+#include <math.h>
+
+#include "attn_common.cuh"
+#include "ptx.cuh"
+#include "tmap.cuh"
+
+namespace dcpk {
+
+static constexpr int kBwdThreads = 192;
+static constexpr int kQTile = 64;
+static constexpr int kKvHalf = 128 * 64 * 2;  // [128 x 64] bf16 half tile, 16 KB
+static constexpr int kQHalf = 64 * 64 * 2;    // [64 x 64] bf16 half tile, 8 KB
+
+struct BwdItem {
+  int q_row;     // arena row of the 64-query tile (same row addresses Q, dO, lse, delta)
+  int n_rows;    // valid queries
+  int head;      // query head
+  int kv_pos0;   // position of this CTA's first key inside the item's concatenated KV
+  int mask_row;  // row in the range table
+  int dq_dev;    // destination index of the dQ accumulator
+  int dq_row;    // arena row in that accumulator
+  int full;      // 1: every (query, key) pair of the tile is allowed
+};
+
+struct BwdCta {
+  int kv_row;    // arena row of the 128-key tile
+  int n_valid;   // valid keys
+  int kv_head;
+  int item_off, n_items;
+  int dkv_dev, dkv_row;
+  int pad;
+};
+
+struct BwdPtrs {
+  float* dq[kMaxPeers];   // fp32 [rows, hq, d]
+  float* dkv[kMaxPeers];  // fp32 [rows, 2, hkv, d]
+};
+
+struct __align__(1024) BwdSmem {
+  uint8_t k[2 * kKvHalf];
+  uint8_t v[2 * kKvHalf];
+  uint8_t q[2][2 * kQHalf];
+  uint8_t dout[2][2 * kQHalf];
+  uint8_t ds[kKvHalf];     // dS^T: [128 keys x 64 queries]
+  // per-warp private copies: the four gradient warps never synchronise with each other
+  float lse2[4][kQTile];
+  float delta[4][kQTile];
+  int4 rng[4][kQTile];
+  uint64_t kv_full, qdo_full[2], qdo_empty[2], sdp_full, s_free, p_ready, dq_full;
+  uint32_t tmem_base;
+  int abort_word;
+};
+
+__device__ __forceinline__ void red_add_f32(float* p, float v) {
+  asm volatile("red.global.add.f32 [%0], %1;" ::"l"(p), "f"(v) : "memory");
+}
+__device__ __forceinline__ void red_add_v4(float* p, float a, float b, float c, float d) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(a), "f"(b), "f"(c), "f"(d)
+               : "memory");
+}
+
+__global__ void __launch_bounds__(kBwdThreads, 1)
+attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
+                const __grid_constant__ CUtensorMap tm_kv, const BwdCta* __restrict__ ctas,
+                const BwdItem* __restrict__ items, const int4* __restrict__ masks,
+                const float* __restrict__ lse, const float* __restrict__ delta, BwdPtrs ptrs, int hq, int hkv,
+                int stat_stride, float scale, int* __restrict__ status) {
+  extern __shared__ uint8_t smem_raw[];
+  BwdSmem& sm = *reinterpret_cast<BwdSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const BwdCta cta = ctas[blockIdx.x];
+  const BwdItem* my_items = items + cta.item_off;
+  const int n_items = cta.n_items;
+
+  if (threadIdx.x == 128) {
+    tma_prefetch_desc(&tm_q);
+    tma_prefetch_desc(&tm_do);
+    tma_prefetch_desc(&tm_kv);
+    mbar_init(&sm.kv_full, 1);
+    for (int i = 0; i < 2; ++i) { mbar_init(&sm.qdo_full[i], 1); mbar_init(&sm.qdo_empty[i], 1); }
+    mbar_init(&sm.sdp_full, 1);
+    mbar_init(&sm.s_free, 128);
+    mbar_init(&sm.p_ready, 128);
+    mbar_init(&sm.dq_full, 1);
+    sm.abort_word = 0;
+    mbar_fence_init();
+  }
+  if (warp == 5) {
+    tmem_alloc(&sm.tmem_base, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = sm.tmem_base;
+  volatile int* abort_word = &sm.abort_word;
+  constexpr uint32_t cS = 0, cdP = 64, cP = 128, cdS = 160, cdQ = 192, cdK = 256, cdV = 384;
+
+  if (warp == 4) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      mbar_expect_tx(&sm.kv_full, 4 * kKvHalf);
+      tma_load_3d(sm.k, &tm_kv, &sm.kv_full, 0, cta.kv_head, cta.kv_row);
+      tma_load_3d(sm.k + kKvHalf, &tm_kv, &sm.kv_full, 64, cta.kv_head, cta.kv_row);
+      tma_load_3d(sm.v, &tm_kv, &sm.kv_full, 0, hkv + cta.kv_head, cta.kv_row);
+      tma_load_3d(sm.v + kKvHalf, &tm_kv, &sm.kv_full, 64, hkv + cta.kv_head, cta.kv_row);
+      bool ok = true;
+      int pending[2] = {-1, -1};
+      for (int i = 0; i < n_items && ok; ++i) {
+        const int st = i & 1, u = i >> 1;
+        const BwdItem itx = my_items[i];
+        ok = mbar_wait(&sm.qdo_empty[st], (u & 1) ^ 1, abort_word);
+        if (!ok) break;
+        mbar_expect_tx(&sm.qdo_full[st], 4 * kQHalf);
+        tma_load_3d(sm.q[st], &tm_q, &sm.qdo_full[st], 0, itx.head, itx.q_row);
+        tma_load_3d(sm.q[st] + kQHalf, &tm_q, &sm.qdo_full[st], 64, itx.head, itx.q_row);
+        tma_load_3d(sm.dout[st], &tm_do, &sm.qdo_full[st], 0, itx.head, itx.q_row);
+        tma_load_3d(sm.dout[st] + kQHalf, &tm_do, &sm.qdo_full[st], 64, itx.head, itx.q_row);
+        pending[st] = u & 1;
+      }
+      if (!ok) {
+        for (int st = 0; st < 2; ++st)
+          if (pending[st] >= 0)
+            for (int spin = 0; spin < 200000 && !mbar_try_wait(&sm.qdo_full[st], pending[st]); ++spin) {}
+      }
+    }
+  } else if (warp == 5) {
+    // ------------------------------------------------------------ UMMA issuer
+    constexpr uint32_t idesc_sdp = make_idesc_bf16(128, 64, 0, 0);
+    constexpr uint32_t idesc_acc = make_idesc_bf16(128, 128, 0, 1);
+    constexpr uint32_t idesc_dq = make_idesc_bf16(128, 64, 1, 1);
+    const uint32_t k_addr = smem_u32(sm.k), v_addr = smem_u32(sm.v), ds_addr = smem_u32(sm.ds);
+    bool ok = mbar_wait(&sm.kv_full, 0, abort_word);
+    auto issue_acc = [&](int t) -> bool {
+      const int st = t & 1;
+      if (!mbar_wait(&sm.p_ready, t & 1, abort_word)) return false;
+      tc_fence_after();
+      if (lane == 0) {
+        const uint32_t q_addr = smem_u32(sm.q[st]), do_addr = smem_u32(sm.dout[st]);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {  // 16 queries per step
+          uint64_t b_do = make_sdesc_sw128(do_addr + k * 2048, kQHalf, 1024);
+          umma_ts(tmem + cdV, tmem + cP + k * 8, b_do, idesc_acc, (t > 0 || k > 0) ? 1u : 0u);
+        }
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          uint64_t b_q = make_sdesc_sw128(q_addr + k * 2048, kQHalf, 1024);
+          umma_ts(tmem + cdK, tmem + cdS + k * 8, b_q, idesc_acc, (t > 0 || k > 0) ? 1u : 0u);
+        }
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {  // 16 keys per step
+          uint64_t a_kt = make_sdesc_sw128(k_addr + k * 2048, kKvHalf, 1024);
+          uint64_t b_ds = make_sdesc_sw128(ds_addr + k * 2048, 16, 1024);
+          umma_ss(tmem + cdQ, a_kt, b_ds, idesc_dq, k > 0 ? 1u : 0u);
+        }
+        umma_commit(&sm.dq_full);
+        umma_commit(&sm.qdo_empty[st]);
+      }
+      __syncwarp();
+      return true;
+    };
+    for (int i = 0; i < n_items && ok; ++i) {
+      const int st = i & 1, u = i >> 1;
+      ok = mbar_wait(&sm.qdo_full[st], u & 1, abort_word);
+      if (ok && i > 0) ok = mbar_wait(&sm.s_free, (i - 1) & 1, abort_word);
+      if (!ok) break;
+      tc_fence_after();
+      if (lane == 0) {
+        const uint32_t q_addr = smem_u32(sm.q[st]), do_addr = smem_u32(sm.dout[st]);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          uint64_t a = make_sdesc_sw128(k_addr + (k >> 2) * kKvHalf + (k & 3) * 32, 16, 1024);
+          uint64_t b = make_sdesc_sw128(q_addr + (k >> 2) * kQHalf + (k & 3) * 32, 16, 1024);
+          umma_ss(tmem + cS, a, b, idesc_sdp, k > 0 ? 1u : 0u);
+        }
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          uint64_t a = make_sdesc_sw128(v_addr + (k >> 2) * kKvHalf + (k & 3) * 32, 16, 1024);
+          uint64_t b = make_sdesc_sw128(do_addr + (k >> 2) * kQHalf + (k & 3) * 32, 16, 1024);
+          umma_ss(tmem + cdP, a, b, idesc_sdp, k > 0 ? 1u : 0u);
+        }
+        umma_commit(&sm.sdp_full);
+      }
+      __syncwarp();
+      if (i > 0) ok = issue_acc(i - 1);
+    }
+    if (ok && n_items > 0) ok = issue_acc(n_items - 1);
+    if (ok && n_items > 0) mbar_wait(&sm.dq_full, (n_items - 1) & 1, abort_word);
+  } else {
+    // ------------------------------------------------------------ softmax-gradient threads
+    const int r = threadIdx.x;  // key row inside the tile == TMEM lane
+    const uint32_t lane_base = uint32_t(warp * 32) << 16;
+    const float sl2 = scale * 1.4426950408889634f;
+    const bool key_valid = r < cta.n_valid;
+    bool ok = true;
+    BwdItem prev{};
+    // adds dQ^T of the previous item (lane = d, column = query) into its fp32 accumulator
+    auto flush_dq = [&](const BwdItem& itx) {
+      float* dq = ptrs.dq[itx.dq_dev] + (size_t(itx.dq_row) * hq + itx.head) * kHeadDim + r;
+      const size_t row_stride = size_t(hq) * kHeadDim;
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        uint32_t reg[32];
+        tmem_ld32(tmem + lane_base + cdQ + c * 32, reg);
+        tmem_wait_ld();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const int qi = c * 32 + i;
+          if (qi < itx.n_rows) red_add_f32(dq + qi * row_stride, __uint_as_float(reg[i]));
+        }
+      }
+    };
+    for (int t = 0; t < n_items && ok; ++t) {
+      const BwdItem itx = my_items[t];
+      // per-query statistics and ranges of this item -> this warp's smem copy
+      __syncwarp();
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int qi = lane + 32 * h;
+        const bool qv = qi < itx.n_rows;
+        const float l = qv ? lse[size_t(itx.head) * stat_stride + itx.q_row + qi] : INFINITY;
+        sm.lse2[warp][qi] = (l == -INFINITY) ? INFINITY : l * 1.4426950408889634f;
+        sm.delta[warp][qi] = qv ? delta[size_t(itx.head) * stat_stride + itx.q_row + qi] : 0.f;
+        int4 m = make_int4(0, 0, 0, 0);
+        if (qv) m = masks[itx.mask_row + qi];
+        m.y = max(m.y, m.x); m.w = max(m.w, m.z);
+        sm.rng[warp][qi] = m;
+      }
+      __syncwarp();
+      ok = mbar_wait(&sm.sdp_full, t & 1, abort_word);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      uint32_t sreg[64], dreg[64];
+      tmem_ld32(tmem + lane_base + cS, sreg);
+      tmem_ld32(tmem + lane_base + cS + 32, sreg + 32);
+      tmem_ld32(tmem + lane_base + cdP, dreg);
+      tmem_ld32(tmem + lane_base + cdP + 32, dreg + 32);
+      tmem_wait_ld();
+      tc_fence_before();
+      mbar_arrive(&sm.s_free);
+      if (t > 0) {
+        ok = mbar_wait(&sm.dq_full, (t - 1) & 1, abort_word);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tc_fence_after();
+        flush_dq(prev);
+      }
+      const int kpos = itx.kv_pos0 + r;
+      uint32_t preg[32], dsreg[32];
+#pragma unroll
+      for (int c = 0; c < 32; ++c) {
+        float pv[2], dv[2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const int qi = 2 * c + h;
+          bool allow = key_valid;
+          if (!itx.full) {
+            const int4 m = sm.rng[warp][qi];
+            allow = allow && ((unsigned(kpos - m.x) < unsigned(m.y - m.x)) || (unsigned(kpos - m.z) < unsigned(m.w - m.z)));
+          } else {
+            allow = allow && (qi < itx.n_rows);
+          }
+          const float p = allow ? fast_exp2(fmaf(__uint_as_float(sreg[qi]), sl2, -sm.lse2[warp][qi])) : 0.f;
+          pv[h] = p;
+          dv[h] = p * (__uint_as_float(dreg[qi]) - sm.delta[warp][qi]) * scale;
+        }
+        preg[c] = pack_bf16x2(pv[0], pv[1]);
+        dsreg[c] = pack_bf16x2(dv[0], dv[1]);
+      }
+      tmem_st32(tmem + lane_base + cP, preg);
+      tmem_st32(tmem + lane_base + cdS, dsreg);
+#pragma unroll
+      for (int ch = 0; ch < 8; ++ch) {
+        uint4 val = make_uint4(dsreg[4 * ch], dsreg[4 * ch + 1], dsreg[4 * ch + 2], dsreg[4 * ch + 3]);
+        *reinterpret_cast<uint4*>(sm.ds + r * 128 + ((ch ^ (r & 7)) << 4)) = val;
+      }
+      fence_proxy_async_smem();
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(&sm.p_ready);
+      prev = itx;
+    }
+    ok = __all_sync(0xffffffffu, ok);
+    if (ok && n_items > 0) {
+      ok = mbar_wait(&sm.dq_full, (n_items - 1) & 1, abort_word);
+      ok = __all_sync(0xffffffffu, ok);
+      if (ok) {
+        tc_fence_after();
+        flush_dq(prev);
+        // dK / dV: lane = key row, 128 fp32 columns each
+        float* dk = ptrs.dkv[cta.dkv_dev] + ((size_t(cta.dkv_row + r) * 2 + 0) * hkv + cta.kv_head) * kHeadDim;
+        float* dv = ptrs.dkv[cta.dkv_dev] + ((size_t(cta.dkv_row + r) * 2 + 1) * hkv + cta.kv_head) * kHeadDim;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint32_t reg[32];
+          tmem_ld32(tmem + lane_base + cdK + c * 32, reg);
+          tmem_wait_ld();
+          if (key_valid) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+              red_add_v4(dk + c * 32 + 4 * i, __uint_as_float(reg[4 * i]), __uint_as_float(reg[4 * i + 1]),
+                         __uint_as_float(reg[4 * i + 2]), __uint_as_float(reg[4 * i + 3]));
+          }
+          tmem_ld32(tmem + lane_base + cdV + c * 32, reg);
+          tmem_wait_ld();
+          if (key_valid) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+              red_add_v4(dv + c * 32 + 4 * i, __uint_as_float(reg[4 * i]), __uint_as_float(reg[4 * i + 1]),
+                         __uint_as_float(reg[4 * i + 2]), __uint_as_float(reg[4 * i + 3]));
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 5) {
+    tc_fence_after();
+    tmem_dealloc(tmem, 512);
+  }
+  if (threadIdx.x == 0 && sm.abort_word) atomicExch(status, kStatusBarrierTimeout);
+}
+
+// delta[h][row] = sum_d dO[row][h][d] * O[row][h][d]; one warp per (row, head)
+__global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_o,
+                                  float* __restrict__ delta, int n_rows, int hq, int stat_stride, int row0) {
+  const int gw = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  if (gw >= n_rows * hq) return;
+  const int row = gw / hq, h = gw % hq;
+  const size_t off = (size_t(row0 + row) * hq + h) * kHeadDim + lane * 4;
+  const uint2 a = *reinterpret_cast<const uint2*>(o + off);
+  const uint2 b = *reinterpret_cast<const uint2*>(d_o + off);
+  const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&a);
+  const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&b);
+  float acc = 0.f;
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    float2 x = __bfloat1622float2(a2[i]), y = __bfloat1622float2(b2[i]);
+    acc += x.x * y.x + x.y * y.y;
+  }
+#pragma unroll
+  for (int s = 16; s > 0; s >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, s);
+  if (lane == 0) delta[size_t(h) * stat_stride + row0 + row] = acc;
+}
+
+static int g_bwd_attr_set = 0;
+
+}  // namespace dcpk
+
+using namespace dcpk;
+
+extern "C" int dcpk_attn_delta(const void* o, const void* d_o, float* delta, int n_rows, int hq, int stat_stride,
+                               int row0, void* stream) {
+  if (n_rows <= 0) return 0;
+  const long warps = long(n_rows) * hq;
+  const int threads = 256;
+  const long blocks = (warps * 32 + threads - 1) / threads;
+  attn_delta_kernel<<<unsigned(blocks), threads, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(o), static_cast<const __nv_bfloat16*>(d_o), delta, n_rows, hq, stat_stride,
+      row0);
+  return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}
+
+// Launches the backward kernel: one CTA per entry of `ctas`.
+extern "C" int dcpk_attn_bwd(const void* q_arena, const void* do_arena, long q_rows, const void* kv_arena,
+                             long kv_rows, int hq, int hkv, const void* ctas, int n_ctas, const void* items,
+                             const void* masks, const float* lse, const float* delta, int stat_stride,
+                             float* const* dq_ptrs, float* const* dkv_ptrs, int n_dst, float scale, int* status,
+                             void* stream) {
+  if (n_ctas <= 0) return 0;
+  if (n_dst > kMaxPeers || hq % hkv != 0) return -3;
+  CUtensorMap tm_q, tm_do, tm_kv;
+  if (encode_arena_map(&tm_q, q_arena, uint64_t(q_rows), uint32_t(hq), kHeadDim, kQTile)) return -1;
+  if (encode_arena_map(&tm_do, do_arena, uint64_t(q_rows), uint32_t(hq), kHeadDim, kQTile)) return -1;
+  if (encode_arena_map(&tm_kv, kv_arena, uint64_t(kv_rows), uint32_t(2 * hkv), kHeadDim, 128)) return -1;
+  BwdPtrs pp;
+  for (int i = 0; i < kMaxPeers; ++i) {
+    pp.dq[i] = i < n_dst ? dq_ptrs[i] : nullptr;
+    pp.dkv[i] = i < n_dst ? dkv_ptrs[i] : nullptr;
+  }
+  const int smem = int(sizeof(BwdSmem)) + 1024;
+  if (!g_bwd_attr_set) {
+    if (cudaFuncSetAttribute(attn_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+      return -4;
+    g_bwd_attr_set = 1;
+  }
+  attn_bwd_kernel<<<n_ctas, kBwdThreads, smem, static_cast<cudaStream_t>(stream)>>>(
+      tm_q, tm_do, tm_kv, static_cast<const BwdCta*>(ctas), static_cast<const BwdItem*>(items),
+      static_cast<const int4*>(masks), lse, delta, pp, hq, hkv, stat_stride, scale, status);
+  return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}

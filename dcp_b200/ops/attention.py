@@ -142,3 +142,118 @@ def attention_reference(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, mask:
     p = torch.where(torch.isinf(lse)[..., None], torch.zeros_like(p), p)
     out = torch.einsum("hqk,hkd->hqd", p, vf).permute(1, 0, 2)
     return out, lse
+
+
+# ----------------------------------------------------------------------------- backward
+Q_TILE_BWD = 64
+
+
+@dataclass
+class BwdTables:
+    ctas: torch.Tensor    # int32 [n_ctas, 8]
+    items: torch.Tensor   # int32 [n_items, 8]
+    masks: torch.Tensor   # int32 [n_mask_rows, 4]
+    n_ctas: int
+    n_items: int
+    flops: float = 0.0
+
+
+def _tile_bounds(rng: np.ndarray, tile: int):
+    """Per-tile union / intersection of the two ranges; rows past the end are neutral."""
+    n = rng.shape[0]
+    n_t = (n + tile - 1) // tile
+    pad = n_t * tile - n
+    r = rng.astype(np.int64)
+    big, small = np.iinfo(np.int32).max, np.iinfo(np.int32).min
+    valid = np.concatenate([np.ones(n, bool), np.zeros(pad, bool)])
+    r = np.concatenate([r, np.zeros((pad, 4), np.int64)], axis=0)
+    e0 = np.maximum(r[:, 1], r[:, 0]); e1 = np.maximum(r[:, 3], r[:, 2])
+    has0 = valid & (e0 > r[:, 0]); has1 = valid & (e1 > r[:, 2])
+    sh = (n_t, tile)
+    u0s = np.where(has0, r[:, 0], big).reshape(sh).min(1); u0e = np.where(has0, e0, small).reshape(sh).max(1)
+    u1s = np.where(has1, r[:, 2], big).reshape(sh).min(1); u1e = np.where(has1, e1, small).reshape(sh).max(1)
+    i0s = np.where(valid, r[:, 0], small).reshape(sh).max(1); i0e = np.where(valid, e0, big).reshape(sh).min(1)
+    i1s = np.where(valid, r[:, 2], small).reshape(sh).max(1); i1e = np.where(valid, e1, big).reshape(sh).min(1)
+    return n_t, (u0s, u0e, u1s, u1e, i0s, i0e, i1s, i1e)
+
+
+def build_bwd_tables(rows: Sequence[AttnRow], block_size: int, hq: int, hkv: int, device) -> BwdTables:
+    """KV-major work lists for the backward kernel: one CTA per (KV tile, KV head)."""
+    group = hq // hkv
+    masks, mask_row = [], 0
+    cta_items = {}  # (kv_row, n_valid, kv_head, dkv_dev, dkv_row) -> list of item arrays
+    pairs = 0.0
+    for row in rows:
+        rng = np.ascontiguousarray(row.ranges, dtype=np.int32).reshape(-1, 4)
+        masks.append(rng)
+        pairs += _pair_count(rng) * len(row.heads)
+        n_qt, (u0s, u0e, u1s, u1e, i0s, i0e, i1s, i1e) = _tile_bounds(rng, Q_TILE_BWD)
+        qt = np.arange(n_qt)
+        n_rows_t = np.minimum(Q_TILE_BWD, row.n_tokens - qt * Q_TILE_BWD)
+        heads = np.asarray(list(row.heads), dtype=np.int64)
+        for e, (kv_row, n_tok) in enumerate(row.kv):
+            dkv_dev, dkv_row = row.dkv[e] if row.dkv else (0, kv_row)
+            for t in range((n_tok + TILE_N - 1) // TILE_N):
+                p0 = e * block_size + t * TILE_N
+                nv = min(TILE_N, n_tok - t * TILE_N)
+                need = ((p0 < u0e) & (p0 + nv > u0s)) | ((p0 < u1e) & (p0 + nv > u1s))
+                idx = qt[need]
+                if idx.size == 0:
+                    continue
+                full = (nv == TILE_N) & (((i0s <= p0) & (i0e >= p0 + nv)) | ((i1s <= p0) & (i1e >= p0 + nv)))
+                for g in np.unique(heads // group):
+                    hs = heads[heads // group == g]
+                    ii = np.repeat(idx, hs.size)
+                    hh = np.tile(hs, idx.size)
+                    arr = np.stack([
+                        row.q_row + ii * Q_TILE_BWD, n_rows_t[ii], hh, np.full(ii.size, p0), mask_row + ii * Q_TILE_BWD,
+                        np.full(ii.size, row.dq_dev), row.dq_row + ii * Q_TILE_BWD, full[ii].astype(np.int64)], axis=1)
+                    key = (kv_row + t * TILE_N, nv, int(g), dkv_dev, dkv_row + t * TILE_N)
+                    cta_items.setdefault(key, []).append(arr)
+        mask_row += row.n_tokens
+    ctas, item_chunks, off = [], [], 0
+    for key, chunks in sorted(cta_items.items(), key=lambda kv: -sum(c.shape[0] for c in kv[1])):
+        n = sum(c.shape[0] for c in chunks)
+        ctas.append((key[0], key[1], key[2], off, n, key[3], key[4], 0))
+        item_chunks.extend(chunks)
+        off += n
+    c_np = np.asarray(ctas, dtype=np.int32).reshape(-1, 8)
+    i_np = (np.concatenate(item_chunks, axis=0) if item_chunks else np.zeros((0, 8))).astype(np.int32)
+    m_np = np.concatenate(masks, axis=0) if masks else np.zeros((0, 4), np.int32)
+    to = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(device, non_blocking=True)
+    return BwdTables(to(c_np), to(i_np), to(m_np), len(ctas), int(off), flops=10.0 * pairs * HEAD_DIM)
+
+
+def attn_delta(out_arena: torch.Tensor, dout_arena: torch.Tensor, delta: torch.Tensor, row0: int, n_rows: int):
+    """delta[h, row] = sum_d dO*O for rows [row0, row0+n_rows) of bf16 [rows, hq, 128] arenas."""
+    lib = _lib.load()
+    rc = lib.dcpk_attn_delta(_lib.ptr(out_arena), _lib.ptr(dout_arena), _lib.ptr(delta), ctypes.c_int(n_rows),
+                             ctypes.c_int(out_arena.shape[1]), ctypes.c_int(delta.shape[1]), ctypes.c_int(row0),
+                             _lib.stream_handle())
+    _lib.check(rc, "dcpk_attn_delta")
+
+
+def attn_bwd(q_arena, do_arena, kv_arena, lse, delta, tables: BwdTables, dq_dsts, dkv_dsts, scale: float,
+             status: torch.Tensor):
+    """Run the backward kernel; dq_dsts/dkv_dsts are fp32 accumulators (zeroed by the caller),
+    [rows, hq, 128] and [rows, 2, hkv, 128]; lse/delta are fp32 [hq, rows]."""
+    lib = _lib.load()
+    hq, hkv = q_arena.shape[1], kv_arena.shape[2]
+    assert q_arena.shape == do_arena.shape and lse.shape == delta.shape
+    rc = lib.dcpk_attn_bwd(
+        _lib.ptr(q_arena), _lib.ptr(do_arena), ctypes.c_long(q_arena.shape[0]), _lib.ptr(kv_arena),
+        ctypes.c_long(kv_arena.shape[0]), ctypes.c_int(hq), ctypes.c_int(hkv), _lib.ptr(tables.ctas),
+        ctypes.c_int(tables.n_ctas), _lib.ptr(tables.items), _lib.ptr(tables.masks), _lib.ptr(lse), _lib.ptr(delta),
+        ctypes.c_int(lse.shape[1]), _ptr_array(dq_dsts), _ptr_array(dkv_dsts), ctypes.c_int(len(dq_dsts)),
+        ctypes.c_float(scale), _lib.ptr(status), _lib.stream_handle())
+    _lib.check(rc, "dcpk_attn_bwd")
+
+
+def attention_reference_bwd(q, k, v, mask, scale, dout):
+    """fp32 autograd through the dense reference. Returns (out, lse, dq, dk, dv)."""
+    qf = q.float().detach().requires_grad_(True)
+    kf = k.float().detach().requires_grad_(True)
+    vf = v.float().detach().requires_grad_(True)
+    out, lse = attention_reference(qf, kf, vf, mask, scale)
+    out.backward(dout.float())
+    return out.detach(), lse.detach(), qf.grad, kf.grad, vf.grad
