@@ -1,0 +1,116 @@
+// pybind11 surface of the native planner: hypergraph partitioning and stage selection.
+#include <pybind11/pybind11.h>
+#include <pybind11/stl.h>
+
+#include "hypergraph.hpp"
+#include "stage_greedy.hpp"
+
+namespace py = pybind11;
+using namespace dcpp;
+
+namespace {
+
+py::tuple py_greedy(const std::set<Device>& devices, const std::set<int>& scheduled,
+                    const std::vector<double>& work_cost, const std::vector<double>& input_size,
+                    const std::vector<std::vector<int>>& work_inputs, const std::vector<std::string>& input_type,
+                    const std::map<Device, std::vector<int>>& device_work,
+                    const std::map<Device, std::map<int, int>>& local_inputs,
+                    const std::map<Device, double>& inter_budget, bool is_bw, int stage_id, py::object /*logger*/,
+                    const std::map<Device, double>& intra_budget) {
+  std::vector<Device> devs(devices.begin(), devices.end());
+  GreedyResult r;
+  {
+    py::gil_scoped_release release;
+    r = greedy_selection_per_device(devs, scheduled, work_cost, input_size, work_inputs, input_type, device_work,
+                                    local_inputs, inter_budget, intra_budget, is_bw, stage_id);
+  }
+  py::dict unlocked;
+  for (auto& kv : r.unlocked) {
+    py::set s;
+    for (int w : kv.second) s.add(py::int_(w));
+    unlocked[py::make_tuple(kv.first.first, kv.first.second)] = s;
+  }
+  py::dict comm;
+  for (auto& kv : r.comm) {
+    py::list l;
+    for (auto& c : kv.second) l.append(py::make_tuple(c.first, py::make_tuple(c.second.first, c.second.second)));
+    comm[py::make_tuple(kv.first.first, kv.first.second)] = l;
+  }
+  return py::make_tuple(unlocked, comm, r.local_inputs);
+}
+
+py::dict py_partition(int n_vertices, const std::vector<int64_t>& vw_comp, const std::vector<int64_t>& vw_mem,
+                      const std::vector<int>& net_offsets, const std::vector<int>& net_pins,
+                      const std::vector<int64_t>& net_weight, int k, const std::vector<int64_t>& cap_comp,
+                      const std::vector<int64_t>& cap_mem, uint64_t seed, int n_tries, const std::vector<int>& fixed,
+                      const std::vector<int>& initial) {
+  Hypergraph hg;
+  hg.n_vertices = n_vertices;
+  hg.vw_comp = vw_comp;
+  hg.vw_mem = vw_mem;
+  hg.net_offsets = net_offsets;
+  hg.net_pins = net_pins;
+  hg.net_weight = net_weight;
+  if (int(vw_comp.size()) != n_vertices || int(vw_mem.size()) != n_vertices ||
+      net_offsets.size() != net_weight.size() + 1 || int(cap_comp.size()) != k || int(cap_mem.size()) != k)
+    throw std::invalid_argument("inconsistent hypergraph arrays");
+  for (int p : net_pins)
+    if (p < 0 || p >= n_vertices) throw std::invalid_argument("pin out of range");
+  PartitionConfig cfg;
+  cfg.k = k;
+  cfg.cap_comp = cap_comp;
+  cfg.cap_mem = cap_mem;
+  cfg.seed = seed;
+  cfg.n_tries = n_tries;
+  cfg.fixed = fixed;
+  PartitionResult r;
+  {
+    py::gil_scoped_release release;
+    hg.finalize();
+    if (!initial.empty()) {
+      r.part = initial;
+      refine(hg, cfg, r.part);
+      r.km1 = connectivity_minus_one(hg, r.part, k);
+      r.load_comp.assign(k, 0);
+      r.load_mem.assign(k, 0);
+      for (int v = 0; v < n_vertices; ++v) { r.load_comp[r.part[v]] += vw_comp[v]; r.load_mem[r.part[v]] += vw_mem[v]; }
+      r.balanced = true;
+      for (int p = 0; p < k; ++p) r.balanced = r.balanced && r.load_comp[p] <= cap_comp[p] && r.load_mem[p] <= cap_mem[p];
+    } else {
+      r = partition(hg, cfg);
+    }
+  }
+  py::dict out;
+  out["part"] = r.part;
+  out["km1"] = r.km1;
+  out["load_comp"] = r.load_comp;
+  out["load_mem"] = r.load_mem;
+  out["balanced"] = r.balanced;
+  return out;
+}
+
+int64_t py_km1(int n_vertices, const std::vector<int>& net_offsets, const std::vector<int>& net_pins,
+               const std::vector<int64_t>& net_weight, const std::vector<int>& part, int k) {
+  Hypergraph hg;
+  hg.n_vertices = n_vertices;
+  hg.net_offsets = net_offsets;
+  hg.net_pins = net_pins;
+  hg.net_weight = net_weight;
+  return connectivity_minus_one(hg, part, k);
+}
+
+}  // namespace
+
+PYBIND11_MODULE(_planner, m) {
+  m.doc() = "native planner kernels: k-way hypergraph partitioning and per-stage greedy selection";
+  m.def("greedy_selection_per_device", &py_greedy, py::arg("devices"), py::arg("scheduled_workloads"),
+        py::arg("workload_costs"), py::arg("input_sizes"), py::arg("workload_input_map"),
+        py::arg("input_block_type_map"), py::arg("device_workload_map"), py::arg("device_local_inputs_map"),
+        py::arg("target_comm_load_per_node"), py::arg("is_bw"), py::arg("stage_id"), py::arg("py_logger") = py::none(),
+        py::arg("intra_node_budget") = std::map<Device, double>());
+  m.def("partition_hypergraph", &py_partition, py::arg("n_vertices"), py::arg("vw_comp"), py::arg("vw_mem"),
+        py::arg("net_offsets"), py::arg("net_pins"), py::arg("net_weight"), py::arg("k"), py::arg("cap_comp"),
+        py::arg("cap_mem"), py::arg("seed") = 42, py::arg("n_tries") = 4, py::arg("fixed") = std::vector<int>(),
+        py::arg("initial") = std::vector<int>());
+  m.def("connectivity_minus_one", &py_km1);
+}

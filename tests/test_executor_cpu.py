@@ -1,0 +1,82 @@
+"""Planner + executor correctness on CPU against dense masked attention.
+
+* in-process ranks (threads + mailboxes) for several device counts / masks, forward and backward;
+* the two-rank gloo run of the reference configuration: lengths 512/1024/2048/4096, block 256,
+  8 Q heads, 2 KV heads, head_dim 64, fp32, outputs/LSE/dQ/dK/dV within 1e-5;
+* host-side failure detection: a rank that dies or a message that is dropped turns into an
+  exception on the survivors within the timeout instead of a hang.
+"""
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+from dcp_b200.core.common import get_default_execution_context
+from dcp_b200.planner import masks
+from dcp_b200.planner.compiler import CompilerConfig, InstrCompiler
+from dcp_b200.planner.workload import generate_workload, pad_seqlens
+from dcp_b200.runtime.comm import CommTimeout, MailboxHub
+from dcp_b200.runtime.simulate import dense_reference, run_plans_in_process
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _compile(n_dev, n_nodes, raw, bs, H, Hkv, d, hbs, mask_name, n_stages=None):
+    ctx = get_default_execution_context(n_dev, n_nodes)
+    pad = pad_seqlens(raw, bs)
+    m = masks.get_mask_fn(mask_name)(raw, pad, torch.int32)
+    wl = generate_workload((sum(pad), H, d), (sum(pad), 2, Hkv, d), raw, pad, bs, hbs, ctx.comp_cost_model, m,
+                           torch.float32)
+    return ctx, pad, m, InstrCompiler(ctx, CompilerConfig(n_stages=n_stages)).compile(wl)
+
+
+@pytest.mark.parametrize("n_dev,n_nodes,mask,hbs,n_stages", [
+    (2, 1, "causal", 4, None), (4, 1, "lambda", 8, 2), (4, 2, "shared_question", 2, None),
+    (8, 2, "causal_blockwise", 2, 3), (3, 1, "chunked_first_chunk", 4, 1)])
+def test_plans_match_dense_attention(n_dev, n_nodes, mask, hbs, n_stages):
+    torch.manual_seed(0)
+    raw, bs, H, Hkv, d = [150, 500, 333, 64], 64, 8, 2, 16
+    ctx, pad, m, (fw_wl, bw_wl, fw, bw) = _compile(n_dev, n_nodes, raw, bs, H, Hkv, d, hbs, mask, n_stages)
+    T = sum(raw)
+    q, kv, dout = torch.randn(T, H, d), torch.randn(T, 2, Hkv, d), torch.randn(T, H, d)
+    out, lse, dq, dkv = run_plans_in_process(ctx, fw_wl, fw, q, kv, raw, bw_wl, bw, dout, timeout_s=30)
+    ro, rl, rdq, rdkv = dense_reference(q, kv, raw, pad, m, d ** -0.5, dout)
+    fin = torch.isfinite(rl)
+    assert (out - ro).abs().max() < 1e-5
+    assert (lse - rl)[fin].abs().max() < 1e-5
+    assert (dq - rdq).abs().max() < 2e-5 and (dkv - rdkv).abs().max() < 2e-5
+
+
+def test_gloo_world2_reference_config():
+    """Two real processes over gloo: the planner/executor correctness configuration."""
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
+           "127.0.0.1", "--master-port", "29611", os.path.join(ROOT, "tests", "gloo_worker.py")]
+    env = dict(os.environ, PYTHONPATH=ROOT, OMP_NUM_THREADS="2")
+    res = subprocess.run(cmd, env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=600)
+    assert res.returncode == 0, res.stdout[-3000:]
+    assert "GLOO_OK" in res.stdout, res.stdout[-3000:]
+
+
+def test_rank_failure_surfaces_as_exception():
+    torch.manual_seed(0)
+    raw = [256, 256]
+    ctx, pad, m, (fw_wl, bw_wl, fw, bw) = _compile(2, 1, raw, 64, 4, 2, 16, 2, "causal")
+    q, kv = torch.randn(sum(raw), 4, 16), torch.randn(sum(raw), 2, 2, 16)
+    with pytest.raises(RuntimeError, match="injected failure"):
+        run_plans_in_process(ctx, fw_wl, fw, q, kv, raw, timeout_s=1.0, fail_rank=1)
+
+
+def test_dropped_message_times_out():
+    torch.manual_seed(0)
+    raw = [512]
+    ctx, pad, m, (fw_wl, bw_wl, fw, bw) = _compile(2, 1, raw, 64, 4, 2, 16, 2, "causal")
+    q, kv = torch.randn(sum(raw), 4, 16), torch.randn(sum(raw), 2, 2, 16)
+    hub = MailboxHub(2, timeout_s=1.0)
+    from dcp_b200.core.instructions import CommLaunchInstr, CommType
+    key = next(i.key for i in fw[(0, 0)].instructions if isinstance(i, CommLaunchInstr)
+               and any(op.comm_type == CommType.SEND for op in i.comm_ops))
+    hub.dropped.add((0, 1, key))
+    with pytest.raises(CommTimeout):
+        run_plans_in_process(ctx, fw_wl, fw, q, kv, raw, hub=hub)

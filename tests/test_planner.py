@@ -1,0 +1,198 @@
+"""Planner tests: workload generation, masks, placement invariants, stage generation, and the
+symbolic checks of compiled plans (every block assigned once, SEND/RECV pairs agree, slots are
+written before they are read)."""
+import numpy as np
+import pytest
+import torch
+
+from dcp_b200.core.blocks import BlockType, WorkloadSpec, deserialize_list_of_workloads, serialize_list_of_workloads
+from dcp_b200.core.common import ExecutionContext, ModelSpec, get_default_execution_context
+from dcp_b200.core.cost_model import AttnRooflineCostModel, CommunicationCostModel
+from dcp_b200.core.instructions import (AttnBackwardInstr, AttnInstr, AttnReductionInstr, BufferType, CommLaunchInstr,
+                                        CommType, CommWaitInstr, MemcpyInstr, SumInstr)
+from dcp_b200.planner import masks
+from dcp_b200.planner.compiler import CompilerConfig, InstrCompiler
+from dcp_b200.planner.partition import (HGPSolver, PlacementGraph, assign_device_by_heuristic,
+                                        construct_and_partition_graph_multiconstraint, placement_vector)
+from dcp_b200.planner.stages import generate_pipelines_n_stages
+from dcp_b200.planner.validate import validate_plans
+from dcp_b200.planner.workload import block_size_heuristic, generate_workload, pad_seqlens
+
+
+def _workload(raw, bs, H=8, Hkv=2, d=64, hbs=4, mask="causal", ctx=None):
+    ctx = ctx or get_default_execution_context(4, 1)
+    pad = pad_seqlens(raw, bs)
+    m = masks.get_mask_fn(mask)(raw, pad, torch.int32)
+    return generate_workload((sum(pad), H, d), (sum(pad), 2, Hkv, d), raw, pad, bs, hbs, ctx.comp_cost_model, m,
+                             torch.bfloat16), m, pad
+
+
+@pytest.mark.parametrize("mask", ["causal", "lambda", "shared_question", "causal_blockwise", "chunked_first_chunk"])
+def test_workload_covers_mask_exactly(mask):
+    """Union of all work-unit mask slices == the dense mask, nothing twice."""
+    raw, bs = [300, 1000, 513], 128
+    wl, m, pad = _workload(raw, bs, mask=mask, hbs=8)
+    full = masks.to_two_range(m)
+    pcu = np.concatenate([[0], np.cumsum(pad)])
+    metas = wl.block_mapping.input_id_to_meta
+    for s, n in enumerate(raw):
+        dense = masks.dense_from_ranges(full[pcu[s]:pcu[s] + pad[s]], n, n)
+        cover = torch.zeros(n, n, dtype=torch.int32)
+        for w, u in wl.block_mapping.work_id_to_meta.items():
+            if u.seq_id != s or u.head_id != 0:
+                continue
+            qi, kj = metas[u.q_id].block_id, metas[u.kv_id].block_id
+            nq, nk = metas[u.q_id].n_tokens, metas[u.kv_id].n_tokens
+            loc = masks.dense_from_ranges(u.local_attn_mask.permute(2, 0, 1) if u.local_attn_mask.dim() == 3
+                                          else u.local_attn_mask.t(), nq, nk)
+            cover[qi * bs:qi * bs + nq, kj * bs:kj * bs + nk] += loc.int()
+        assert torch.equal(cover, dense.int())
+
+
+def test_mask_functions_match_loop_definitions():
+    raw, pad = [700], [768]
+    lam = masks.lambda_mask_fn(raw, pad, torch.int32, n_starting=4, l_pretrain=16)
+    i = 100
+    assert lam[i].tolist() == [[0, 4], [i - 15, i + 1]]
+    sq = masks.shared_question_mask_fn(raw, pad, torch.int32, question_proportion=0.2, n_answers=4)
+    nq = 140
+    per = (700 - nq) // 4
+    assert sq[50].tolist() == [[0, 51], [51, 51]]
+    assert sq[nq + per + 3].tolist() == [[0, nq], [nq + per, nq + per + 4]]
+    cb = masks.causal_blockwise_mask_fn(raw, pad, torch.int32, block_size=256, k_local=1)
+    assert cb[300].tolist() == [[0, 256], [256, 301]]       # middle chunk: first chunk + window
+    assert cb[600].tolist() == [[0, 256], [256, 601]]       # last chunk sees everything before
+    ch = masks.chunked_first_chunk_mask_fn(raw, pad, torch.int32, chunk_size=256)
+    assert ch[600].tolist() == [[0, 256], [512, 601]]
+    assert lam[700:].abs().sum() == 0                        # padding rows are empty
+    mm = masks.modality_specific_mask_fn([20], [32], torch.int32, [{"image_size": 6, "text_lengths": [5, 9]}])
+    assert mm[4].tolist() == [0, 5] and mm[7].tolist() == [0, 11] and mm[12].tolist() == [0, 13]
+
+
+def test_workload_ids_and_gqa_layout():
+    wl, _, _ = _workload([256, 512], 256, H=8, Hkv=2, hbs=2)
+    im = wl.block_mapping.input_id_to_meta
+    # sequence 0 has 1 token block: 4 q head blocks then 2 kv head blocks
+    assert [im[i].type for i in range(6)] == ["Q"] * 4 + ["KV"] * 2
+    u = wl.block_mapping.work_id_to_meta[3]     # head block 3 -> kv head block (3*2)//4 = 1
+    assert u.head_id == 3 and im[u.kv_id].head_id == 1 and im[u.kv_id].per_token_shape == (2, 1, 64)
+    om = wl.block_mapping.output_id_to_meta
+    assert om[u.out_id].type == BlockType.Out and om[u.lse_id].type == BlockType.LSE and u.lse_id == u.out_id + 1
+    blob = serialize_list_of_workloads([wl])
+    back, rest = deserialize_list_of_workloads(blob)
+    assert rest == b"" and back[0].workloads == wl.workloads and back[0].work_unit_input_map == wl.work_unit_input_map
+    assert back[0].block_mapping.input_id_to_meta == wl.block_mapping.input_id_to_meta
+
+
+@pytest.mark.parametrize("n_dev,n_nodes", [(2, 1), (4, 1), (8, 1), (8, 2)])
+def test_partition_invariants(n_dev, n_nodes):
+    ctx = get_default_execution_context(n_dev, n_nodes)
+    wl, _, _ = _workload([4000, 1500, 900, 700, 260], 256, ctx=ctx)
+    d2w, d2i, d2o = construct_and_partition_graph_multiconstraint(ctx, wl, 0.2, 0.2)
+    assert sorted(w for ws in d2w.values() for w in ws) == list(range(len(wl.workloads)))
+    assert sorted(i for v in d2i.values() for i in v) == sorted(wl.block_mapping.input_id_to_meta)
+    assert sorted(o for v in d2o.values() for o in v) == sorted(wl.block_mapping.output_id_to_meta)
+    for ins, outs in wl.colocation_constraints:            # co-location groups stay together
+        devs = {wl.input_to_device_map[i] for i in ins} | {wl.output_to_device_map[o] for o in outs}
+        assert len(devs) == 1
+    mem = np.array([sum(wl.input_sizes[i] for i in d2i[d]) for d in ctx.devices()], dtype=float)
+    assert mem.max() <= 1.35 * mem.mean() + max(wl.input_sizes) * 6
+    # deterministic
+    wl2, _, _ = _workload([4000, 1500, 900, 700, 260], 256, ctx=ctx)
+    construct_and_partition_graph_multiconstraint(ctx, wl2, 0.2, 0.2)
+    assert wl2.work_to_device_map == wl.work_to_device_map
+
+
+def test_partition_cuts_less_than_zigzag_on_mixed_batch():
+    ctx = get_default_execution_context(8, 1)
+    wl, _, _ = _workload([8192, 2048, 1024, 1024, 512, 512, 300, 200], 256, hbs=4, ctx=ctx)
+    g = PlacementGraph(wl)
+    construct_and_partition_graph_multiconstraint(ctx, wl)
+    ours = g.km1(placement_vector(wl, g, ctx), 8)
+    assign_device_by_heuristic(ctx, wl)
+    zig = g.km1(placement_vector(wl, g, ctx), 8)
+    assert ours <= zig
+
+
+def test_native_partitioner_small_optimum():
+    from dcp_b200 import _planner
+    # two triangles joined by one light net: the optimum cuts only the light net
+    offs, pins, w = [0, 3, 6, 8], [0, 1, 2, 3, 4, 5, 2, 3], [10, 10, 1]
+    r = _planner.partition_hypergraph(6, [1] * 6, [1] * 6, offs, pins, w, 2, [3, 3], [3, 3], 7, 4)
+    assert r["km1"] == 1 and r["balanced"]
+    assert len({r["part"][0], r["part"][1], r["part"][2]}) == 1
+
+
+def test_stage_generation_schedules_everything_once():
+    ctx = get_default_execution_context(4, 1)
+    wl, _, _ = _workload([3000, 1500, 900, 260], 256, ctx=ctx)
+    construct_and_partition_graph_multiconstraint(ctx, wl)
+    work, comm, comm2 = generate_pipelines_n_stages(4, ctx.devices(), wl.workloads, wl.work_unit_input_map,
+                                                    wl.block_mapping.input_id_to_meta, wl.input_sizes,
+                                                    wl.work_to_device_map, wl.input_to_device_map, False)
+    assert len(work) == 5
+    seen = [w for st in work for ws in st.values() for w in ws]
+    assert sorted(seen) == list(range(len(wl.workloads)))
+    have = {d: {i for i, dev in wl.input_to_device_map.items() if dev == d} for d in ctx.devices()}
+    for s in range(5):
+        for d in ctx.devices():
+            for i, src in comm[s][d]:
+                assert i in have[tuple(src)], "a block is only served by a device that already holds it"
+        for d in ctx.devices():
+            have[d] |= {i for i, _ in comm[s][d]}
+            for w in work[s][d]:
+                assert set(wl.work_unit_input_map[w]) <= have[d]
+    assert all(not comm[0][d] for d in ctx.devices())      # stage 0 is purely local
+
+
+def test_native_greedy_respects_budget_and_is_deterministic():
+    from dcp_b200 import _planner
+    devs = {(0, 0), (0, 1)}
+    args = (devs, set(), [1.0, 2.0, 3.0], [10.0, 10.0, 10.0, 10.0], [[0, 2], [1, 3], [0, 3]], ["Q", "Q", "KV", "KV"],
+            {(0, 0): [0, 1, 2], (0, 1): []}, {(0, 0): {0: -1, 1: -1}, (0, 1): {2: -1, 3: -1}}, {d: 0.0 for d in devs},
+            False, 0, None, {d: 10.0 for d in devs})
+    a = _planner.greedy_selection_per_device(*args)
+    b = _planner.greedy_selection_per_device(*args)
+    assert a == b
+    unlocked, comm, local = a
+    # unit 2 (most expensive) fetches block 3 within the 10-byte budget; unit 1 then needs nothing more;
+    # unit 0 would need block 2 as well and stays behind
+    assert unlocked[(0, 0)] == {1, 2}
+    assert comm[(0, 0)] == [(3, (0, 1))] and local[(0, 0)][3] == 0
+
+
+@pytest.mark.parametrize("mask,n_dev,n_nodes,hbs", [("causal", 2, 1, 4), ("lambda", 4, 1, 8), ("shared_question", 8, 2, 2),
+                                                     ("causal_blockwise", 4, 2, 4)])
+def test_compiled_plans_validate(mask, n_dev, n_nodes, hbs):
+    ctx = get_default_execution_context(n_dev, n_nodes)
+    wl, _, _ = _workload([1500, 700, 400, 130], 128, hbs=hbs, mask=mask, ctx=ctx)
+    fw_wl, bw_wl, fw, bw = InstrCompiler(ctx).compile(wl)
+    rep = validate_plans(ctx, fw_wl, fw, True)
+    assert rep["attn_units"] == len(fw_wl.workloads)
+    rep_b = validate_plans(ctx, bw_wl, bw, False)
+    assert rep_b["attn_units"] == len(bw_wl.workloads)
+    for d in ctx.devices():
+        assert fw[d].local_cu_seqlens[-1] == sum(m.n_tokens for i, m in fw_wl.block_mapping.input_id_to_meta.items()
+                                                 if m.type == "Q" and fw_wl.input_to_device_map[i] == d)
+
+
+def test_block_size_heuristic_and_cost_models():
+    assert block_size_heuristic([100000, 300, 200], 8, 0.2) < block_size_heuristic([8000] * 8, 8, 0.2)
+    assert block_size_heuristic([8192] * 8, 8) == 8192
+    comm = CommunicationCostModel()
+    assert comm.get_cost((0, 0), (0, 0), 1 << 20) == 0
+    assert comm.get_cost((0, 0), (1, 0), 1 << 20) > comm.get_cost((0, 0), (0, 1), 1 << 20) > 0
+    c2, rest = CommunicationCostModel.deserialize(comm.serialize())
+    assert c2 == comm and rest == b""
+    comp = AttnRooflineCostModel()
+    m1 = torch.tensor([[0] * 128, list(range(1, 129))], dtype=torch.int32)
+    f, mem = comp.get_cost([128], [128], m1, 8, 2, 128)
+    f_b, _ = comp.get_cost([128], [128], m1, 8, 2, 128, is_forward=False)
+    assert f > 0 and mem > 0 and abs(f_b / f - 2.5) < 1e-9
+    two = torch.stack([m1, m1])                    # identical ranges overlap fully: counted once
+    assert comp.get_cost([128], [128], two, 8, 2, 128)[0] == pytest.approx(f)
+    ctx = get_default_execution_context(8, 2)
+    c, rest = ExecutionContext.deserialize(ctx.serialize())
+    assert (c.n_nodes, c.n_devices_per_node) == (2, 4) and rest == b""
+    ms, _ = ModelSpec.deserialize(ModelSpec(128, 32, 8).serialize())
+    assert ms == ModelSpec(128, 32, 8)
