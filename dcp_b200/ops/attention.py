@@ -52,6 +52,14 @@ class FwdTables:
     block_size: int
     flops: float = 0.0
 
+    def to(self, device, non_blocking: bool = True) -> "FwdTables":
+        mv = lambda t: t.to(device, non_blocking=non_blocking)
+        return FwdTables(mv(self.tiles), mv(self.kv_entries), mv(self.masks), self.n_tiles, self.block_size, self.flops)
+
+    def pin(self) -> "FwdTables":
+        return FwdTables(self.tiles.pin_memory(), self.kv_entries.pin_memory(), self.masks.pin_memory(), self.n_tiles,
+                         self.block_size, self.flops)
+
 
 def _pair_count(ranges: np.ndarray) -> float:
     """Number of (query, key) pairs allowed by a [n,4] range table (ranges assumed disjoint)."""
@@ -94,7 +102,7 @@ def _ptr_array(tensors) -> ctypes.Array:
 
 
 def attn_fwd(q_arena: torch.Tensor, kv_arena: torch.Tensor, tables: FwdTables, out_dsts, lse_dsts,
-             scale: float, status: torch.Tensor, variant: int = 0):
+             scale: float, status: torch.Tensor, variant: int = 0, lse_stride: Optional[int] = None):
     """Run the forward kernel.
 
     q_arena: bf16 [rows, hq, 128]; kv_arena: bf16 [rows, 2, hkv, 128]; out_dsts / lse_dsts: lists of
@@ -106,8 +114,8 @@ def attn_fwd(q_arena: torch.Tensor, kv_arena: torch.Tensor, tables: FwdTables, o
     assert q_arena.is_contiguous() and kv_arena.is_contiguous()
     assert q_arena.shape[-1] == HEAD_DIM and kv_arena.shape[-1] == HEAD_DIM
     hq, hkv = q_arena.shape[1], kv_arena.shape[2]
-    lse0 = lse_dsts[0]
-    lse_stride = lse0.shape[1] if not isinstance(lse0, int) else int(out_dsts[0].shape[0])
+    if lse_stride is None:
+        lse_stride = lse_dsts[0].shape[1]
     rc = lib.dcpk_attn_fwd(
         _lib.ptr(q_arena), ctypes.c_long(q_arena.shape[0]), _lib.ptr(kv_arena), ctypes.c_long(kv_arena.shape[0]),
         ctypes.c_int(hq), ctypes.c_int(hkv), _lib.ptr(tables.tiles), ctypes.c_int(tables.n_tiles),
@@ -156,6 +164,14 @@ class BwdTables:
     n_ctas: int
     n_items: int
     flops: float = 0.0
+
+    def to(self, device, non_blocking: bool = True) -> "BwdTables":
+        mv = lambda t: t.to(device, non_blocking=non_blocking)
+        return BwdTables(mv(self.ctas), mv(self.items), mv(self.masks), self.n_ctas, self.n_items, self.flops)
+
+    def pin(self) -> "BwdTables":
+        return BwdTables(self.ctas.pin_memory(), self.items.pin_memory(), self.masks.pin_memory(), self.n_ctas,
+                         self.n_items, self.flops)
 
 
 def _tile_bounds(rng: np.ndarray, tile: int):

@@ -1,0 +1,187 @@
+"""Fused sm_100a executor: runs a ``FusedProgram`` with communication folded into kernels.
+
+Per attention call (all layers of an iteration share one executor and one program):
+
+forward   barrier -> [side stream] pull stage s+1 operands from peers' arenas
+                  -> [main stream] tcgen05 attention of stage s; every tile stores its partial
+                     (out, lse) into the owner's partial arena / final buffer over NVLink
+          barrier -> merge kernel on the owner
+backward  delta = rowsum(dO * O); barrier -> pulls (Q, dO, lse, delta, KV) overlapped with the
+          backward kernel per stage, dQ/dK/dV accumulated with fp32 red into arena mirrors
+          -> push-add of staged gradients into the owners' accumulators -> barrier
+
+No NCCL call is made on these paths.  Takes the role of AttentionExecutor
+(dcp/runtime/flash_attention/executor.py:340-2133) for single-node NVSwitch machines.
+"""
+from __future__ import annotations
+
+from typing import List, Optional
+
+import numpy as np
+import torch
+
+from ..ops import attention as attn_ops
+from ..ops import block_ops
+from ..planner.lowering import FusedProgram
+from .symm import SymmetricArena
+
+HEAD_DIM = 128
+
+
+class FusedAttentionExecutor:
+    def __init__(self, heads_q: int, heads_kv: int, max_q_rows: int, max_kv_rows: int, max_part_rows: int,
+                 device: torch.device, group=None, softmax_scale: Optional[float] = None, timeout_s: float = 10.0,
+                 variant: int = 0):
+        self.hq, self.hkv = heads_q, heads_kv
+        self.device = device
+        self.scale = softmax_scale if softmax_scale is not None else HEAD_DIM ** -0.5
+        self.variant = variant
+        rq, rkv, rp = (-(-int(x) // 128) * 128 + 128 for x in (max_q_rows, max_kv_rows, max_part_rows))
+        rq = rp = max(rq, rp)  # partial and final LSE buffers share one row stride in the kernel
+        self.cap = (rq, rkv, rp)
+        bf, f32 = torch.bfloat16, torch.float32
+        regions = {
+            "q": ((rq, heads_q, HEAD_DIM), bf), "kv": ((rkv, 2, heads_kv, HEAD_DIM), bf),
+            "dout": ((rq, heads_q, HEAD_DIM), bf), "out": ((rq, heads_q, HEAD_DIM), bf),
+            "lse": ((heads_q, rq), f32), "delta": ((heads_q, rq), f32),
+            "part_out": ((rp, heads_q, HEAD_DIM), bf), "part_lse": ((heads_q, rp), f32),
+            "dq": ((rq, heads_q, HEAD_DIM), f32), "dkv": ((rkv, 2, heads_kv, HEAD_DIM), f32),
+        }
+        self.arena = SymmetricArena(regions, device, group, timeout_s)
+        self.world, self.rank = self.arena.world, self.arena.rank
+        for name in regions:
+            setattr(self, name, self.arena.view(name))
+        self.side = torch.cuda.Stream(device=device)
+        self.program: Optional[FusedProgram] = None
+        self.arena_epoch = 0          # bumped whenever q/kv local regions are rewritten
+        self._staging_valid = False   # remote Q/KV rows in staging match the current local data on peers
+        self.kernel_launches = 0
+
+    # ---- program upload
+    def prepare(self, program: FusedProgram) -> None:
+        assert program.heads_q == self.hq and program.heads_kv == self.hkv
+        need = program.max_rows()
+        if any(n > c for n, c in zip(need, self.cap)):
+            raise RuntimeError(f"program needs rows {need} but the arenas hold {self.cap}")
+        dev = self.device
+        up = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(dev, non_blocking=True)
+        self.program = program
+        self.q_pulls = [up(x) for x in program.q_pulls]
+        self.kv_pulls = [up(x) for x in program.kv_pulls]
+        self.fwd_tabs = [t.to(dev) if t is not None else None for t in program.fwd]
+        self.bwd_tabs = [t.to(dev) if t is not None else None for t in program.bwd]
+        self.merge_ops, self.merge_src = up(program.merge_ops), up(program.merge_src)
+        self.dq_push, self.dkv_push = up(program.dq_push), up(program.dkv_push)
+        self._staging_valid = False
+
+    # ---- views the model writes into / reads from
+    def q_local(self) -> torch.Tensor:
+        return self.q[:self.program.q_local_rows]
+
+    def kv_local(self) -> torch.Tensor:
+        return self.kv[:self.program.kv_local_rows]
+
+    def out_local(self) -> torch.Tensor:
+        return self.out[:self.program.q_local_rows]
+
+    def lse_local(self) -> torch.Tensor:
+        return self.lse[:, :self.program.q_local_rows]
+
+    def inputs_written(self) -> None:
+        self.arena_epoch += 1
+        self._staging_valid = False
+
+    def _pull_inputs(self, s: int, with_grads: bool, skip_qkv: bool = False) -> None:
+        a = self.arena
+        if not skip_qkv:
+            block_ops.gather_rows(self.q_pulls[s], a.peer_ptrs("q"), self.q, self.hq * HEAD_DIM * 2)
+            block_ops.gather_rows(self.kv_pulls[s], a.peer_ptrs("kv"), self.kv, 2 * self.hkv * HEAD_DIM * 2)
+            self.kernel_launches += 2 * (self.q_pulls[s].shape[0] > 0)
+        if with_grads:
+            block_ops.gather_rows(self.q_pulls[s], a.peer_ptrs("dout"), self.dout, self.hq * HEAD_DIM * 2)
+            block_ops.gather_stats(self.q_pulls[s], a.peer_ptrs("lse"), self.lse, self.hq, self.cap[0])
+            block_ops.gather_stats(self.q_pulls[s], a.peer_ptrs("delta"), self.delta, self.hq, self.cap[0])
+            self.kernel_launches += 3 * (self.q_pulls[s].shape[0] > 0)
+
+    # ---- forward
+    def forward(self):
+        """Attention over the Q/KV already present in ``q_local()`` / ``kv_local()``.
+        Returns views (out [rows, hq, d] bf16, lse [hq, rows] fp32) of this rank's own tokens."""
+        p, a = self.program, self.arena
+        main = torch.cuda.current_stream(self.device)
+        a.barrier()                                   # every rank's inputs are in place
+        ready = []
+        if self.world > 1:
+            self.side.wait_stream(main)
+            with torch.cuda.stream(self.side):
+                for s in range(p.n_stages):
+                    self._pull_inputs(s, with_grads=False)
+                    ev = torch.cuda.Event()
+                    ev.record(self.side)
+                    ready.append(ev)
+        out_dsts = a.peer_ptrs("part_out") + a.peer_ptrs("out")
+        lse_dsts = a.peer_ptrs("part_lse") + a.peer_ptrs("lse")
+        for s in range(p.n_stages):
+            if ready:
+                main.wait_event(ready[s])
+            t = self.fwd_tabs[s]
+            if t is None:
+                continue
+            self._launch_fwd(t, out_dsts, lse_dsts)
+        if self.world > 1:
+            a.barrier()                               # all partials have landed at their owners
+        if self.merge_ops.shape[0]:
+            block_ops.merge_out_lse(self.merge_ops, self.merge_src, self.part_out, self.part_lse, self.out, self.lse)
+            self.kernel_launches += 1
+        self._staging_valid = True
+        return self.out_local(), self.lse_local()
+
+    def _launch_fwd(self, t, out_dsts, lse_dsts) -> None:
+        attn_ops.attn_fwd(self.q, self.kv, t, out_dsts, lse_dsts, self.scale, a_status(self), self.variant,
+                          lse_stride=self.cap[0])
+        self.kernel_launches += 1
+
+    # ---- backward
+    def backward(self, dout_local: torch.Tensor):
+        """dout_local [rows, hq, d] bf16 for this rank's tokens; returns fp32 accumulator views
+        (dq [rows, hq, d], dkv [rows, 2, hkv, d]) valid until the next backward call."""
+        p, a = self.program, self.arena
+        main = torch.cuda.current_stream(self.device)
+        n = p.q_local_rows
+        self.dout[:n].copy_(dout_local.reshape(n, self.hq, HEAD_DIM))
+        attn_ops.attn_delta(self.out, self.dout, self.delta, 0, n)
+        self.dq[:p.q_rows].zero_()
+        self.dkv[:p.kv_rows].zero_()
+        self.kernel_launches += 1
+        a.barrier()
+        ready = []
+        if self.world > 1:
+            self.side.wait_stream(main)
+            with torch.cuda.stream(self.side):
+                for s in range(p.n_stages):
+                    self._pull_inputs(s, with_grads=True, skip_qkv=self._staging_valid)
+                    ev = torch.cuda.Event()
+                    ev.record(self.side)
+                    ready.append(ev)
+        for s in range(p.n_stages):
+            if ready:
+                main.wait_event(ready[s])
+            t = self.bwd_tabs[s]
+            if t is None:
+                continue
+            attn_ops.attn_bwd(self.q, self.dout, self.kv, self.lse, self.delta, t, [self.dq], [self.dkv], self.scale,
+                              a_status(self))
+            self.kernel_launches += 1
+        if self.world > 1:
+            block_ops.push_add_rows(self.dq_push, self.dq, a.peer_ptrs("dq"), self.hq * HEAD_DIM)
+            block_ops.push_add_rows(self.dkv_push, self.dkv, a.peer_ptrs("dkv"), 2 * self.hkv * HEAD_DIM)
+            self.kernel_launches += 2
+            a.barrier()
+        return self.dq[:n], self.dkv[:p.kv_local_rows]
+
+    def check_status(self) -> None:
+        self.arena.check_status()
+
+
+def a_status(ex: FusedAttentionExecutor) -> torch.Tensor:
+    return ex.arena.status

@@ -1,0 +1,94 @@
+"""Symmetric (peer-mapped) device memory for the fused executor.
+
+One byte arena per rank is allocated through ``torch.distributed._symmetric_memory`` and
+rendezvoused once, which gives every rank the device address of every peer's arena over
+NVLink.  Named regions are carved at identical offsets on all ranks, so "region X of rank r" is
+``ptrs[r] + offset(X)`` everywhere.  With a single rank the arena is ordinary device memory.
+
+Cross-GPU synchronisation uses a flag row per rank inside the arena and the bounded
+``signal_barrier`` kernel: a peer that never arrives turns into a status code, not a hang.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional, Tuple
+
+import torch
+
+from ..ops import block_ops
+
+_ALIGN = 1024
+
+
+class SymmetricArena:
+    def __init__(self, regions: Dict[str, Tuple[Tuple[int, ...], torch.dtype]], device: torch.device, group=None,
+                 timeout_s: float = 10.0):
+        """regions: name -> (shape, dtype).  ``group`` None or of size 1 -> local memory only."""
+        self.device = device
+        self.group = group
+        self.timeout_s = timeout_s
+        self.world = 1
+        self.rank = 0
+        if group is not None:
+            import torch.distributed as dist
+            self.world = dist.get_world_size(group)
+            self.rank = dist.get_rank(group)
+        self.offsets: Dict[str, int] = {}
+        self.specs = dict(regions)
+        off = 0
+        for name, (shape, dtype) in regions.items():
+            self.offsets[name] = off
+            n = 1
+            for s in shape:
+                n *= int(s)
+            off += -(-(n * torch.empty((), dtype=dtype).element_size()) // _ALIGN) * _ALIGN
+        self.offsets["__flags__"] = off
+        off += _ALIGN
+        self.nbytes = off
+        if self.world > 1:
+            import torch.distributed._symmetric_memory as symm_mem
+            self.buf = symm_mem.empty(self.nbytes, dtype=torch.uint8, device=device)
+            self.buf.zero_()
+            torch.cuda.synchronize(device)
+            self.handle = symm_mem.rendezvous(self.buf, group.group_name)
+            self.ptrs: List[int] = [int(p) for p in self.handle.buffer_ptrs]
+        else:
+            self.buf = torch.zeros(self.nbytes, dtype=torch.uint8, device=device)
+            self.handle = None
+            self.ptrs = [self.buf.data_ptr()]
+        self.status = torch.zeros(1, dtype=torch.int32, device=device)
+        self.epoch = 0
+        self._views: Dict[str, torch.Tensor] = {}
+
+    def view(self, name: str) -> torch.Tensor:
+        if name not in self._views:
+            shape, dtype = self.specs[name]
+            n = 1
+            for s in shape:
+                n *= int(s)
+            nbytes = n * torch.empty((), dtype=dtype).element_size()
+            off = self.offsets[name]
+            self._views[name] = self.buf[off:off + nbytes].view(dtype).view(*shape)
+        return self._views[name]
+
+    def peer_ptrs(self, name: str) -> List[int]:
+        """Device address of region ``name`` on every rank (index = rank)."""
+        off = self.offsets[name]
+        return [p + off for p in self.ptrs]
+
+    def barrier(self) -> None:
+        """All ranks' prior work on the current stream is complete and visible when this returns
+        on the stream (device-side; the host does not block)."""
+        if self.world <= 1:
+            return
+        self.epoch += 1
+        block_ops.signal_barrier(self.peer_ptrs("__flags__"), self.rank, self.world, self.epoch, self.status,
+                                 self.timeout_s)
+
+    def check_status(self) -> None:
+        """Host-side check of the device status word (synchronises the stream)."""
+        code = int(self.status.item())
+        if code != 0:
+            names = {1: "an mbarrier wait inside a compute kernel ran out",
+                     2: "a peer never reached a cross-GPU barrier within the deadline", 3: "bad kernel arguments"}
+            self.status.zero_()
+            raise RuntimeError(f"device-side failure detected (code {code}): {names.get(code, 'unknown')}")
