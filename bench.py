@@ -1,0 +1,211 @@
+"""Headline benchmark: Llama-3-8B-architecture DCP training throughput (tokens/s) on N B200s.
+
+    python bench.py --gpus N --steps K --warmup W            (N > 1: launched by torch.distributed.run)
+
+Default configuration = the scaling configuration: bf16, random-initialised Llama-3-8B
+architecture, 32768 tokens per GPU per step (weak scaling), heavy-tailed synthetic lengths (70 %
+U[1024, 8192] + 30 % lognormal median 65536 sigma 0.5 clipped to 131072), causal mask, DCP block
+size 2048, context-parallel group = all N GPUs, AdamW with sharded fp32 state, full activation
+recompute.  ``--config causal131k`` / ``masks`` select the fixed 131072-token configurations.
+
+Two timed regions of K steps each, every step a complete forward + backward + optimizer step:
+  * device-timed: inputs already staged on the device, CUDA events on the launching stream
+    around the K steps, barrier + synchronize on both sides, max over ranks  -> "value";
+  * end to end through ``TrainEngine.train_step``: per step the pinned-host -> device copy of
+    token ids / labels / positions / kernel tables and the device -> host read of the loss
+    -> "e2e".
+Inputs differ every step and a step streams the 16 GB of bf16 weights twice, far beyond the
+126 MB L2, so no explicit L2 flush is needed between timed iterations.
+
+``--impl reference`` would run the unmodified reference from baseline/_ref; it cannot run on
+this image (see the message it prints).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import time
+
+os.environ.setdefault("PYTORCH_CUDA_ALLOC_CONF", "expandable_segments:True")
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+# Published DCP number the ratio is quoted against: GPT-8B, LongAlign, 131072 max length, causal,
+# 64 x A100 (TP4 x DCP16): 46.3k tokens/s for the whole job.
+BASELINE_TOKENS_PER_S = 46300.0
+QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+
+def reference_arm() -> None:
+    reason = ("reference needs dcp_flash_attn (CUDA fork of flash-attention 2.6.3), kahypar, redis-server, "
+              "Megatron-LM and TransformerEngine, none of which are on this offline image; "
+              "`pip install --no-deps` of /root/reference succeeds but `import dcp.graph_partition.graph` and "
+              "`dcp.runtime.flash_attention.executor` fail with ModuleNotFoundError")
+    print(json.dumps({"impl": "reference", "unavailable": reason}))
+
+
+class ClockSampler:
+    def __init__(self, path: str):
+        self.path, self.proc = path, None
+
+    def start(self):
+        try:
+            self.f = open(self.path, "w")
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={QUERY}", "--format=csv,noheader,nounits", "-lms", "200"],
+                                         stdout=self.f, stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        self.f.close()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in open(self.path):
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1])); mx.append(float(parts[2]))
+            except ValueError:
+                continue
+            for n, v in zip(names, parts[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        sm.sort()
+        busy = [x for x in sm if x > 0]
+        return {"sm_mhz": busy[len(busy) // 2] if busy else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=4)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--config", default="scaling", choices=["scaling", "causal131k", "masks"])
+    ap.add_argument("--model", default="llama3-8b", choices=["llama3-8b", "tiny"])
+    ap.add_argument("--dcp-size", type=int, default=0, help="ranks per context-parallel group (0 = all)")
+    ap.add_argument("--tokens-per-gpu", type=int, default=32768)
+    ap.add_argument("--block-size", type=int, default=2048)
+    ap.add_argument("--stages", type=int, default=None)
+    args = ap.parse_args()
+    if args.impl == "reference":
+        reference_arm()
+        return
+
+    import torch
+    from dcp_b200.data import synth
+    from dcp_b200.models.llama import LLAMA3_8B, tiny_config
+    from dcp_b200.ops import _lib
+    from dcp_b200.train import EngineConfig, TrainEngine, init_distributed
+
+    rank, world, local, group = init_distributed()
+    assert world == args.gpus or world == 1 and args.gpus == 1, f"launched with {world} ranks for --gpus {args.gpus}"
+    dev = torch.device("cuda", local)
+    model = LLAMA3_8B if args.model == "llama3-8b" else tiny_config()
+    if args.config == "scaling":
+        tokens, dist_, mask, scaling = args.tokens_per_gpu * world, synth.MIXTURE, "causal", "weak"
+    elif args.config == "causal131k":
+        tokens, dist_, mask, scaling = 131072, synth.LOGNORMAL_8K, "causal", "strong"
+    else:
+        tokens, dist_, mask, scaling = 131072, synth.LOGNORMAL_16K, "mixed", "strong"
+    cfg = EngineConfig(model, tokens, args.dcp_size, args.block_size, mask, dist_, n_stages=args.stages,
+                       planner_workers=2, lookahead=args.steps + 1)
+    eng = TrainEngine(cfg, dev, group)
+    W, K = args.warmup, args.steps
+
+    def barrier():
+        if world > 1:
+            import torch.distributed as dist
+            dist.barrier(group=group)
+        torch.cuda.synchronize(dev)
+
+    it = 0
+    for _ in range(W):
+        eng.train_step(eng.plans.get(it)); it += 1
+
+    # ---- region A: device-timed, inputs staged beforehand (tables are per step, so each step's
+    # program is uploaded before its own timing window opens and the windows are summed)
+    sampler = ClockSampler(os.path.join(ROOT, "gpurun_out", f"clocks_rank{rank}.csv") if os.path.isdir(
+        os.path.join(ROOT, "gpurun_out")) else f"/tmp/clocks_rank{rank}.csv")
+    if rank == 0:
+        sampler.start()
+    dev_ms, launches0 = 0.0, _lib.LAUNCHES
+    tokens_timed = 0
+    timed_plans = []
+    for _ in range(K):
+        plan = eng.plans.get(it); it += 1
+        timed_plans.append(plan)      # region B runs the same K batches, so the two numbers compare
+        toks, labels, pos = eng.stage_inputs(plan)
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        loss = eng.run_step(toks, labels, pos, plan.n_global_tokens)
+        e1.record()
+        barrier()
+        dev_ms += e0.elapsed_time(e1)
+        tokens_timed += plan.n_global_tokens
+    launches = _lib.LAUNCHES - launches0
+    clocks = sampler.stop() if rank == 0 else {}
+    eng.executor.check_status()
+
+    # ---- region B: end to end through the public API (H2D of inputs + D2H of the loss per step)
+    barrier()
+    t0 = time.perf_counter()
+    e2e_tokens, h2d, d2h, last_loss = 0, 0, 0, None
+    for plan in timed_plans:
+        last_loss = eng.train_step(plan)
+        e2e_tokens += plan.n_global_tokens
+        h2d, d2h = eng.h2d_bytes, eng.d2h_bytes
+    barrier()
+    e2e_s = time.perf_counter() - t0
+
+    t = torch.tensor([dev_ms, e2e_s], dtype=torch.float64, device=dev)
+    if world > 1:
+        import torch.distributed as dist
+        dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group)
+    dev_ms, e2e_s = float(t[0]), float(t[1])
+    eng.close()
+    if rank == 0:
+        value = tokens_timed / (dev_ms / 1e3)
+        dcp = cfg.dcp_size or world
+        par = f"cp{dcp}" if dcp == world else f"cp{dcp}xdp{world // dcp}"
+        out = {
+            "metric": "training tokens/s (device-timed, max over ranks)", "value": round(value, 1), "unit": "tokens/s",
+            "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": round(dev_ms / K, 2), "higher_is_better": True,
+            "scaling": scaling, "vs_baseline": round(value / BASELINE_TOKENS_PER_S, 4), "dtype": "bf16",
+            "data": "synthetic (seeded length distribution, uniform token ids, random-init weights)",
+            "config": {"model": "llama-3-8b-architecture" if args.model == "llama3-8b" else "tiny-llama (debug)",
+                       "global_batch": tokens, "seq_len": "variable, <= 131072", "parallelism": par,
+                       "tokens_per_gpu": tokens // world, "mask": mask, "length_dist": dist_.kind,
+                       "dcp_block_size": args.block_size, "optimizer": "AdamW (sharded fp32 state), grad clip 1.0",
+                       "recompute": "full per layer",
+                       "l2": "inputs change every step and exceed L2 (16 GB of weights streamed per pass)",
+                       "baseline_number": "46.3k tokens/s: DCP on 64 x A100, GPT-8B, LongAlign 131072 causal"},
+            "clocks": clocks,
+            "e2e": {"value": round(e2e_tokens / e2e_s, 1), "unit": "tokens/s", "h2d_bytes_per_step": int(h2d),
+                    "d2h_bytes_per_step": int(d2h), "planner_wait_s": round(eng.plans.wait_seconds, 3)},
+            "gpu_launches": int(launches), "final_loss": last_loss,
+        }
+        print(json.dumps(out))
+    if world > 1:
+        import torch.distributed as dist
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

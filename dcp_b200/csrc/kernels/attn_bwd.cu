@@ -34,25 +34,38 @@ static constexpr int kQTile = 64;
 static constexpr int kKvHalf = 128 * 64 * 2;  // [128 x 64] bf16 half tile, 16 KB
 static constexpr int kQHalf = 64 * 64 * 2;    // [64 x 64] bf16 half tile, 8 KB
 
-struct BwdItem {
+// One item = one 64-query tile that attends to the CTA's key tile; the CTA visits it once per
+// query head of its KV head's group, so the table does not grow with the head count.
+struct BwdItemDesc {
   int q_row;     // arena row of the 64-query tile (same row addresses Q, dO, lse, delta)
   int n_rows;    // valid queries
-  int head;      // query head
   int kv_pos0;   // position of this CTA's first key inside the item's concatenated KV
   int mask_row;  // row in the range table
   int dq_dev;    // destination index of the dQ accumulator
   int dq_row;    // arena row in that accumulator
   int full;      // 1: every (query, key) pair of the tile is allowed
+  int pad;
+};
+
+struct BwdItem {  // descriptor + the query head of the current visit
+  int q_row, n_rows, head, kv_pos0, mask_row, dq_dev, dq_row, full;
 };
 
 struct BwdCta {
   int kv_row;    // arena row of the 128-key tile
   int n_valid;   // valid keys
-  int kv_head;
   int item_off, n_items;
   int dkv_dev, dkv_row;
-  int pad;
+  int pad0, pad1;
 };
+
+__device__ __forceinline__ BwdItem load_item(const BwdItemDesc* descs, int visit, int group, int kv_head) {
+  const BwdItemDesc d = descs[visit / group];
+  BwdItem it;
+  it.q_row = d.q_row; it.n_rows = d.n_rows; it.head = kv_head * group + visit % group; it.kv_pos0 = d.kv_pos0;
+  it.mask_row = d.mask_row; it.dq_dev = d.dq_dev; it.dq_row = d.dq_row; it.full = d.full;
+  return it;
+}
 
 struct BwdPtrs {
   float* dq[kMaxPeers];   // fp32 [rows, hq, d]
@@ -65,6 +78,10 @@ struct __align__(1024) BwdSmem {
   uint8_t q[2][2 * kQHalf];
   uint8_t dout[2][2 * kQHalf];
   uint8_t ds[kKvHalf];     // dS^T: [128 keys x 64 queries]
+  // dQ staging, one private [64 queries x 32 channels] fp32 tile per gradient warp; drained to the
+  // fp32 accumulator with bulk reduce-add copies (L2 handles those a line at a time, scalar
+  // red.add is limited to one element per L2 slice per clock)
+  float dq_stage[4][kQTile * 32];
   // per-warp private copies: the four gradient warps never synchronise with each other
   float lse2[4][kQTile];
   float delta[4][kQTile];
@@ -85,15 +102,18 @@ __device__ __forceinline__ void red_add_v4(float* p, float a, float b, float c, 
 __global__ void __launch_bounds__(kBwdThreads, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
                 const __grid_constant__ CUtensorMap tm_kv, const BwdCta* __restrict__ ctas,
-                const BwdItem* __restrict__ items, const int4* __restrict__ masks,
+                const BwdItemDesc* __restrict__ items, const int4* __restrict__ masks,
                 const float* __restrict__ lse, const float* __restrict__ delta, BwdPtrs ptrs, int hq, int hkv,
                 int stat_stride, float scale, int* __restrict__ status) {
   extern __shared__ uint8_t smem_raw[];
   BwdSmem& sm = *reinterpret_cast<BwdSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const BwdCta cta = ctas[blockIdx.x];
-  const BwdItem* my_items = items + cta.item_off;
-  const int n_items = cta.n_items;
+  // grid = (kv heads, key tiles): neighbouring CTAs share the item list and the mask rows
+  const BwdCta cta = ctas[blockIdx.y];
+  const int kv_head = blockIdx.x;
+  const int group = hq / hkv;
+  const BwdItemDesc* my_items = items + cta.item_off;
+  const int n_items = cta.n_items * group;  // visits
 
   if (threadIdx.x == 128) {
     tma_prefetch_desc(&tm_q);
@@ -123,15 +143,15 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
       mbar_expect_tx(&sm.kv_full, 4 * kKvHalf);
-      tma_load_3d(sm.k, &tm_kv, &sm.kv_full, 0, cta.kv_head, cta.kv_row);
-      tma_load_3d(sm.k + kKvHalf, &tm_kv, &sm.kv_full, 64, cta.kv_head, cta.kv_row);
-      tma_load_3d(sm.v, &tm_kv, &sm.kv_full, 0, hkv + cta.kv_head, cta.kv_row);
-      tma_load_3d(sm.v + kKvHalf, &tm_kv, &sm.kv_full, 64, hkv + cta.kv_head, cta.kv_row);
+      tma_load_3d(sm.k, &tm_kv, &sm.kv_full, 0, kv_head, cta.kv_row);
+      tma_load_3d(sm.k + kKvHalf, &tm_kv, &sm.kv_full, 64, kv_head, cta.kv_row);
+      tma_load_3d(sm.v, &tm_kv, &sm.kv_full, 0, hkv + kv_head, cta.kv_row);
+      tma_load_3d(sm.v + kKvHalf, &tm_kv, &sm.kv_full, 64, hkv + kv_head, cta.kv_row);
       bool ok = true;
       int pending[2] = {-1, -1};
       for (int i = 0; i < n_items && ok; ++i) {
         const int st = i & 1, u = i >> 1;
-        const BwdItem itx = my_items[i];
+        const BwdItem itx = load_item(my_items, i, group, kv_head);
         ok = mbar_wait(&sm.qdo_empty[st], (u & 1) ^ 1, abort_word);
         if (!ok) break;
         mbar_expect_tx(&sm.qdo_full[st], 4 * kQHalf);
@@ -217,39 +237,73 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     const bool key_valid = r < cta.n_valid;
     bool ok = true;
     BwdItem prev{};
-    // adds dQ^T of the previous item (lane = d, column = query) into its fp32 accumulator
+    // adds dQ^T of the previous item (lane = d, column = query) into its fp32 accumulator:
+    // transpose through this warp's staging tile, then one 128-byte bulk reduce per query row
     auto flush_dq = [&](const BwdItem& itx) {
-      float* dq = ptrs.dq[itx.dq_dev] + (size_t(itx.dq_row) * hq + itx.head) * kHeadDim + r;
-      const size_t row_stride = size_t(hq) * kHeadDim;
+      if (itx.dq_dev < 0) return;  // dQ not wanted (used to measure the cost of the drain)
+      float* stage = sm.dq_stage[warp];
+      asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");  // earlier drains have left smem
+      __syncwarp();
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
         uint32_t reg[32];
         tmem_ld32(tmem + lane_base + cdQ + c * 32, reg);
         tmem_wait_ld();
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const int qi = c * 32 + i;
-          if (qi < itx.n_rows) red_add_f32(dq + qi * row_stride, __uint_as_float(reg[i]));
+        for (int i = 0; i < 32; ++i) stage[(c * 32 + i) * 32 + lane] = __uint_as_float(reg[i]);
+      }
+      fence_proxy_async_smem();
+      __syncwarp();
+      float* dq = ptrs.dq[itx.dq_dev] + (size_t(itx.dq_row) * hq + itx.head) * kHeadDim + warp * 32;
+      const size_t row_stride = size_t(hq) * kHeadDim;
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int qi = lane + 32 * h;
+        if (qi < itx.n_rows) {
+          asm volatile("cp.reduce.async.bulk.global.shared::cta.bulk_group.add.f32 [%0], [%1], %2;"
+                       ::"l"(dq + qi * row_stride), "r"(smem_u32(stage + qi * 32)), "r"(128)
+                       : "memory");
         }
       }
+      asm volatile("cp.async.bulk.commit_group;" ::: "memory");
     };
+    // the descriptor and per-query statistics of item t+1 are fetched while item t is processed, so
+    // their global-memory latency never sits on the critical path
+    struct Stats { float l[2], d[2]; int4 m[2]; };
+    auto fetch_stats = [&](const BwdItem& it, Stats& st) {
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int qi = lane + 32 * h;
+        const bool qv = qi < it.n_rows;
+        st.l[h] = qv ? lse[size_t(it.head) * stat_stride + it.q_row + qi] : INFINITY;
+        st.d[h] = qv ? delta[size_t(it.head) * stat_stride + it.q_row + qi] : 0.f;
+        st.m[h] = make_int4(0, 0, 0, 0);
+        if (qv && !it.full) st.m[h] = masks[it.mask_row + qi];
+      }
+    };
+    BwdItem nxt{};
+    Stats nst{};
+    if (n_items > 0) {
+      nxt = load_item(my_items, 0, group, kv_head);
+      fetch_stats(nxt, nst);
+    }
     for (int t = 0; t < n_items && ok; ++t) {
-      const BwdItem itx = my_items[t];
-      // per-query statistics and ranges of this item -> this warp's smem copy
+      const BwdItem itx = nxt;
       __syncwarp();
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
         const int qi = lane + 32 * h;
-        const bool qv = qi < itx.n_rows;
-        const float l = qv ? lse[size_t(itx.head) * stat_stride + itx.q_row + qi] : INFINITY;
-        sm.lse2[warp][qi] = (l == -INFINITY) ? INFINITY : l * 1.4426950408889634f;
-        sm.delta[warp][qi] = qv ? delta[size_t(itx.head) * stat_stride + itx.q_row + qi] : 0.f;
-        int4 m = make_int4(0, 0, 0, 0);
-        if (qv) m = masks[itx.mask_row + qi];
+        sm.lse2[warp][qi] = (nst.l[h] == -INFINITY) ? INFINITY : nst.l[h] * 1.4426950408889634f;
+        sm.delta[warp][qi] = nst.d[h];
+        int4 m = nst.m[h];
         m.y = max(m.y, m.x); m.w = max(m.w, m.z);
         sm.rng[warp][qi] = m;
       }
       __syncwarp();
+      if (t + 1 < n_items) {
+        nxt = load_item(my_items, t + 1, group, kv_head);
+        fetch_stats(nxt, nst);
+      }
       ok = mbar_wait(&sm.sdp_full, t & 1, abort_word);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
@@ -311,9 +365,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       if (ok) {
         tc_fence_after();
         flush_dq(prev);
+        asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
         // dK / dV: lane = key row, 128 fp32 columns each
-        float* dk = ptrs.dkv[cta.dkv_dev] + ((size_t(cta.dkv_row + r) * 2 + 0) * hkv + cta.kv_head) * kHeadDim;
-        float* dv = ptrs.dkv[cta.dkv_dev] + ((size_t(cta.dkv_row + r) * 2 + 1) * hkv + cta.kv_head) * kHeadDim;
+        float* dk = ptrs.dkv[cta.dkv_dev] + ((size_t(cta.dkv_row + r) * 2 + 0) * hkv + kv_head) * kHeadDim;
+        float* dv = ptrs.dkv[cta.dkv_dev] + ((size_t(cta.dkv_row + r) * 2 + 1) * hkv + kv_head) * kHeadDim;
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
           uint32_t reg[32];
@@ -336,6 +391,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         }
       }
     }
+    // no staged dQ tile may still be in flight when the CTA retires (also on the abort path)
+    asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
   }
   tc_fence_before();
   __syncthreads();
@@ -386,7 +443,7 @@ extern "C" int dcpk_attn_delta(const void* o, const void* d_o, float* delta, int
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
 
-// Launches the backward kernel: one CTA per entry of `ctas`.
+// Launches the backward kernel: one CTA per (entry of `ctas`, KV head).
 extern "C" int dcpk_attn_bwd(const void* q_arena, const void* do_arena, long q_rows, const void* kv_arena,
                              long kv_rows, int hq, int hkv, const void* ctas, int n_ctas, const void* items,
                              const void* masks, const float* lse, const float* delta, int stat_stride,
@@ -409,8 +466,8 @@ extern "C" int dcpk_attn_bwd(const void* q_arena, const void* do_arena, long q_r
       return -4;
     g_bwd_attr_set = 1;
   }
-  attn_bwd_kernel<<<n_ctas, kBwdThreads, smem, static_cast<cudaStream_t>(stream)>>>(
-      tm_q, tm_do, tm_kv, static_cast<const BwdCta*>(ctas), static_cast<const BwdItem*>(items),
+  attn_bwd_kernel<<<dim3(hkv, n_ctas), kBwdThreads, smem, static_cast<cudaStream_t>(stream)>>>(
+      tm_q, tm_do, tm_kv, static_cast<const BwdCta*>(ctas), static_cast<const BwdItemDesc*>(items),
       static_cast<const int4*>(masks), lse, delta, pp, hq, hkv, stat_stride, scale, status);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }

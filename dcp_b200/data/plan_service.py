@@ -1,0 +1,171 @@
+"""Ahead-of-time planning of training iterations in worker processes.
+
+Planning one iteration (block generation, hypergraph placement, staging, lowering) is CPU work
+that takes a sizeable fraction of a second for 100k-token batches; it is hidden behind GPU work
+by planning iterations ahead in a pool of processes.  Planning is deterministic in its inputs, so
+every rank plans the same batch independently and keeps only its own share: no plan has to cross
+ranks and no key-value server is needed (the reference ships pickled plans through Redis,
+dcp/data/dataloader.py:519-740, 754-932, dcp/data/kv_redis.py:22-135).
+
+``plan_iteration`` is the pure function; ``PlanService`` adds the look-ahead pool.
+"""
+from __future__ import annotations
+
+import concurrent.futures as cf
+import multiprocessing as mp
+import time
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from ..core.common import get_default_execution_context
+from ..core.instructions import BufferType
+from ..planner import masks as mask_lib
+from ..planner.compiler import CompilerConfig, InstrCompiler
+from ..planner.lowering import FusedProgram, lower_all
+from ..planner.workload import generate_workload, pad_seqlens
+from ..runtime.layout import LocalLayout, seq_token_offsets
+from . import synth
+
+
+@dataclass
+class PlanSpec:
+    """Everything that determines the plans of one iteration."""
+    world: int                      # ranks taking part in training
+    dcp_size: int                   # ranks per context-parallel group (world % dcp_size == 0)
+    tokens_per_step: int            # global token budget
+    n_heads: int
+    n_kv_heads: int
+    head_dim: int = 128
+    block_size: int = 2048
+    head_block_size: int = 0        # 0 -> all heads in one block
+    mask: str = "causal"            # a name from planner.masks.MASK_FNS ("mixed" draws per sequence)
+    length_dist: synth.LengthDist = field(default_factory=lambda: synth.LOGNORMAL_8K)
+    vocab: int = 128256
+    seed: int = 0
+    n_stages: Optional[int] = None
+    build_backward: bool = True
+    build_instruction_plans: bool = False   # also emit ExecutionPlans (plan-interpreting executors)
+
+
+@dataclass
+class RankPlan:
+    iteration: int
+    program: FusedProgram
+    tokens: torch.Tensor            # int64 [local tokens] (pinned by the consumer)
+    labels: torch.Tensor
+    positions: torch.Tensor
+    n_global_tokens: int
+    n_group_tokens: int
+    seqlens: List[int]
+    plan_seconds: float
+    fw_plan: object = None
+    bw_plan: object = None
+    fw_workload: object = None
+    bw_workload: object = None
+
+
+def split_batch_over_groups(seqlens: Sequence[int], n_groups: int) -> List[List[int]]:
+    """Indices of the sequences each context-parallel group takes: longest first onto the group
+    with the least attention work (~ len^2) so far."""
+    load = [0.0] * n_groups
+    out: List[List[int]] = [[] for _ in range(n_groups)]
+    for i in sorted(range(len(seqlens)), key=lambda i: -seqlens[i]):
+        g = load.index(min(load))
+        out[g].append(i)
+        load[g] += float(seqlens[i]) ** 2 + 4096.0 * seqlens[i]
+    return [sorted(x) for x in out]
+
+
+def plan_iteration(spec: PlanSpec, iteration: int, rank: int) -> RankPlan:
+    """Synthesise iteration ``iteration``'s batch from the spec's length distribution and plan it."""
+    seed = spec.seed * 1000003 + iteration
+    seqlens = synth.sample_seqlens(spec.tokens_per_step, spec.length_dist, seed)
+    batch = synth.make_token_batch(seqlens, spec.vocab, seed)
+    info = synth.assign_mask_kinds(seqlens, seed) if spec.mask == "mixed" else None
+    return plan_batch(spec, iteration, rank, seqlens, batch, info)
+
+
+def plan_batch(spec: PlanSpec, iteration: int, rank: int, seqlens: Sequence[int], batch: Dict[str, np.ndarray],
+               mask_fn_info: Optional[List[dict]] = None, mask_fn=None) -> RankPlan:
+    """Plan one packed batch (``batch`` holds per-token arrays over the concatenated sequences) and
+    return rank ``rank``'s share: its fused program, its tokens in local buffer order and, when
+    requested, its instruction plans."""
+    t0 = time.time()
+    seqlens = [int(x) for x in seqlens]
+    n_groups = spec.world // spec.dcp_size
+    group_id, group_rank = divmod(rank, spec.dcp_size)
+    members = split_batch_over_groups(seqlens, n_groups)[group_id] if n_groups > 1 else list(range(len(seqlens)))
+    raw = [seqlens[i] for i in members]
+    cu_all = seq_token_offsets(seqlens)
+    bs = spec.block_size
+    pad = pad_seqlens(raw, bs)
+    info = [mask_fn_info[i] for i in members] if mask_fn_info is not None else None
+    fn = mask_fn or mask_lib.get_mask_fn(spec.mask)
+    mask = fn(raw, pad, torch.int32, info)
+    ctx = get_default_execution_context(spec.dcp_size, 1)
+    hbs = spec.head_block_size or spec.n_heads
+    d = spec.head_dim
+    wl = generate_workload((sum(pad), spec.n_heads, d), (sum(pad), 2, spec.n_kv_heads, d), raw, pad, bs, hbs,
+                           ctx.comp_cost_model, mask, torch.bfloat16)
+    compiler = InstrCompiler(ctx, CompilerConfig(n_stages=spec.n_stages))
+    fw_wl, bw_wl, fw_plans, bw_plans = compiler.compile(wl, generate_backward=spec.build_instruction_plans)
+    dev = (0, group_rank)
+    program = lower_all(ctx, fw_wl, spec.build_backward, only=dev)[dev]
+    lay = LocalLayout(fw_wl, dev)
+    idx = []
+    for _, m in lay.blocks.get(BufferType.LOCAL_Q, []):
+        if m.head_id != 0:
+            continue
+        t0_tok = int(cu_all[members[m.seq_id]]) + m.block_id * bs
+        idx.append(np.arange(t0_tok, t0_tok + m.n_tokens))
+    idx = np.concatenate(idx) if idx else np.zeros(0, dtype=np.int64)
+    to_t = lambda a: torch.from_numpy(np.ascontiguousarray(np.asarray(a)[idx]))
+    return RankPlan(iteration, program, to_t(batch["tokens"]), to_t(batch["labels"]), to_t(batch["positions"]),
+                    int(sum(seqlens)), int(sum(raw)), list(seqlens), time.time() - t0,
+                    fw_plans.get(dev) if spec.build_instruction_plans else None,
+                    bw_plans.get(dev) if (spec.build_instruction_plans and bw_plans) else None,
+                    fw_wl if spec.build_instruction_plans else None, bw_wl if spec.build_instruction_plans else None)
+
+
+def _worker_init():
+    torch.set_num_threads(1)
+
+
+class PlanService:
+    """Look-ahead planner: ``get(i)`` returns iteration i's plan and keeps ``lookahead`` more in flight."""
+
+    def __init__(self, spec: PlanSpec, rank: int, n_workers: int = 2, lookahead: int = 3, start: int = 0):
+        self.spec, self.rank = spec, rank
+        self.lookahead = max(1, lookahead)
+        self._pool = None
+        if n_workers > 0:
+            self._pool = cf.ProcessPoolExecutor(max_workers=n_workers, mp_context=mp.get_context("spawn"),
+                                                initializer=_worker_init)
+        self._pending: Dict[int, "cf.Future"] = {}
+        self._next_submit = start
+        self.wait_seconds = 0.0
+
+    def _submit_up_to(self, last: int) -> None:
+        while self._next_submit <= last:
+            i = self._next_submit
+            if self._pool is not None:
+                self._pending[i] = self._pool.submit(plan_iteration, self.spec, i, self.rank)
+            self._next_submit += 1
+
+    def get(self, iteration: int) -> RankPlan:
+        self._submit_up_to(iteration + self.lookahead)
+        if self._pool is None:
+            return plan_iteration(self.spec, iteration, self.rank)
+        t0 = time.time()
+        fut = self._pending.pop(iteration, None)
+        plan = fut.result() if fut is not None else plan_iteration(self.spec, iteration, self.rank)
+        self.wait_seconds += time.time() - t0
+        return plan
+
+    def close(self) -> None:
+        if self._pool is not None:
+            self._pool.shutdown(wait=False, cancel_futures=True)
+            self._pool = None

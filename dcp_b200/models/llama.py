@@ -149,9 +149,9 @@ class LlamaModel:
         self.p: Dict[str, torch.Tensor] = {}
         for name, shp in shapes:
             off, n = self.offsets[name]
-            t = self.params_flat[off:off + n].view(shp)
+            t = self.params_flat[off:off + n].view(shp).data
             t.requires_grad_(True)
-            t.grad = self.grads_flat[off:off + n].view(shp)
+            t.grad = self.grads_flat[off:off + n].view(shp).data
             self.p[name] = t
         self.init_weights(seed)
 

@@ -43,6 +43,11 @@ def stream_handle():
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
+LAUNCHES = 0  # kernel-entry calls made through this library since import (each launches >= 1 kernel)
+
+
 def check(rc: int, what: str):
+    global LAUNCHES
+    LAUNCHES += 1
     if rc != 0:
         raise RuntimeError(f"{what} failed with code {rc}")

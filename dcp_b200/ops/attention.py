@@ -194,43 +194,40 @@ def _tile_bounds(rng: np.ndarray, tile: int):
 
 
 def build_bwd_tables(rows: Sequence[AttnRow], block_size: int, hq: int, hkv: int, device) -> BwdTables:
-    """KV-major work lists for the backward kernel: one CTA per (KV tile, KV head)."""
-    group = hq // hkv
+    """KV-major work lists for the backward kernel: one table entry per key tile (the kernel runs
+    it once per KV head) listing the 64-query tiles that see it; heads are not materialised."""
     masks, mask_row = [], 0
-    cta_items = {}  # (kv_row, n_valid, kv_head, dkv_dev, dkv_row) -> list of item arrays
+    cta_items = {}  # (kv_row, n_valid, dkv_dev, dkv_row) -> list of item arrays
     pairs = 0.0
     for row in rows:
         rng = np.ascontiguousarray(row.ranges, dtype=np.int32).reshape(-1, 4)
         masks.append(rng)
+        assert len(row.heads) == hq, "the backward kernel visits every query head of a row"
         pairs += _pair_count(rng) * len(row.heads)
         n_qt, (u0s, u0e, u1s, u1e, i0s, i0e, i1s, i1e) = _tile_bounds(rng, Q_TILE_BWD)
         qt = np.arange(n_qt)
         n_rows_t = np.minimum(Q_TILE_BWD, row.n_tokens - qt * Q_TILE_BWD)
-        heads = np.asarray(list(row.heads), dtype=np.int64)
         for e, (kv_row, n_tok) in enumerate(row.kv):
             dkv_dev, dkv_row = row.dkv[e] if row.dkv else (0, kv_row)
-            for t in range((n_tok + TILE_N - 1) // TILE_N):
-                p0 = e * block_size + t * TILE_N
-                nv = min(TILE_N, n_tok - t * TILE_N)
-                need = ((p0 < u0e) & (p0 + nv > u0s)) | ((p0 < u1e) & (p0 + nv > u1s))
-                idx = qt[need]
-                if idx.size == 0:
-                    continue
-                full = (nv == TILE_N) & (((i0s <= p0) & (i0e >= p0 + nv)) | ((i1s <= p0) & (i1e >= p0 + nv)))
-                for g in np.unique(heads // group):
-                    hs = heads[heads // group == g]
-                    ii = np.repeat(idx, hs.size)
-                    hh = np.tile(hs, idx.size)
-                    arr = np.stack([
-                        row.q_row + ii * Q_TILE_BWD, n_rows_t[ii], hh, np.full(ii.size, p0), mask_row + ii * Q_TILE_BWD,
-                        np.full(ii.size, row.dq_dev), row.dq_row + ii * Q_TILE_BWD, full[ii].astype(np.int64)], axis=1)
-                    key = (kv_row + t * TILE_N, nv, int(g), dkv_dev, dkv_row + t * TILE_N)
-                    cta_items.setdefault(key, []).append(arr)
+            n_sub = (n_tok + TILE_N - 1) // TILE_N
+            p0 = e * block_size + np.arange(n_sub) * TILE_N                      # [n_sub]
+            nv = np.minimum(TILE_N, n_tok - np.arange(n_sub) * TILE_N)
+            lo, hi = p0[:, None], (p0 + nv)[:, None]
+            need = ((lo < u0e[None]) & (hi > u0s[None])) | ((lo < u1e[None]) & (hi > u1s[None]))   # [n_sub, n_qt]
+            full = (nv[:, None] == TILE_N) & (((i0s[None] <= lo) & (i0e[None] >= hi)) | ((i1s[None] <= lo) & (i1e[None] >= hi)))
+            for t in np.nonzero(need.any(axis=1))[0].tolist():
+                ii = qt[need[t]]
+                arr = np.stack([row.q_row + ii * Q_TILE_BWD, n_rows_t[ii], np.full(ii.size, p0[t]),
+                                mask_row + ii * Q_TILE_BWD, np.full(ii.size, row.dq_dev),
+                                row.dq_row + ii * Q_TILE_BWD, full[t][ii].astype(np.int64),
+                                np.zeros(ii.size, dtype=np.int64)], axis=1)
+                key = (kv_row + t * TILE_N, int(nv[t]), dkv_dev, dkv_row + t * TILE_N)
+                cta_items.setdefault(key, []).append(arr)
         mask_row += row.n_tokens
     ctas, item_chunks, off = [], [], 0
     for key, chunks in sorted(cta_items.items(), key=lambda kv: -sum(c.shape[0] for c in kv[1])):
         n = sum(c.shape[0] for c in chunks)
-        ctas.append((key[0], key[1], key[2], off, n, key[3], key[4], 0))
+        ctas.append((key[0], key[1], off, n, key[2], key[3], 0, 0))
         item_chunks.extend(chunks)
         off += n
     c_np = np.asarray(ctas, dtype=np.int32).reshape(-1, 8)

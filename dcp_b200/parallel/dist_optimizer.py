@@ -1,9 +1,10 @@
 """ZeRO-1 style sharded AdamW over flat bf16 parameter / gradient buffers in peer memory.
 
-step():  barrier -> fused reduce-scatter (peer loads of every rank's gradient slice, fp32 sum,
-scale, squared-norm) -> optional global-norm clip (one tiny NCCL all-reduce of a scalar)
--> fused AdamW + parameter all-gather (updated bf16 values stored into every rank's parameter
-buffer) -> barrier.  The rank-local fp32 state (master weights, m, v) covers 1/world of the
+step():  barrier -> (when clipping) squared norm of the rank-summed gradient slice, read straight
+from every rank's bf16 gradient buffer, + one tiny NCCL all-reduce of the scalar -> ONE kernel
+that sums the slice over ranks with peer loads (reduce-scatter), applies scale and clip, updates
+the fp32 AdamW state, and stores the new bf16 parameters into every rank's parameter buffer
+(all-gather) -> barrier.  No fp32 gradient copy is ever materialised.  The rank-local fp32 state (master weights, m, v) covers 1/world of the
 model.  This is the role Megatron's distributed optimizer + DDP reduce-scatter play for the
 reference (benchmark/mlm/launch_template.txt:73-80).
 """
@@ -45,7 +46,6 @@ class ShardedAdamW:
         self.master = bufs.params[self.shard_off:self.shard_off + self.shard_len].float()
         self.m = torch.zeros_like(self.master)
         self.v = torch.zeros_like(self.master)
-        self.main_grad = torch.empty_like(self.master)
         self.sq_norm = torch.zeros(1, dtype=torch.float32, device=dev)
         self.clip_coef = torch.ones(1, dtype=torch.float32, device=dev)
         self.step_count = 0
@@ -66,26 +66,24 @@ class ShardedAdamW:
         a = b.arena
         self.step_count += 1
         a.barrier()   # every rank finished writing its gradients
-        self.sq_norm.zero_()
-        _lib.check(lib.dcpk_grad_reduce_scatter(_ptr_array(a.peer_ptrs("grads")), ctypes.c_int(b.world),
-                                                ctypes.c_long(self.shard_off), ctypes.c_long(self.shard_len),
-                                                ctypes.c_float(grad_scale), _lib.ptr(self.main_grad),
-                                                _lib.ptr(self.sq_norm), _lib.stream_handle()), "grad_reduce_scatter")
+        grads, params = _ptr_array(a.peer_ptrs("grads")), _ptr_array(a.peer_ptrs("params"))
+        off, n = ctypes.c_long(self.shard_off), ctypes.c_long(self.shard_len)
         clip_ptr = ctypes.c_void_p(0)
         if self.clip is not None:
+            self.sq_norm.zero_()
+            _lib.check(lib.dcpk_grad_sqnorm(grads, ctypes.c_int(b.world), off, n, ctypes.c_float(grad_scale),
+                                            _lib.ptr(self.sq_norm), _lib.stream_handle()), "grad_sqnorm")
             if b.world > 1:
                 import torch.distributed as dist
                 dist.all_reduce(self.sq_norm, group=self.group)
             torch.clamp(self.clip / (self.sq_norm.sqrt() + 1e-6), max=1.0, out=self.clip_coef)
             clip_ptr = _lib.ptr(self.clip_coef)
-        _lib.check(lib.dcpk_adamw_all_gather(_lib.ptr(self.master), _lib.ptr(self.m), _lib.ptr(self.v),
-                                             _lib.ptr(self.main_grad), _ptr_array(a.peer_ptrs("params")),
-                                             ctypes.c_int(b.world), ctypes.c_long(self.shard_off),
-                                             ctypes.c_long(self.shard_len), ctypes.c_float(self.lr),
-                                             ctypes.c_float(self.betas[0]), ctypes.c_float(self.betas[1]),
-                                             ctypes.c_float(self.eps), ctypes.c_float(self.wd),
-                                             ctypes.c_int(self.step_count), clip_ptr, _lib.stream_handle()),
-                   "adamw_all_gather")
+        _lib.check(lib.dcpk_fused_rs_adamw_ag(grads, params, ctypes.c_int(b.world), off, n, ctypes.c_float(grad_scale),
+                                              _lib.ptr(self.master), _lib.ptr(self.m), _lib.ptr(self.v),
+                                              ctypes.c_float(self.lr), ctypes.c_float(self.betas[0]),
+                                              ctypes.c_float(self.betas[1]), ctypes.c_float(self.eps),
+                                              ctypes.c_float(self.wd), ctypes.c_int(self.step_count), clip_ptr,
+                                              _lib.stream_handle()), "fused_rs_adamw_ag")
         self.kernel_launches += 2
         a.barrier()   # every rank's parameter buffer holds all updated shards
 

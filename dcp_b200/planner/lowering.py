@@ -60,7 +60,9 @@ def _i4(rows) -> np.ndarray:
     return np.asarray(rows, dtype=np.int32).reshape(-1, 4)
 
 
-def lower_all(context: ExecutionContext, workload: WorkloadSpec, build_backward: bool = True) -> Dict[Device, FusedProgram]:
+def lower_all(context: ExecutionContext, workload: WorkloadSpec, build_backward: bool = True,
+              only: Optional[Device] = None) -> Dict[Device, FusedProgram]:
+    """Programs of all devices, or just of ``only`` (row and slot numbering is global either way)."""
     wl = workload
     devices = context.devices()
     world = len(devices)
@@ -135,6 +137,8 @@ def lower_all(context: ExecutionContext, workload: WorkloadSpec, build_backward:
 
     programs: Dict[Device, FusedProgram] = {}
     for d in devices:
+        if only is not None and tuple(only) != d:
+            continue
         prog = FusedProgram(rank_of[d], world, block_size, hq, hkv, n_stages,
                             layouts[d].n_tokens(BufferType.LOCAL_Q), layouts[d].n_tokens(BufferType.LOCAL_KV),
                             q_next[d], kv_next[d], part_next[d])

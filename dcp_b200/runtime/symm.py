@@ -67,7 +67,9 @@ class SymmetricArena:
                 n *= int(s)
             nbytes = n * torch.empty((), dtype=dtype).element_size()
             off = self.offsets[name]
-            self._views[name] = self.buf[off:off + nbytes].view(dtype).view(*shape)
+            # .data: an alias with its own autograd version counter, so in-place writes to one region
+            # (e.g. gradient accumulation) do not invalidate tensors autograd saved from another
+            self._views[name] = self.buf[off:off + nbytes].view(dtype).view(*shape).data
         return self._views[name]
 
     def peer_ptrs(self, name: str) -> List[int]:

@@ -1,0 +1,217 @@
+"""Training engine: Llama-architecture model + DCP attention executor + sharded optimizer.
+
+``TrainEngine.train_step(plan)`` is the public per-iteration call: it stages the iteration's
+token ids / labels / positions and kernel tables from pinned host memory, runs forward,
+backward and the optimizer step, and returns the loss.  ``python -m dcp_b200.train`` runs a
+synthetic-data training loop (one process per GPU under torch.distributed.run) and logs
+"elapsed time per iteration (ms)" and "Training loss:" lines in the format the reference's log
+parsers read (benchmark/plotting/utils.py:10-31).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import time
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+
+from .data import synth
+from .data.plan_service import PlanService, PlanSpec, RankPlan
+from .models.llama import LLAMA3_8B, LlamaConfig, LlamaModel, tiny_config
+from .ops import _lib
+from .parallel.dist_optimizer import FlatBuffers, ShardedAdamW
+from .runtime.executor_fused import FusedAttentionExecutor
+
+
+@dataclass
+class EngineConfig:
+    model: LlamaConfig
+    tokens_per_step: int
+    dcp_size: int = 0               # 0 -> all ranks form one context-parallel group
+    block_size: int = 2048
+    mask: str = "causal"
+    length_dist: synth.LengthDist = None
+    n_stages: Optional[int] = None
+    lr: float = 3e-4
+    weight_decay: float = 0.1
+    clip_grad: Optional[float] = 1.0
+    recompute: bool = True
+    seed: int = 0
+    planner_workers: int = 2
+    lookahead: int = 3
+    lm_head_chunk: int = 4096
+
+
+class TrainEngine:
+    def __init__(self, cfg: EngineConfig, device: torch.device, world_group=None):
+        import torch.distributed as dist
+        self.cfg, self.device = cfg, device
+        self.world = dist.get_world_size(world_group) if world_group is not None else 1
+        self.rank = dist.get_rank(world_group) if world_group is not None else 0
+        self.world_group = world_group
+        dcp = cfg.dcp_size or self.world
+        assert self.world % dcp == 0
+        self.dcp_size = dcp
+        self.dcp_group = world_group
+        if world_group is not None and dcp != self.world:
+            # one subgroup per context-parallel group; every rank has to create all of them
+            for g in range(self.world // dcp):
+                ranks = list(range(g * dcp, (g + 1) * dcp))
+                grp = dist.new_group(ranks)
+                if self.rank in ranks:
+                    self.dcp_group = grp
+        m = cfg.model
+        n_flat = LlamaModel.flat_size(m)
+        self.bufs = FlatBuffers(n_flat, device, world_group if self.world > 1 else None)
+        self.model = LlamaModel(m, device, self.bufs.params, self.bufs.grads, seed=cfg.seed, recompute=cfg.recompute,
+                                lm_head_chunk=cfg.lm_head_chunk)
+        self.optimizer = ShardedAdamW(self.bufs, cfg.lr, weight_decay=cfg.weight_decay, clip_grad=cfg.clip_grad,
+                                      group=world_group)
+        group_tokens = cfg.tokens_per_step // (self.world // dcp)
+        cap = int(group_tokens * 1.3) + 4 * cfg.block_size
+        self.executor = FusedAttentionExecutor(m.n_heads, m.n_kv_heads, cap, cap, cap, device,
+                                               self.dcp_group if dcp > 1 else None)
+        self.model.set_executor(self.executor)
+        self.spec = PlanSpec(self.world, dcp, cfg.tokens_per_step, m.n_heads, m.n_kv_heads, m.head_dim, cfg.block_size,
+                             0, cfg.mask, cfg.length_dist or synth.LOGNORMAL_8K, m.vocab, cfg.seed, cfg.n_stages)
+        self.plans = PlanService(self.spec, self.rank, cfg.planner_workers, cfg.lookahead)
+        self.iteration = 0
+        self.h2d_bytes = 0
+        self.d2h_bytes = 0
+
+    # ---- one iteration
+    def stage_inputs(self, plan: RankPlan):
+        """Pinned host -> device copies of this iteration's inputs and kernel tables."""
+        dev = self.device
+        host = [plan.tokens.pin_memory(), plan.labels.pin_memory(), plan.positions.pin_memory()]
+        toks, labels, pos = (t.to(dev, non_blocking=True) for t in host)
+        self.executor.prepare(plan.program)
+        n = sum(t.numel() * t.element_size() for t in host)
+        p = plan.program
+        for tabs in list(p.fwd) + list(p.bwd):
+            if tabs is not None:
+                n += sum(t.numel() * t.element_size() for t in (getattr(tabs, "tiles", None), getattr(tabs, "kv_entries", None),
+                                                                 getattr(tabs, "ctas", None), getattr(tabs, "items", None),
+                                                                 tabs.masks) if t is not None)
+        self.h2d_bytes = n
+        return toks, labels, pos
+
+    def run_step(self, toks, labels, pos, n_global_tokens: int) -> torch.Tensor:
+        """Forward + backward + optimizer on staged inputs; returns the device loss tensor."""
+        self.model.zero_grad()
+        loss = self.model.loss(toks, labels, pos, 1.0 / max(n_global_tokens, 1))
+        loss.backward()
+        self.optimizer.step(1.0)
+        return loss.detach()
+
+    def train_step(self, plan: Optional[RankPlan] = None) -> float:
+        """Public API: plan (or fetch) the iteration, copy its inputs in, step, read the loss back."""
+        if plan is None:
+            plan = self.plans.get(self.iteration)
+        toks, labels, pos = self.stage_inputs(plan)
+        loss = self.run_step(toks, labels, pos, plan.n_global_tokens)
+        if self.world > 1:
+            import torch.distributed as dist
+            dist.all_reduce(loss, group=self.world_group)
+        value = float(loss.item())         # device -> host read of the step's result
+        self.d2h_bytes = loss.numel() * loss.element_size()
+        self.executor.check_status()
+        self.iteration += 1
+        return value
+
+    def close(self) -> None:
+        self.plans.close()
+
+    # ---- checkpoint / resume: per-rank shard files
+    def save_checkpoint(self, directory: str) -> str:
+        os.makedirs(directory, exist_ok=True)
+        path = os.path.join(directory, f"rank{self.rank:03d}.pt")
+        state = {"iteration": self.iteration, "optimizer": self.optimizer.state_dict(),
+                 "model_cfg": self.cfg.model.__dict__, "world": self.world, "seed": self.cfg.seed,
+                 "rng": torch.get_rng_state(), "cuda_rng": torch.cuda.get_rng_state(self.device)}
+        if self.rank == 0:
+            state["params_bf16"] = self.bufs.params
+        torch.save(state, path)
+        return path
+
+    def load_checkpoint(self, directory: str) -> None:
+        path = os.path.join(directory, f"rank{self.rank:03d}.pt")
+        state = torch.load(path, map_location=self.device, weights_only=False)
+        assert state["world"] == self.world, "resume needs the world size the checkpoint was written with"
+        self.optimizer.load_state_dict(state["optimizer"])
+        self.iteration = int(state["iteration"])
+        torch.set_rng_state(state["rng"].cpu())
+        torch.cuda.set_rng_state(state["cuda_rng"].cpu(), self.device)
+        # every rank rebuilds the bf16 parameters from the fp32 master shards
+        o = self.optimizer
+        self.bufs.arena.barrier()
+        self.bufs.params[o.shard_off:o.shard_off + o.shard_len].copy_(o.master)
+        if self.world > 1:
+            import torch.distributed as dist
+            shards = [torch.empty_like(self.bufs.params[:o.shard_len]) for _ in range(self.world)]
+            dist.all_gather(shards, self.bufs.params[o.shard_off:o.shard_off + o.shard_len].contiguous(),
+                            group=self.world_group)
+            per = o.shard_len
+            for r, s in enumerate(shards):
+                n = min(per, self.bufs.n_flat - r * per)
+                if n > 0:
+                    self.bufs.params[r * per:r * per + n].copy_(s[:n])
+        self.plans.close()
+        self.plans = PlanService(self.spec, self.rank, self.cfg.planner_workers, self.cfg.lookahead, start=self.iteration)
+
+
+def init_distributed():
+    """(rank, world, local_rank, group): NCCL process group when launched with several ranks."""
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    group = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        group = dist.group.WORLD
+    return rank, world, local, group
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser(description="Synthetic-data DCP training loop")
+    ap.add_argument("--model", default="llama3-8b", choices=["llama3-8b", "tiny"])
+    ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--tokens-per-step", type=int, default=131072)
+    ap.add_argument("--dcp-size", type=int, default=0)
+    ap.add_argument("--dcp-block-size", type=int, default=2048)
+    ap.add_argument("--dcp-mask-type", default="causal")
+    ap.add_argument("--length-dist", default="lognormal8k", choices=["lognormal8k", "lognormal16k", "mixture"])
+    ap.add_argument("--lr", type=float, default=3e-4)
+    ap.add_argument("--log-interval", type=int, default=1)
+    ap.add_argument("--save", default=None)
+    ap.add_argument("--load", default=None)
+    args = ap.parse_args(argv)
+    rank, world, local, group = init_distributed()
+    dists = {"lognormal8k": synth.LOGNORMAL_8K, "lognormal16k": synth.LOGNORMAL_16K, "mixture": synth.MIXTURE}
+    model = LLAMA3_8B if args.model == "llama3-8b" else tiny_config()
+    cfg = EngineConfig(model, args.tokens_per_step, args.dcp_size, args.dcp_block_size, args.dcp_mask_type,
+                       dists[args.length_dist], lr=args.lr)
+    eng = TrainEngine(cfg, torch.device("cuda", local), group)
+    if args.load:
+        eng.load_checkpoint(args.load)
+    t_last = time.time()
+    for it in range(eng.iteration, eng.iteration + args.iters):
+        loss = eng.train_step()
+        if rank == 0 and (it + 1) % args.log_interval == 0:
+            now = time.time()
+            ms = (now - t_last) * 1000 / args.log_interval
+            t_last = now
+            print(f" iteration {it + 1:8d} | elapsed time per iteration (ms): {ms:.1f} | Training loss: {loss:.6f}",
+                  flush=True)
+    if args.save:
+        eng.save_checkpoint(args.save)
+    eng.close()
+
+
+if __name__ == "__main__":
+    main()
