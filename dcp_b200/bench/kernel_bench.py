@@ -97,6 +97,18 @@ def bench_attention(kind, args):
         dkv = torch.zeros(nkv + 128, 2, hkv, 128, device=dev)
         ms = time_fn(lambda: A.attn_bwd(q, dout, kv, lse, delta, bt, [dq], [dkv], scale, status), args.iters, 3, flush)
         flops = bt.flops
+        if args.timeline:
+            from ..ops import _lib
+            tl = torch.zeros(16, dtype=torch.int64, device=dev)
+            _lib.load().dcpk_attn_bwd_set_timeline(_lib.ptr(tl))
+            A.attn_bwd(q, dout, kv, lse, delta, bt, [dq], [dkv], scale, status)
+            torch.cuda.synchronize()
+            _lib.load().dcpk_attn_bwd_set_timeline(None)
+            n_vis = int(bt.ctas[0, 3].item()) * (hq // hkv)
+            names = ["stats->smem", "wait S/dP", "ld S,dP", "wait dQ(t-1)", "drain dQ", "math", "store P,dS + arrive", "-",
+                     "umma: issue S/dP", "umma: wait P ready", "umma: issue acc", "umma: wait Q,dO + S free"]
+            print("timeline of CTA (0,0), cycles per visit (", n_vis, "visits ):",
+                  {n: round(v / max(n_vis, 1)) for n, v in zip(names, tl.tolist()) if n != "-"})
     torch.cuda.synchronize()
     assert status.item() == 0
     tfs = flops / ms / 1e9
@@ -162,6 +174,7 @@ def main():
     ap.add_argument("--mask", default="causal", choices=["full", "causal", "lambda"])
     ap.add_argument("--variant", type=int, default=0)
     ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--timeline", action="store_true", help="print per-phase cycle counts of one backward CTA")
     ap.add_argument("--skip-dq", action="store_true", help="backward without the dQ drain (upper bound probe)")
     args = ap.parse_args()
     if args.kind == "ops":

@@ -91,6 +91,14 @@ struct __align__(1024) BwdSmem {
   int abort_word;
 };
 
+// Optional per-phase cycle counters of CTA (0,0) (set with dcpk_attn_bwd_set_timeline; null = off).
+// Layout: [phase][sum of cycles]; phases 0-7 gradient warp 0, 8-11 UMMA warp.
+__device__ long long* g_bwd_timeline = nullptr;
+#define TL_ADD(idx, t_prev)                                                        \
+  do {                                                                             \
+    if (tl) { long long now_ = clock64(); if (lane == 0) tl[idx] += now_ - (t_prev); (t_prev) = now_; } \
+  } while (0)
+
 __device__ __forceinline__ void red_add_f32(float* p, float v) {
   asm volatile("red.global.add.f32 [%0], %1;" ::"l"(p), "f"(v) : "memory");
 }
@@ -101,8 +109,8 @@ __device__ __forceinline__ void red_add_v4(float* p, float a, float b, float c, 
 
 __global__ void __launch_bounds__(kBwdThreads, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
-                const __grid_constant__ CUtensorMap tm_kv, const BwdCta* __restrict__ ctas,
-                const BwdItemDesc* __restrict__ items, const int4* __restrict__ masks,
+                const __grid_constant__ CUtensorMap tm_kv, const __grid_constant__ CUtensorMap tm_dq,
+                const BwdCta* __restrict__ ctas, const BwdItemDesc* __restrict__ items, const int4* __restrict__ masks,
                 const float* __restrict__ lse, const float* __restrict__ delta, BwdPtrs ptrs, int hq, int hkv,
                 int stat_stride, float scale, int* __restrict__ status) {
   extern __shared__ uint8_t smem_raw[];
@@ -119,6 +127,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     tma_prefetch_desc(&tm_q);
     tma_prefetch_desc(&tm_do);
     tma_prefetch_desc(&tm_kv);
+    tma_prefetch_desc(&tm_dq);
     mbar_init(&sm.kv_full, 1);
     for (int i = 0; i < 2; ++i) { mbar_init(&sm.qdo_full[i], 1); mbar_init(&sm.qdo_empty[i], 1); }
     mbar_init(&sm.sdp_full, 1);
@@ -139,6 +148,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   volatile int* abort_word = &sm.abort_word;
   constexpr uint32_t cS = 0, cdP = 64, cP = 128, cdS = 160, cdQ = 192, cdK = 256, cdV = 384;
 
+  long long* tl = (blockIdx.x == 0 && blockIdx.y == 0 && (warp == 0 || warp == 5)) ? g_bwd_timeline : nullptr;
+  long long tl_t = clock64();
   if (warp == 4) {
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
@@ -176,7 +187,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     bool ok = mbar_wait(&sm.kv_full, 0, abort_word);
     auto issue_acc = [&](int t) -> bool {
       const int st = t & 1;
+      TL_ADD(8, tl_t);
       if (!mbar_wait(&sm.p_ready, t & 1, abort_word)) return false;
+      TL_ADD(9, tl_t);
       tc_fence_after();
       if (lane == 0) {
         const uint32_t q_addr = smem_u32(sm.q[st]), do_addr = smem_u32(sm.dout[st]);
@@ -200,6 +213,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         umma_commit(&sm.qdo_empty[st]);
       }
       __syncwarp();
+      TL_ADD(10, tl_t);
       return true;
     };
     for (int i = 0; i < n_items && ok; ++i) {
@@ -207,6 +221,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       ok = mbar_wait(&sm.qdo_full[st], u & 1, abort_word);
       if (ok && i > 0) ok = mbar_wait(&sm.s_free, (i - 1) & 1, abort_word);
       if (!ok) break;
+      TL_ADD(11, tl_t);
       tc_fence_after();
       if (lane == 0) {
         const uint32_t q_addr = smem_u32(sm.q[st]), do_addr = smem_u32(sm.dout[st]);
@@ -254,15 +269,27 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       }
       fence_proxy_async_smem();
       __syncwarp();
-      float* dq = ptrs.dq[itx.dq_dev] + (size_t(itx.dq_row) * hq + itx.head) * kHeadDim + warp * 32;
-      const size_t row_stride = size_t(hq) * kHeadDim;
+      if (itx.dq_dev == 0) {
+        // local accumulator: one tiled TMA reduce-add drains the whole [64 x 32] tile.  Rows past
+        // n_rows hold exact zeros (their probabilities are masked to 0), so adding them is harmless.
+        if (lane == 0) {
+          asm volatile(
+              "cp.reduce.async.bulk.tensor.3d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3, %4}], [%1];"
+              ::"l"(reinterpret_cast<uint64_t>(&tm_dq)), "r"(smem_u32(stage)), "r"(warp * 32), "r"(itx.head),
+              "r"(itx.dq_row)
+              : "memory");
+        }
+      } else {
+        float* dq = ptrs.dq[itx.dq_dev] + (size_t(itx.dq_row) * hq + itx.head) * kHeadDim + warp * 32;
+        const size_t row_stride = size_t(hq) * kHeadDim;
 #pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        const int qi = lane + 32 * h;
-        if (qi < itx.n_rows) {
-          asm volatile("cp.reduce.async.bulk.global.shared::cta.bulk_group.add.f32 [%0], [%1], %2;"
-                       ::"l"(dq + qi * row_stride), "r"(smem_u32(stage + qi * 32)), "r"(128)
-                       : "memory");
+        for (int h = 0; h < 2; ++h) {
+          const int qi = lane + 32 * h;
+          if (qi < itx.n_rows) {
+            asm volatile("cp.reduce.async.bulk.global.shared::cta.bulk_group.add.f32 [%0], [%1], %2;"
+                         ::"l"(dq + qi * row_stride), "r"(smem_u32(stage + qi * 32)), "r"(128)
+                         : "memory");
+          }
         }
       }
       asm volatile("cp.async.bulk.commit_group;" ::: "memory");
@@ -304,9 +331,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         nxt = load_item(my_items, t + 1, group, kv_head);
         fetch_stats(nxt, nst);
       }
+      TL_ADD(0, tl_t);
       ok = mbar_wait(&sm.sdp_full, t & 1, abort_word);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
+      TL_ADD(1, tl_t);
       tc_fence_after();
       uint32_t sreg[64], dreg[64];
       tmem_ld32(tmem + lane_base + cS, sreg);
@@ -316,35 +345,59 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       tmem_wait_ld();
       tc_fence_before();
       mbar_arrive(&sm.s_free);
+      TL_ADD(2, tl_t);
       if (t > 0) {
         ok = mbar_wait(&sm.dq_full, (t - 1) & 1, abort_word);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
+        TL_ADD(3, tl_t);
         tc_fence_after();
         flush_dq(prev);
+        TL_ADD(4, tl_t);
       }
       const int kpos = itx.kv_pos0 + r;
       uint32_t preg[32], dsreg[32];
+      // The tile-level "no masking needed" switch is taken once, outside the element loop: with a
+      // branch per element every element becomes its own basic block and the compiler cannot
+      // interleave the independent exp / multiply chains (one warp per scheduler has nothing else
+      // to hide their latency with).
+      const float* lse2_w = sm.lse2[warp];
+      const float* delta_w = sm.delta[warp];
+      if (itx.full) {
 #pragma unroll
-      for (int c = 0; c < 32; ++c) {
-        float pv[2], dv[2];
+        for (int c = 0; c < 32; ++c) {
+          float pv[2], dv[2];
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          const int qi = 2 * c + h;
-          bool allow = key_valid;
-          if (!itx.full) {
-            const int4 m = sm.rng[warp][qi];
-            allow = allow && ((unsigned(kpos - m.x) < unsigned(m.y - m.x)) || (unsigned(kpos - m.z) < unsigned(m.w - m.z)));
-          } else {
-            allow = allow && (qi < itx.n_rows);
+          for (int h = 0; h < 2; ++h) {
+            const int qi = 2 * c + h;
+            const bool allow = key_valid && (qi < itx.n_rows);
+            const float e = fast_exp2(fmaf(__uint_as_float(sreg[qi]), sl2, -lse2_w[qi]));
+            pv[h] = allow ? e : 0.f;
+            dv[h] = pv[h] * (__uint_as_float(dreg[qi]) - delta_w[qi]) * scale;
           }
-          const float p = allow ? fast_exp2(fmaf(__uint_as_float(sreg[qi]), sl2, -sm.lse2[warp][qi])) : 0.f;
-          pv[h] = p;
-          dv[h] = p * (__uint_as_float(dreg[qi]) - sm.delta[warp][qi]) * scale;
+          preg[c] = pack_bf16x2(pv[0], pv[1]);
+          dsreg[c] = pack_bf16x2(dv[0], dv[1]);
         }
-        preg[c] = pack_bf16x2(pv[0], pv[1]);
-        dsreg[c] = pack_bf16x2(dv[0], dv[1]);
+      } else {
+        const int4* rng_w = sm.rng[warp];
+#pragma unroll
+        for (int c = 0; c < 32; ++c) {
+          float pv[2], dv[2];
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            const int qi = 2 * c + h;
+            const int4 m = rng_w[qi];
+            const bool allow = key_valid && ((unsigned(kpos - m.x) < unsigned(m.y - m.x)) ||
+                                             (unsigned(kpos - m.z) < unsigned(m.w - m.z)));
+            const float e = fast_exp2(fmaf(__uint_as_float(sreg[qi]), sl2, -lse2_w[qi]));
+            pv[h] = allow ? e : 0.f;
+            dv[h] = pv[h] * (__uint_as_float(dreg[qi]) - delta_w[qi]) * scale;
+          }
+          preg[c] = pack_bf16x2(pv[0], pv[1]);
+          dsreg[c] = pack_bf16x2(dv[0], dv[1]);
+        }
       }
+      TL_ADD(5, tl_t);
       tmem_st32(tmem + lane_base + cP, preg);
       tmem_st32(tmem + lane_base + cdS, dsreg);
 #pragma unroll
@@ -356,6 +409,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(&sm.p_ready);
+      TL_ADD(6, tl_t);
       prev = itx;
     }
     ok = __all_sync(0xffffffffu, ok);
@@ -443,6 +497,12 @@ extern "C" int dcpk_attn_delta(const void* o, const void* d_o, float* delta, int
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
 
+// Points the kernel's cycle-counter timeline at `buf` (>= 16 int64, device memory) or disables it (null).
+extern "C" int dcpk_attn_bwd_set_timeline(void* buf) {
+  long long* p = static_cast<long long*>(buf);
+  return cudaMemcpyToSymbol(g_bwd_timeline, &p, sizeof(p)) == cudaSuccess ? 0 : -5;
+}
+
 // Launches the backward kernel: one CTA per (entry of `ctas`, KV head).
 extern "C" int dcpk_attn_bwd(const void* q_arena, const void* do_arena, long q_rows, const void* kv_arena,
                              long kv_rows, int hq, int hkv, const void* ctas, int n_ctas, const void* items,
@@ -451,7 +511,8 @@ extern "C" int dcpk_attn_bwd(const void* q_arena, const void* do_arena, long q_r
                              void* stream) {
   if (n_ctas <= 0) return 0;
   if (n_dst > kMaxPeers || hq % hkv != 0) return -3;
-  CUtensorMap tm_q, tm_do, tm_kv;
+  CUtensorMap tm_q, tm_do, tm_kv, tm_dq;
+  if (encode_f32_tile_map(&tm_dq, dq_ptrs[0], uint64_t(q_rows), uint32_t(hq), kHeadDim, kQTile, 32)) return -1;
   if (encode_arena_map(&tm_q, q_arena, uint64_t(q_rows), uint32_t(hq), kHeadDim, kQTile)) return -1;
   if (encode_arena_map(&tm_do, do_arena, uint64_t(q_rows), uint32_t(hq), kHeadDim, kQTile)) return -1;
   if (encode_arena_map(&tm_kv, kv_arena, uint64_t(kv_rows), uint32_t(2 * hkv), kHeadDim, 128)) return -1;
@@ -467,7 +528,7 @@ extern "C" int dcpk_attn_bwd(const void* q_arena, const void* do_arena, long q_r
     g_bwd_attr_set = 1;
   }
   attn_bwd_kernel<<<dim3(hkv, n_ctas), kBwdThreads, smem, static_cast<cudaStream_t>(stream)>>>(
-      tm_q, tm_do, tm_kv, static_cast<const BwdCta*>(ctas), static_cast<const BwdItemDesc*>(items),
+      tm_q, tm_do, tm_kv, tm_dq, static_cast<const BwdCta*>(ctas), static_cast<const BwdItemDesc*>(items),
       static_cast<const int4*>(masks), lse, delta, pp, hq, hkv, stat_stride, scale, status);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }

@@ -47,4 +47,24 @@ inline int encode_arena_map(CUtensorMap* out, const void* base, uint64_t rows, u
   return 0;
 }
 
+// fp32 accumulator arena [rows, heads, 128] addressed as [box_rows x 1 x 32 floats] tiles (no swizzle),
+// the shape the backward kernel's per-warp dQ staging tiles have
+inline int encode_f32_tile_map(CUtensorMap* out, const void* base, uint64_t rows, uint32_t heads, uint32_t d,
+                               uint32_t box_rows, uint32_t box_inner) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return -1;
+  cuuint64_t dims[3] = {d, heads, rows};
+  cuuint64_t strides[2] = {uint64_t(d) * 4, uint64_t(d) * heads * 4};
+  cuuint32_t box[3] = {box_inner, 1, box_rows};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    fprintf(stderr, "dcpk: cuTensorMapEncodeTiled (fp32 tile) failed (%d)\n", int(r));
+    return -2;
+  }
+  return 0;
+}
+
 }  // namespace dcpk

