@@ -63,15 +63,26 @@ class _AttentionFn(torch.autograd.Function):
     """qkv [T, (hq+2hkv)*128] -> attention output [T, hq*128] through the executor's arenas."""
 
     @staticmethod
-    def forward(ctx, qkv, model, cos, sin):
+    def forward(ctx, qkv, model, cos, sin, layer):
         ex = model.executor
         cfg = model.cfg
         model_ops.qkv_rope_split(qkv, cos, sin, ex.q, ex.kv, cfg.n_heads, cfg.n_kv_heads)
         ex.inputs_written()
-        out, lse = ex.forward()
+        stash = model._attn_stash.pop(layer, None) if model._stash_enabled else None
+        if stash is not None:
+            # activation recompute: the attention result of this layer was kept from the first
+            # forward, so only the operands are put back (the backward needs them in the arenas)
+            result, lse_c = stash
+            ex.out_local().copy_(result.view(-1, cfg.n_heads, cfg.head_dim))
+            ex.lse_local().copy_(lse_c)
+        else:
+            out, lse = ex.forward()
+            result = out.reshape(out.shape[0], -1).clone()
+            lse_c = lse.clone()
+            if model._stash_enabled:
+                model._attn_stash[layer] = (result, lse_c)
         ctx.model, ctx.epoch = model, ex.arena_epoch
-        result = out.reshape(out.shape[0], -1).clone()
-        ctx.save_for_backward(qkv, cos, sin, result, lse.clone())
+        ctx.save_for_backward(qkv, cos, sin, result, lse_c)
         return result
 
     @staticmethod
@@ -87,7 +98,7 @@ class _AttentionFn(torch.autograd.Function):
             ex.lse_local().copy_(lse)
         dq, dkv = ex.backward(dout.contiguous().view(-1, cfg.n_heads, cfg.head_dim))
         dqkv = model_ops.qkv_rope_pack_bwd(dq, dkv, cos, sin, qkv.shape[0], cfg.n_heads, cfg.n_kv_heads)
-        return dqkv, None, None, None
+        return dqkv, None, None, None, None
 
 
 class _LMHeadLossFn(torch.autograd.Function):
@@ -127,6 +138,11 @@ class LlamaModel:
         self.recompute = recompute
         self.lm_head_chunk = lm_head_chunk
         self.executor = None
+        # keep each layer's attention output across the checkpoint boundary so the recompute pass
+        # does not run attention (and its communication) a second time
+        self.cache_attention = True
+        self._attn_stash: Dict[int, tuple] = {}
+        self._stash_enabled = False
         shapes: List[Tuple[str, Tuple[int, ...]]] = [("embed", (cfg.vocab, cfg.hidden))]
         for l in range(cfg.n_layers):
             shapes += [(f"l{l}.norm1", (cfg.hidden,)), (f"l{l}.wqkv", (cfg.qkv_dim, cfg.hidden)),
@@ -196,7 +212,7 @@ class LlamaModel:
         p, cfg = self.p, self.cfg
         h = model_ops.rmsnorm(x, p[f"l{l}.norm1"], cfg.eps)
         qkv = F.linear(h, p[f"l{l}.wqkv"])
-        a = _AttentionFn.apply(qkv, self, cos, sin)
+        a = _AttentionFn.apply(qkv, self, cos, sin, l)
         x = x + F.linear(a, p[f"l{l}.wo"])
         h = model_ops.rmsnorm(x, p[f"l{l}.norm2"], cfg.eps)
         gu = F.linear(h, p[f"l{l}.wgu"])
@@ -207,6 +223,8 @@ class LlamaModel:
         """Sum over this rank's tokens of the token losses times ``grad_scale`` (1 / global token
         count); ``labels`` < 0 are ignored.  Call ``.backward()`` on the result."""
         cfg = self.cfg
+        self._attn_stash.clear()
+        self._stash_enabled = self.cache_attention and self.recompute and torch.is_grad_enabled()
         cos, sin = model_ops.rope_tables(positions, cfg.rope_theta, cfg.head_dim)
         x = F.embedding(tokens, self.p["embed"])
         for l in range(cfg.n_layers):

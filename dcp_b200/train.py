@@ -35,7 +35,7 @@ class EngineConfig:
     mask: str = "causal"
     length_dist: synth.LengthDist = None
     n_stages: Optional[int] = None
-    lr: float = 3e-4
+    lr: float = 1e-4
     weight_decay: float = 0.1
     clip_grad: Optional[float] = 1.0
     recompute: bool = True
