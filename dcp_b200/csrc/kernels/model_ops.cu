@@ -14,6 +14,7 @@
 #include <cuda_runtime.h>
 #include <math.h>
 #include <stdint.h>
+#include <stdio.h>
 
 namespace dcpk {
 
@@ -395,5 +396,51 @@ extern "C" int dcpk_adamw(float* master, float* m, float* v, const float* grad, 
   const float bc1 = 1.f - powf(beta1, float(step)), bc2 = 1.f - powf(beta2, float(step));
   adamw_kernel<<<148 * 8, 256, 0, STREAM>>>(master, m, v, grad, static_cast<__nv_bfloat16*>(param_bf16), size_t(n), lr,
                                             beta1, beta2, eps, wd, bc1, bc2, clip_coef);
+  return LAUNCH_OK;
+}
+
+// ------------------------------------------------------------------ allocation-free RMSNorm backward
+// See noalloc.h.  The fp32 weight-gradient accumulator the regular entry point takes from its
+// caller lives here, in a file-scope device array, so callers that must not allocate can still
+// run the backward pass.
+#include "noalloc.h"
+
+static __device__ __align__(256) float g_noalloc_dw_accum[DCPK_NOALLOC_MAX_HIDDEN];
+
+namespace dcpk {
+static constexpr int kNoallocMaxDevices = 64;
+// device address of g_noalloc_dw_accum per device; in host code the array's name is only a
+// handle, the address a kernel can use comes from cudaGetSymbolAddress
+static float* g_noalloc_accum_ptr[kNoallocMaxDevices] = {nullptr};
+
+__global__ void dw_accum_to_bf16_kernel(const float* __restrict__ acc, __nv_bfloat16* __restrict__ dw, int hidden) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < hidden) dw[i] = __float2bfloat16(acc[i]);
+}
+}  // namespace dcpk
+
+extern "C" int dcpk_rmsnorm_bwd_noalloc(const void* x, const void* w, const void* dy, const float* rstd, void* dx,
+                                        void* dw_bf16, int n_rows, int hidden, void* stream) {
+  if (hidden > DCPK_NOALLOC_MAX_HIDDEN || (hidden != 1024 && hidden != 2048 && hidden != 4096 && hidden != 8192)) {
+    fprintf(stderr, "dcpk_rmsnorm_bwd_noalloc: hidden=%d is not supported (1024, 2048, 4096 or 8192, at most %d)\n",
+            hidden, DCPK_NOALLOC_MAX_HIDDEN);
+    return -3;
+  }
+  if (n_rows < 0) return -3;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kNoallocMaxDevices) return -6;
+  if (g_noalloc_accum_ptr[dev] == nullptr) {
+    float* p = nullptr;
+    if (cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_noalloc_dw_accum) != cudaSuccess || p == nullptr) return -6;
+    g_noalloc_accum_ptr[dev] = p;
+  }
+  float* accum = g_noalloc_accum_ptr[dev];
+  // the array keeps what the previous call left: clear the part this call accumulates into
+  if (cudaMemsetAsync(accum, 0, size_t(hidden) * sizeof(float), STREAM) != cudaSuccess) return -6;
+  if (n_rows > 0) {
+    const int rc = dcpk_rmsnorm_bwd(x, w, dy, rstd, dx, accum, n_rows, hidden, stream);
+    if (rc != 0) return rc;
+  }
+  dw_accum_to_bf16_kernel<<<(hidden + 255) / 256, 256, 0, STREAM>>>(accum, static_cast<__nv_bfloat16*>(dw_bf16), hidden);
   return LAUNCH_OK;
 }
