@@ -79,8 +79,8 @@ template <bool kPSmem>
 __global__ void __launch_bounds__(kFwdThreads, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_kv,
                 const AttnTile* __restrict__ tiles, const KvEntry* __restrict__ kv_entries,
-                const int4* __restrict__ masks, PeerPtrs ptrs, int hq, int hkv, int lse_stride,
-                int block_size, float scale, int* __restrict__ status) {
+                const int4* __restrict__ masks, PeerPtrs ptrs, int hq, int hkv, int lse_stride_a,
+                int lse_stride_b, int n_dst_a, int block_size, float scale, int* __restrict__ status) {
   extern __shared__ uint8_t smem_raw[];
   FwdSmem& sm = *reinterpret_cast<FwdSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -314,7 +314,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(ptrs.out[tile.out_dev]) +
                            (size_t(tile.out_row + r) * hq + tile.head) * kHeadDim;
       if (store)
-        ptrs.lse[tile.out_dev][size_t(tile.head) * lse_stride + tile.out_row + r] =
+        ptrs.lse[tile.out_dev][size_t(tile.head) * (tile.out_dev < n_dst_a ? lse_stride_a : lse_stride_b) + tile.out_row + r] =
             l_run > 0.f ? m_run * scale + logf(l_run) : -INFINITY;
       const uint32_t o_addr = tmem + lane_base + 256;
 #pragma unroll
@@ -355,13 +355,14 @@ static int g_fwd_attr_set[2] = {0, 0};
 
 using namespace dcpk;
 
+// Destinations [0, n_dst_a) have LSE row stride lse_stride_a (partial arenas), the rest lse_stride_b.
 // Launches the forward kernel over `n_tiles` tiles.  `variant` 0 keeps P in TMEM (TS
 // UMMA), 1 stages P through shared memory (SS UMMA).  Returns 0 or a negative error.
 extern "C" int dcpk_attn_fwd(const void* q_arena, long q_rows, const void* kv_arena, long kv_rows, int hq,
                              int hkv, const void* tiles, int n_tiles, const void* kv_entries,
                              const void* masks, void* const* out_ptrs, float* const* lse_ptrs, int n_dst,
-                             int lse_stride, int block_size, float scale, int* status, int variant,
-                             void* stream) {
+                             int lse_stride_a, int lse_stride_b, int n_dst_a, int block_size, float scale,
+                             int* status, int variant, void* stream) {
   if (n_tiles <= 0) return 0;
   if (n_dst > kMaxPeers || hq % hkv != 0) return -3;
   CUtensorMap tm_q, tm_kv;
@@ -384,10 +385,10 @@ extern "C" int dcpk_attn_fwd(const void* q_arena, long q_rows, const void* kv_ar
   if (v)
     attn_fwd_kernel<true><<<n_tiles, kFwdThreads, smem, s>>>(
         tm_q, tm_kv, static_cast<const AttnTile*>(tiles), static_cast<const KvEntry*>(kv_entries),
-        static_cast<const int4*>(masks), pp, hq, hkv, lse_stride, block_size, scale, status);
+        static_cast<const int4*>(masks), pp, hq, hkv, lse_stride_a, lse_stride_b, n_dst_a, block_size, scale, status);
   else
     attn_fwd_kernel<false><<<n_tiles, kFwdThreads, smem, s>>>(
         tm_q, tm_kv, static_cast<const AttnTile*>(tiles), static_cast<const KvEntry*>(kv_entries),
-        static_cast<const int4*>(masks), pp, hq, hkv, lse_stride, block_size, scale, status);
+        static_cast<const int4*>(masks), pp, hq, hkv, lse_stride_a, lse_stride_b, n_dst_a, block_size, scale, status);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }

@@ -102,7 +102,8 @@ def _ptr_array(tensors) -> ctypes.Array:
 
 
 def attn_fwd(q_arena: torch.Tensor, kv_arena: torch.Tensor, tables: FwdTables, out_dsts, lse_dsts,
-             scale: float, status: torch.Tensor, variant: int = 0, lse_stride: Optional[int] = None):
+             scale: float, status: torch.Tensor, variant: int = 0, lse_stride: Optional[int] = None,
+             lse_stride_b: Optional[int] = None, n_dst_a: Optional[int] = None):
     """Run the forward kernel.
 
     q_arena: bf16 [rows, hq, 128]; kv_arena: bf16 [rows, 2, hkv, 128]; out_dsts / lse_dsts: lists of
@@ -120,7 +121,9 @@ def attn_fwd(q_arena: torch.Tensor, kv_arena: torch.Tensor, tables: FwdTables, o
         _lib.ptr(q_arena), ctypes.c_long(q_arena.shape[0]), _lib.ptr(kv_arena), ctypes.c_long(kv_arena.shape[0]),
         ctypes.c_int(hq), ctypes.c_int(hkv), _lib.ptr(tables.tiles), ctypes.c_int(tables.n_tiles),
         _lib.ptr(tables.kv_entries), _lib.ptr(tables.masks), _ptr_array(out_dsts), _ptr_array(lse_dsts),
-        ctypes.c_int(len(out_dsts)), ctypes.c_int(lse_stride), ctypes.c_int(tables.block_size),
+        ctypes.c_int(len(out_dsts)), ctypes.c_int(lse_stride),
+        ctypes.c_int(lse_stride if lse_stride_b is None else lse_stride_b),
+        ctypes.c_int(len(out_dsts) if n_dst_a is None else n_dst_a), ctypes.c_int(tables.block_size),
         ctypes.c_float(scale), _lib.ptr(status), ctypes.c_int(variant), _lib.stream_handle())
     _lib.check(rc, "dcpk_attn_fwd")
 

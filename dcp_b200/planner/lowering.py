@@ -51,6 +51,7 @@ class FusedProgram:
     fwd_flops: float = 0.0
     bwd_flops: float = 0.0
     pull_bytes: float = 0.0
+    need_all: Tuple[int, int, int] = (0, 0, 0)   # max over all ranks of (q_rows, kv_rows, part_rows)
 
     def max_rows(self) -> Tuple[int, int, int]:
         return self.q_rows, self.kv_rows, self.part_rows
@@ -143,6 +144,7 @@ def lower_all(context: ExecutionContext, workload: WorkloadSpec, build_backward:
                             layouts[d].n_tokens(BufferType.LOCAL_Q), layouts[d].n_tokens(BufferType.LOCAL_KV),
                             q_next[d], kv_next[d], part_next[d])
         prog.pull_bytes = pull_bytes[d]
+        prog.need_all = (max(q_next.values()), max(kv_next.values()), max(part_next.values()))
         for s in range(n_stages):
             prog.q_pulls.append(_i4(q_pulls[d][s]))
             prog.kv_pulls.append(_i4(kv_pulls[d][s]))

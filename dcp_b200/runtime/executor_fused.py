@@ -36,33 +36,49 @@ class FusedAttentionExecutor:
         self.device = device
         self.scale = softmax_scale if softmax_scale is not None else HEAD_DIM ** -0.5
         self.variant = variant
-        rq, rkv, rp = (-(-int(x) // 128) * 128 + 128 for x in (max_q_rows, max_kv_rows, max_part_rows))
-        rq = rp = max(rq, rp)  # partial and final LSE buffers share one row stride in the kernel
-        self.cap = (rq, rkv, rp)
-        bf, f32 = torch.bfloat16, torch.float32
-        regions = {
-            "q": ((rq, heads_q, HEAD_DIM), bf), "kv": ((rkv, 2, heads_kv, HEAD_DIM), bf),
-            "dout": ((rq, heads_q, HEAD_DIM), bf), "out": ((rq, heads_q, HEAD_DIM), bf),
-            "lse": ((heads_q, rq), f32), "delta": ((heads_q, rq), f32),
-            "part_out": ((rp, heads_q, HEAD_DIM), bf), "part_lse": ((heads_q, rp), f32),
-            "dq": ((rq, heads_q, HEAD_DIM), f32), "dkv": ((rkv, 2, heads_kv, HEAD_DIM), f32),
-        }
-        self.arena = SymmetricArena(regions, device, group, timeout_s)
-        self.world, self.rank = self.arena.world, self.arena.rank
-        for name in regions:
-            setattr(self, name, self.arena.view(name))
+        self.group, self.timeout_s = group, timeout_s
+        self.arena = None
+        self.n_reallocations = 0
+        self._allocate((max_q_rows, max_kv_rows, max_part_rows))
         self.side = torch.cuda.Stream(device=device)
         self.program: Optional[FusedProgram] = None
         self.arena_epoch = 0          # bumped whenever q/kv local regions are rewritten
         self._staging_valid = False   # remote Q/KV rows in staging match the current local data on peers
         self.kernel_launches = 0
 
+    def _allocate(self, rows) -> None:
+        """(Re)create the symmetric arenas for (q rows, kv rows, partial rows).  Collective: every
+        rank of the group must call it with the same sizes (they come from the plan, which is the
+        same on all ranks)."""
+        rq, rkv, rp = (-(-int(x) // 128) * 128 + 128 for x in rows)
+        self.cap = (rq, rkv, rp)
+        hq, hkv = self.hq, self.hkv
+        bf, f32 = torch.bfloat16, torch.float32
+        regions = {
+            "q": ((rq, hq, HEAD_DIM), bf), "kv": ((rkv, 2, hkv, HEAD_DIM), bf),
+            "dout": ((rq, hq, HEAD_DIM), bf), "out": ((rq, hq, HEAD_DIM), bf),
+            "lse": ((hq, rq), f32), "delta": ((hq, rq), f32),
+            "part_out": ((rp, hq, HEAD_DIM), bf), "part_lse": ((hq, rp), f32),
+            "dq": ((rq, hq, HEAD_DIM), f32), "dkv": ((rkv, 2, hkv, HEAD_DIM), f32),
+        }
+        if self.arena is not None:
+            torch.cuda.synchronize(self.device)
+            for name in regions:
+                delattr(self, name)
+            self.arena = None
+            self.n_reallocations += 1
+        self.arena = SymmetricArena(regions, self.device, self.group, self.timeout_s)
+        self.world, self.rank = self.arena.world, self.arena.rank
+        for name in regions:
+            setattr(self, name, self.arena.view(name))
+
     # ---- program upload
     def prepare(self, program: FusedProgram) -> None:
         assert program.heads_q == self.hq and program.heads_kv == self.hkv
-        need = program.max_rows()
+        need = tuple(max(a, b) for a, b in zip(program.need_all, program.max_rows()))
         if any(n > c for n, c in zip(need, self.cap)):
-            raise RuntimeError(f"program needs rows {need} but the arenas hold {self.cap}")
+            # grow with headroom; all ranks see the same need_all, so all of them get here together
+            self._allocate(tuple(max(int(n * 1.25), c) for n, c in zip(need, self.cap)))
         dev = self.device
         up = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(dev, non_blocking=True)
         self.program = program
@@ -137,8 +153,9 @@ class FusedAttentionExecutor:
         return self.out_local(), self.lse_local()
 
     def _launch_fwd(self, t, out_dsts, lse_dsts) -> None:
+        # destinations 0..world-1 are partial arenas (row stride cap[2]), the rest final buffers (cap[0])
         attn_ops.attn_fwd(self.q, self.kv, t, out_dsts, lse_dsts, self.scale, a_status(self), self.variant,
-                          lse_stride=self.cap[0])
+                          lse_stride=self.cap[2], lse_stride_b=self.cap[0], n_dst_a=self.world)
         self.kernel_launches += 1
 
     # ---- backward

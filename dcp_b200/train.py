@@ -72,7 +72,7 @@ class TrainEngine:
                                       group=world_group)
         group_tokens = cfg.tokens_per_step // (self.world // dcp)
         cap = int(group_tokens * 1.3) + 4 * cfg.block_size
-        self.executor = FusedAttentionExecutor(m.n_heads, m.n_kv_heads, cap, cap, cap, device,
+        self.executor = FusedAttentionExecutor(m.n_heads, m.n_kv_heads, cap, cap, 2 * cap, device,
                                                self.dcp_group if dcp > 1 else None)
         self.model.set_executor(self.executor)
         self.spec = PlanSpec(self.world, dcp, cfg.tokens_per_step, m.n_heads, m.n_kv_heads, m.head_dim, cfg.block_size,
