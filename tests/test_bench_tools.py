@@ -1,0 +1,52 @@
+"""Benchmark tooling that needs no GPU: preprocessing, log parsing, grid runner watchdog, replay."""
+import json
+import os
+import pickle
+import sys
+
+from dcp_b200.bench import parse_logs, preprocessing
+from dcp_b200.bench.run_experiments import run_cell
+
+
+def test_preprocessing_scales_and_packs(tmp_path):
+    assert preprocessing.scale_lengths([100, 100000, 10], 2.0, 131072) == [200, 131072, 20]
+    b = preprocessing.pack_batches([60000, 50000, 40000, 200000, 10], 131072)
+    assert b == [[60000, 50000], [40000], [131072], [10]] and preprocessing.max_dp_degree(b) == 1
+    out = tmp_path / "b.json"
+    preprocessing.main(["--synthetic", "lognormal8k", "--n", "200", "--out", str(out)])
+    d = json.load(open(out))
+    assert all(sum(x) <= 131072 for x in d["batches"]) and d["max_dp_degree"] >= 1
+
+
+def test_log_parsers():
+    text = "\n".join(f" iteration {i} | elapsed time per iteration (ms): {100 + i}.0 | Training loss: {5 - 0.1 * i:.3f}"
+                     for i in range(6)) + "\nDCP: total time 40.0 ms\nUlysses: total time 60.0 ms\n"
+    assert parse_logs.parse_iteration_times(text) == (102 + 103 + 104 + 105) / 4
+    assert parse_logs.parse_loss_curve(text)[:2] == [5.0, 4.9]
+    assert parse_logs.parse_microbenchmark(text, 4) == {"DCP": 10.0, "Ulysses": 15.0}
+    assert parse_logs.losses_overlap([5.0, 4.9], [5.01, 4.88]) and not parse_logs.losses_overlap([5.0], [6.0])
+
+
+def test_grid_runner_detects_failure_and_stall(tmp_path):
+    ok = run_cell([sys.executable, "-c", "print('fine')"], str(tmp_path / "a.log"))
+    bad = run_cell([sys.executable, "-c", "raise SystemExit(3)"], str(tmp_path / "b.log"))
+    stalled = run_cell([sys.executable, "-c", "import time; print('x', flush=True); time.sleep(60)"],
+                       str(tmp_path / "c.log"), no_progress_s=3.0)
+    assert (ok, bad, stalled) == ("ok", "failed", "stalled")
+
+
+def test_replay_of_saved_plans(tmp_path):
+    import torch
+    from dcp_b200.bench.replay import replay_plans
+    from dcp_b200.core.common import get_default_execution_context
+    from dcp_b200.planner.compiler import InstrCompiler
+    from dcp_b200.planner.workload import generate_workload, pad_seqlens
+    ctx = get_default_execution_context(2, 1)
+    raw = [400, 250]
+    pad = pad_seqlens(raw, 64)
+    wl = generate_workload((sum(pad), 4, 16), (sum(pad), 2, 2, 16), raw, pad, 64, 4, ctx.comp_cost_model)
+    res = InstrCompiler(ctx).compile(wl)
+    p = tmp_path / "plans.pkl"
+    pickle.dump(res, open(p, "wb"))
+    rep = replay_plans(str(p))
+    assert rep["forward"]["attn_units"] == len(res[0].workloads) == rep["backward"]["attn_units"]
