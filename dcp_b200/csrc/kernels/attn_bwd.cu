@@ -29,7 +29,7 @@
 
 namespace dcpk {
 
-static constexpr int kBwdThreads = 192;
+static constexpr int kBwdThreads = 320;  // 8 gradient warps + TMA producer + UMMA issuer
 static constexpr int kQTile = 64;
 static constexpr int kKvHalf = 128 * 64 * 2;  // [128 x 64] bf16 half tile, 16 KB
 static constexpr int kQHalf = 64 * 64 * 2;    // [64 x 64] bf16 half tile, 8 KB
@@ -78,14 +78,15 @@ struct __align__(1024) BwdSmem {
   uint8_t q[2][2 * kQHalf];
   uint8_t dout[2][2 * kQHalf];
   uint8_t ds[kKvHalf];     // dS^T: [128 keys x 64 queries]
+  uint8_t p[kKvHalf];      // P^T:  [128 keys x 64 queries]
   // dQ staging, one private [64 queries x 32 channels] fp32 tile per gradient warp; drained to the
   // fp32 accumulator with bulk reduce-add copies (L2 handles those a line at a time, scalar
   // red.add is limited to one element per L2 slice per clock)
-  float dq_stage[4][kQTile * 32];
+  float dq_stage[8][32 * 32];
   // per-warp private copies: the four gradient warps never synchronise with each other
-  float lse2[4][kQTile];
-  float delta[4][kQTile];
-  int4 rng[4][kQTile];
+  float lse2[8][32];
+  float delta[8][32];
+  int4 rng[8][32];
   uint64_t kv_full, qdo_full[2], qdo_empty[2], sdp_full, s_free, p_ready, dq_full;
   uint32_t tmem_base;
   int abort_word;
@@ -123,7 +124,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   const BwdItemDesc* my_items = items + cta.item_off;
   const int n_items = cta.n_items * group;  // visits
 
-  if (threadIdx.x == 128) {
+  if (threadIdx.x == 256) {
     tma_prefetch_desc(&tm_q);
     tma_prefetch_desc(&tm_do);
     tma_prefetch_desc(&tm_kv);
@@ -131,13 +132,13 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     mbar_init(&sm.kv_full, 1);
     for (int i = 0; i < 2; ++i) { mbar_init(&sm.qdo_full[i], 1); mbar_init(&sm.qdo_empty[i], 1); }
     mbar_init(&sm.sdp_full, 1);
-    mbar_init(&sm.s_free, 128);
-    mbar_init(&sm.p_ready, 128);
+    mbar_init(&sm.s_free, 256);
+    mbar_init(&sm.p_ready, 256);
     mbar_init(&sm.dq_full, 1);
     sm.abort_word = 0;
     mbar_fence_init();
   }
-  if (warp == 5) {
+  if (warp == 9) {
     tmem_alloc(&sm.tmem_base, 512);
     tmem_relinquish();
   }
@@ -146,11 +147,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   tc_fence_after();
   const uint32_t tmem = sm.tmem_base;
   volatile int* abort_word = &sm.abort_word;
-  constexpr uint32_t cS = 0, cdP = 64, cP = 128, cdS = 160, cdQ = 192, cdK = 256, cdV = 384;
+  constexpr uint32_t cS = 0, cdP = 64, cdQ = 128 /* two 64-column buffers */, cdK = 256, cdV = 384;
 
-  long long* tl = (blockIdx.x == 0 && blockIdx.y == 0 && (warp == 0 || warp == 5)) ? g_bwd_timeline : nullptr;
+  long long* tl = (blockIdx.x == 0 && blockIdx.y == 0 && (warp == 0 || warp == 9)) ? g_bwd_timeline : nullptr;
   long long tl_t = clock64();
-  if (warp == 4) {
+  if (warp == 8) {
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
       mbar_expect_tx(&sm.kv_full, 4 * kKvHalf);
@@ -178,12 +179,12 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             for (int spin = 0; spin < 200000 && !mbar_try_wait(&sm.qdo_full[st], pending[st]); ++spin) {}
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == 9) {
     // ------------------------------------------------------------ UMMA issuer
     constexpr uint32_t idesc_sdp = make_idesc_bf16(128, 64, 0, 0);
     constexpr uint32_t idesc_acc = make_idesc_bf16(128, 128, 0, 1);
     constexpr uint32_t idesc_dq = make_idesc_bf16(128, 64, 1, 1);
-    const uint32_t k_addr = smem_u32(sm.k), v_addr = smem_u32(sm.v), ds_addr = smem_u32(sm.ds);
+    const uint32_t k_addr = smem_u32(sm.k), v_addr = smem_u32(sm.v), ds_addr = smem_u32(sm.ds), p_addr = smem_u32(sm.p);
     bool ok = mbar_wait(&sm.kv_full, 0, abort_word);
     auto issue_acc = [&](int t) -> bool {
       const int st = t & 1;
@@ -194,20 +195,22 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       if (lane == 0) {
         const uint32_t q_addr = smem_u32(sm.q[st]), do_addr = smem_u32(sm.dout[st]);
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {  // 16 queries per step
+        for (int k = 0; k < 4; ++k) {  // 16 queries per step; A = P^T tile, K-major (queries contiguous)
+          uint64_t a_p = make_sdesc_sw128(p_addr + k * 32, 16, 1024);
           uint64_t b_do = make_sdesc_sw128(do_addr + k * 2048, kQHalf, 1024);
-          umma_ts(tmem + cdV, tmem + cP + k * 8, b_do, idesc_acc, (t > 0 || k > 0) ? 1u : 0u);
+          umma_ss(tmem + cdV, a_p, b_do, idesc_acc, (t > 0 || k > 0) ? 1u : 0u);
         }
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
+          uint64_t a_ds = make_sdesc_sw128(ds_addr + k * 32, 16, 1024);
           uint64_t b_q = make_sdesc_sw128(q_addr + k * 2048, kQHalf, 1024);
-          umma_ts(tmem + cdK, tmem + cdS + k * 8, b_q, idesc_acc, (t > 0 || k > 0) ? 1u : 0u);
+          umma_ss(tmem + cdK, a_ds, b_q, idesc_acc, (t > 0 || k > 0) ? 1u : 0u);
         }
 #pragma unroll
-        for (int k = 0; k < 8; ++k) {  // 16 keys per step
+        for (int k = 0; k < 8; ++k) {  // 16 keys per step; same dS^T bytes read as the MN-major B operand
           uint64_t a_kt = make_sdesc_sw128(k_addr + k * 2048, kKvHalf, 1024);
           uint64_t b_ds = make_sdesc_sw128(ds_addr + k * 2048, 16, 1024);
-          umma_ss(tmem + cdQ, a_kt, b_ds, idesc_dq, k > 0 ? 1u : 0u);
+          umma_ss(tmem + cdQ + (t & 1) * 64, a_kt, b_ds, idesc_dq, k > 0 ? 1u : 0u);
         }
         umma_commit(&sm.dq_full);
         umma_commit(&sm.qdo_empty[st]);
@@ -246,67 +249,58 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     if (ok && n_items > 0) mbar_wait(&sm.dq_full, (n_items - 1) & 1, abort_word);
   } else {
     // ------------------------------------------------------------ softmax-gradient threads
-    const int r = threadIdx.x;  // key row inside the tile == TMEM lane
-    const uint32_t lane_base = uint32_t(warp * 32) << 16;
+    // 8 warps: warp w works on TMEM lanes 32*(w&3).. (key rows) and on query columns 32*(w>>2)..+31
+    const int quad = warp & 3, hf = warp >> 2;
+    const int r = quad * 32 + lane;  // key row inside the tile == TMEM lane
+    const uint32_t lane_base = uint32_t(quad * 32) << 16;
     const float sl2 = scale * 1.4426950408889634f;
     const bool key_valid = r < cta.n_valid;
     bool ok = true;
     BwdItem prev{};
-    // adds dQ^T of the previous item (lane = d, column = query) into its fp32 accumulator:
-    // transpose through this warp's staging tile, then one 128-byte bulk reduce per query row
-    auto flush_dq = [&](const BwdItem& itx) {
+    // adds this warp's [32 d x 32 q] part of dQ^T of the previous item into the fp32 accumulator:
+    // transpose through the warp's staging tile, then one TMA reduce-add of the [32 q x 32 d] tile
+    auto flush_dq = [&](const BwdItem& itx, int buf) {
       if (itx.dq_dev < 0) return;  // dQ not wanted (used to measure the cost of the drain)
       float* stage = sm.dq_stage[warp];
       asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");  // earlier drains have left smem
       __syncwarp();
+      uint32_t reg[32];
+      tmem_ld32(tmem + lane_base + cdQ + buf * 64 + hf * 32, reg);
+      tmem_wait_ld();
 #pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        uint32_t reg[32];
-        tmem_ld32(tmem + lane_base + cdQ + c * 32, reg);
-        tmem_wait_ld();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) stage[(c * 32 + i) * 32 + lane] = __uint_as_float(reg[i]);
-      }
+      for (int i = 0; i < 32; ++i) stage[i * 32 + lane] = __uint_as_float(reg[i]);
       fence_proxy_async_smem();
       __syncwarp();
       if (itx.dq_dev == 0) {
-        // local accumulator: one tiled TMA reduce-add drains the whole [64 x 32] tile.  Rows past
-        // n_rows hold exact zeros (their probabilities are masked to 0), so adding them is harmless.
+        // rows past n_rows hold exact zeros (their probabilities are masked to 0): adding them is harmless
         if (lane == 0) {
           asm volatile(
               "cp.reduce.async.bulk.tensor.3d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3, %4}], [%1];"
-              ::"l"(reinterpret_cast<uint64_t>(&tm_dq)), "r"(smem_u32(stage)), "r"(warp * 32), "r"(itx.head),
-              "r"(itx.dq_row)
+              ::"l"(reinterpret_cast<uint64_t>(&tm_dq)), "r"(smem_u32(stage)), "r"(quad * 32), "r"(itx.head),
+              "r"(itx.dq_row + hf * 32)
               : "memory");
         }
       } else {
-        float* dq = ptrs.dq[itx.dq_dev] + (size_t(itx.dq_row) * hq + itx.head) * kHeadDim + warp * 32;
-        const size_t row_stride = size_t(hq) * kHeadDim;
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          const int qi = lane + 32 * h;
-          if (qi < itx.n_rows) {
-            asm volatile("cp.reduce.async.bulk.global.shared::cta.bulk_group.add.f32 [%0], [%1], %2;"
-                         ::"l"(dq + qi * row_stride), "r"(smem_u32(stage + qi * 32)), "r"(128)
-                         : "memory");
-          }
+        const int qi = hf * 32 + lane;
+        if (qi < itx.n_rows) {
+          float* dq = ptrs.dq[itx.dq_dev] + (size_t(itx.dq_row + qi) * hq + itx.head) * kHeadDim + quad * 32;
+          asm volatile("cp.reduce.async.bulk.global.shared::cta.bulk_group.add.f32 [%0], [%1], %2;"
+                       ::"l"(dq), "r"(smem_u32(stage + lane * 32)), "r"(128)
+                       : "memory");
         }
       }
       asm volatile("cp.async.bulk.commit_group;" ::: "memory");
     };
     // the descriptor and per-query statistics of item t+1 are fetched while item t is processed, so
     // their global-memory latency never sits on the critical path
-    struct Stats { float l[2], d[2]; int4 m[2]; };
+    struct Stats { float l, d; int4 m; };
     auto fetch_stats = [&](const BwdItem& it, Stats& st) {
-#pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        const int qi = lane + 32 * h;
-        const bool qv = qi < it.n_rows;
-        st.l[h] = qv ? lse[size_t(it.head) * stat_stride + it.q_row + qi] : INFINITY;
-        st.d[h] = qv ? delta[size_t(it.head) * stat_stride + it.q_row + qi] : 0.f;
-        st.m[h] = make_int4(0, 0, 0, 0);
-        if (qv && !it.full) st.m[h] = masks[it.mask_row + qi];
-      }
+      const int qi = hf * 32 + lane;
+      const bool qv = qi < it.n_rows;
+      st.l = qv ? lse[size_t(it.head) * stat_stride + it.q_row + qi] : INFINITY;
+      st.d = qv ? delta[size_t(it.head) * stat_stride + it.q_row + qi] : 0.f;
+      st.m = make_int4(0, 0, 0, 0);
+      if (qv && !it.full) st.m = masks[it.mask_row + qi];
     };
     BwdItem nxt{};
     Stats nst{};
@@ -317,14 +311,12 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     for (int t = 0; t < n_items && ok; ++t) {
       const BwdItem itx = nxt;
       __syncwarp();
-#pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        const int qi = lane + 32 * h;
-        sm.lse2[warp][qi] = (nst.l[h] == -INFINITY) ? INFINITY : nst.l[h] * 1.4426950408889634f;
-        sm.delta[warp][qi] = nst.d[h];
-        int4 m = nst.m[h];
+      {
+        sm.lse2[warp][lane] = (nst.l == -INFINITY) ? INFINITY : nst.l * 1.4426950408889634f;
+        sm.delta[warp][lane] = nst.d;
+        int4 m = nst.m;
         m.y = max(m.y, m.x); m.w = max(m.w, m.z);
-        sm.rng[warp][qi] = m;
+        sm.rng[warp][lane] = m;
       }
       __syncwarp();
       if (t + 1 < n_items) {
@@ -337,40 +329,29 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       if (!ok) break;
       TL_ADD(1, tl_t);
       tc_fence_after();
-      uint32_t sreg[64], dreg[64];
-      tmem_ld32(tmem + lane_base + cS, sreg);
-      tmem_ld32(tmem + lane_base + cS + 32, sreg + 32);
-      tmem_ld32(tmem + lane_base + cdP, dreg);
-      tmem_ld32(tmem + lane_base + cdP + 32, dreg + 32);
+      uint32_t sreg[32], dreg[32];
+      tmem_ld32(tmem + lane_base + cS + hf * 32, sreg);
+      tmem_ld32(tmem + lane_base + cdP + hf * 32, dreg);
       tmem_wait_ld();
       tc_fence_before();
       mbar_arrive(&sm.s_free);
       TL_ADD(2, tl_t);
-      if (t > 0) {
-        ok = mbar_wait(&sm.dq_full, (t - 1) & 1, abort_word);
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) break;
-        TL_ADD(3, tl_t);
-        tc_fence_after();
-        flush_dq(prev);
-        TL_ADD(4, tl_t);
-      }
       const int kpos = itx.kv_pos0 + r;
-      uint32_t preg[32], dsreg[32];
+      const int n_rows_h = itx.n_rows - hf * 32;  // valid queries inside this warp's column half
+      uint32_t preg[16], dsreg[16];
       // The tile-level "no masking needed" switch is taken once, outside the element loop: with a
       // branch per element every element becomes its own basic block and the compiler cannot
-      // interleave the independent exp / multiply chains (one warp per scheduler has nothing else
-      // to hide their latency with).
+      // interleave the independent exp / multiply chains.
       const float* lse2_w = sm.lse2[warp];
       const float* delta_w = sm.delta[warp];
       if (itx.full) {
 #pragma unroll
-        for (int c = 0; c < 32; ++c) {
+        for (int c = 0; c < 16; ++c) {
           float pv[2], dv[2];
 #pragma unroll
           for (int h = 0; h < 2; ++h) {
             const int qi = 2 * c + h;
-            const bool allow = key_valid && (qi < itx.n_rows);
+            const bool allow = key_valid && (qi < n_rows_h);
             const float e = fast_exp2(fmaf(__uint_as_float(sreg[qi]), sl2, -lse2_w[qi]));
             pv[h] = allow ? e : 0.f;
             dv[h] = pv[h] * (__uint_as_float(dreg[qi]) - delta_w[qi]) * scale;
@@ -381,7 +362,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       } else {
         const int4* rng_w = sm.rng[warp];
 #pragma unroll
-        for (int c = 0; c < 32; ++c) {
+        for (int c = 0; c < 16; ++c) {
           float pv[2], dv[2];
 #pragma unroll
           for (int h = 0; h < 2; ++h) {
@@ -398,18 +379,29 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         }
       }
       TL_ADD(5, tl_t);
-      tmem_st32(tmem + lane_base + cP, preg);
-      tmem_st32(tmem + lane_base + cdS, dsreg);
+      if (t > 0) {
+        // the accumulating UMMAs of the previous item must have finished reading the P^T / dS^T tiles
+        ok = mbar_wait(&sm.dq_full, (t - 1) & 1, abort_word);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tc_fence_after();
+      }
+      TL_ADD(3, tl_t);
 #pragma unroll
-      for (int ch = 0; ch < 8; ++ch) {
-        uint4 val = make_uint4(dsreg[4 * ch], dsreg[4 * ch + 1], dsreg[4 * ch + 2], dsreg[4 * ch + 3]);
-        *reinterpret_cast<uint4*>(sm.ds + r * 128 + ((ch ^ (r & 7)) << 4)) = val;
+      for (int i = 0; i < 4; ++i) {
+        const int ch = hf * 4 + i;
+        const uint32_t off = r * 128 + ((ch ^ (r & 7)) << 4);
+        *reinterpret_cast<uint4*>(sm.p + off) = make_uint4(preg[4 * i], preg[4 * i + 1], preg[4 * i + 2], preg[4 * i + 3]);
+        *reinterpret_cast<uint4*>(sm.ds + off) = make_uint4(dsreg[4 * i], dsreg[4 * i + 1], dsreg[4 * i + 2], dsreg[4 * i + 3]);
       }
       fence_proxy_async_smem();
-      tmem_wait_st();
       tc_fence_before();
       mbar_arrive(&sm.p_ready);
       TL_ADD(6, tl_t);
+      // dQ^T of the previous item sits in the other TMEM buffer: drain it while the tensor core
+      // already accumulates this item
+      if (t > 0) flush_dq(prev, (t - 1) & 1);
+      TL_ADD(4, tl_t);
       prev = itx;
     }
     ok = __all_sync(0xffffffffu, ok);
@@ -418,15 +410,14 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       ok = __all_sync(0xffffffffu, ok);
       if (ok) {
         tc_fence_after();
-        flush_dq(prev);
-        asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
-        // dK / dV: lane = key row, 128 fp32 columns each
-        float* dk = ptrs.dkv[cta.dkv_dev] + ((size_t(cta.dkv_row + r) * 2 + 0) * hkv + kv_head) * kHeadDim;
-        float* dv = ptrs.dkv[cta.dkv_dev] + ((size_t(cta.dkv_row + r) * 2 + 1) * hkv + kv_head) * kHeadDim;
+        flush_dq(prev, (n_items - 1) & 1);
+        // dK / dV: lane = key row; this warp adds channels 64*hf .. 64*hf+63 of both
+        float* dk = ptrs.dkv[cta.dkv_dev] + ((size_t(cta.dkv_row + r) * 2 + 0) * hkv + kv_head) * kHeadDim + hf * 64;
+        float* dv = ptrs.dkv[cta.dkv_dev] + ((size_t(cta.dkv_row + r) * 2 + 1) * hkv + kv_head) * kHeadDim + hf * 64;
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
+        for (int c = 0; c < 2; ++c) {
           uint32_t reg[32];
-          tmem_ld32(tmem + lane_base + cdK + c * 32, reg);
+          tmem_ld32(tmem + lane_base + cdK + hf * 64 + c * 32, reg);
           tmem_wait_ld();
           if (key_valid) {
 #pragma unroll
@@ -434,7 +425,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
               red_add_v4(dk + c * 32 + 4 * i, __uint_as_float(reg[4 * i]), __uint_as_float(reg[4 * i + 1]),
                          __uint_as_float(reg[4 * i + 2]), __uint_as_float(reg[4 * i + 3]));
           }
-          tmem_ld32(tmem + lane_base + cdV + c * 32, reg);
+          tmem_ld32(tmem + lane_base + cdV + hf * 64 + c * 32, reg);
           tmem_wait_ld();
           if (key_valid) {
 #pragma unroll
@@ -450,7 +441,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 5) {
+  if (warp == 9) {
     tc_fence_after();
     tmem_dealloc(tmem, 512);
   }
@@ -512,7 +503,7 @@ extern "C" int dcpk_attn_bwd(const void* q_arena, const void* do_arena, long q_r
   if (n_ctas <= 0) return 0;
   if (n_dst > kMaxPeers || hq % hkv != 0) return -3;
   CUtensorMap tm_q, tm_do, tm_kv, tm_dq;
-  if (encode_f32_tile_map(&tm_dq, dq_ptrs[0], uint64_t(q_rows), uint32_t(hq), kHeadDim, kQTile, 32)) return -1;
+  if (encode_f32_tile_map(&tm_dq, dq_ptrs[0], uint64_t(q_rows), uint32_t(hq), kHeadDim, 32, 32)) return -1;
   if (encode_arena_map(&tm_q, q_arena, uint64_t(q_rows), uint32_t(hq), kHeadDim, kQTile)) return -1;
   if (encode_arena_map(&tm_do, do_arena, uint64_t(q_rows), uint32_t(hq), kHeadDim, kQTile)) return -1;
   if (encode_arena_map(&tm_kv, kv_arena, uint64_t(kv_rows), uint32_t(2 * hkv), kHeadDim, 128)) return -1;
