@@ -85,6 +85,16 @@ def bench_attention(kind, args):
     if kind == "attn_fwd":
         ms = time_fn(fwd, args.iters, 3, flush)
         flops = ft.flops
+        if args.timeline:
+            from ..ops import _lib
+            tl = torch.zeros(16, dtype=torch.int64, device=dev)
+            _lib.load().dcpk_attn_fwd_set_timeline(_lib.ptr(tl))
+            fwd()
+            torch.cuda.synchronize()
+            _lib.load().dcpk_attn_fwd_set_timeline(None)
+            names = ["loop top", "wait S", "ld S", "max/exp/pack", "store P + wait O(j-1)", "rescale O + arrive", "probe: empty", "probe: try_wait on a completed barrier",
+                     "umma: after QK issue", "umma: wait P", "umma: wait V", "umma: issue PV", "umma: wait K"]
+            print("timeline of CTA 0 (total cycles):", {n: v for n, v in zip(names, tl.tolist()) if n != "-"})
     else:
         fwd()
         dout = torch.randn_like(q)

@@ -1,21 +1,22 @@
 // Blockwise range-masked attention backward for sm_100a.
 //
-// One CTA owns one 128-row KV tile of one KV head and walks a host-built list of
-// (64-query tile, query head) items that attend to it.  Everything is computed in the
-// transposed orientation so that the probability and score-gradient tiles land in TMEM
-// with lane = key row, ready to be the A operand of the accumulating UMMAs:
-//   S^T  = K  Q^T          (SS, M=128 keys, N=64 queries, K=d)
-//   dP^T = V  dO^T         (SS)
-//   P^T  = exp2(S^T*c - lse),  dS^T = P^T o (dP^T - delta) * scale      (threads, TMEM)
-//   dV  += P^T  dO         (TS, M=128, N=d, K=64 queries)
-//   dK  += dS^T Q          (TS)
-//   dQ^T = K^T dS^T        (SS, M=d, N=64 queries, K=128 keys; dS^T staged in smem)
-// dQ^T is read back with lane = d, so each warp adds 128 contiguous bytes per query row
-// with red.global.add.f32 into the fp32 dQ accumulator of the destination (which may be
-// a peer GPU's memory).  dK/dV stay in TMEM for the CTA's lifetime and are added once,
-// at the end, into the fp32 dKV accumulator of their owner.
-// TMEM columns: S^T [0,64) dP^T [64,128) P^T [128,160) dS^T [160,192) dQ^T [192,256)
-//               dK [256,384) dV [384,512).
+// One CTA owns one 128-row KV tile of one KV head and walks a host-built list of 64-query
+// tiles that attend to it, once per query head of the GQA group.  Everything is computed in
+// the transposed orientation (lane = key row):
+//   S^T  = K  Q^T          (SS UMMA, M=128 keys, N=64 queries, K=d)        -> TMEM
+//   dP^T = V  dO^T         (SS)                                             -> TMEM
+//   P^T  = exp2(S^T*c - lse),  dS^T = P^T o (dP^T - delta) * scale          (8 gradient warps)
+//   P^T and dS^T are written as bf16 into two swizzled smem tiles, then
+//   dV  += P^T  dO         (SS, A = P^T tile K-major, B = dO MN-major, accumulates in TMEM)
+//   dK  += dS^T Q          (SS)
+//   dQ^T = K^T dS^T        (SS, A = K MN-major, B = the same dS^T bytes MN-major)
+// The Q/dO stage is handed back to the TMA producer after dV and dK are issued, so the load of
+// the next-but-one item overlaps dQ^T.  dQ^T alternates between two TMEM buffers; while the
+// tensor core works on item t the gradient warps transpose dQ^T(t-1) through a per-warp
+// [32 q x 32 d] fp32 staging tile and add it to the accumulator with one tiled TMA reduce-add
+// (local accumulator) or one 128-byte bulk reduce per query row (peer accumulator).  dK/dV stay
+// in TMEM for the CTA's lifetime and are added once with red.global.add.v4.f32.
+// TMEM columns: S^T [0,64) dP^T [64,128) dQ^T [128,192) [192,256) dK [256,384) dV [384,512).
 //
 // Reference behaviour covered: the varlen backward the executor calls at
 // dcp/runtime/flash_attention/executor.py:1058-1115, plus the blockwise partial sums
@@ -93,11 +94,13 @@ struct __align__(1024) BwdSmem {
 };
 
 // Optional per-phase cycle counters of CTA (0,0) (set with dcpk_attn_bwd_set_timeline; null = off).
-// Layout: [phase][sum of cycles]; phases 0-7 gradient warp 0, 8-11 UMMA warp.
+// Layout: [phase][sum of cycles]; phases 0-7 gradient warp 0, 8-11 UMMA warp.  The counters live in
+// a separately instantiated kernel (kTL) so the production kernel carries no probe branches; each
+// phase includes the cost of one probe (about 110 cycles).
 __device__ long long* g_bwd_timeline = nullptr;
 #define TL_ADD(idx, t_prev)                                                        \
   do {                                                                             \
-    if (tl) { long long now_ = clock64(); if (lane == 0) tl[idx] += now_ - (t_prev); (t_prev) = now_; } \
+    if constexpr (kTL) if (tl) { long long now_ = clock64(); if (lane == 0) atomicAdd(reinterpret_cast<unsigned long long*>(tl + (idx)), (unsigned long long)(now_ - (t_prev))); (t_prev) = now_; } \
   } while (0)
 
 __device__ __forceinline__ void red_add_f32(float* p, float v) {
@@ -108,6 +111,7 @@ __device__ __forceinline__ void red_add_v4(float* p, float a, float b, float c, 
                : "memory");
 }
 
+template <bool kTL>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
                 const __grid_constant__ CUtensorMap tm_kv, const __grid_constant__ CUtensorMap tm_dq,
@@ -149,8 +153,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   volatile int* abort_word = &sm.abort_word;
   constexpr uint32_t cS = 0, cdP = 64, cdQ = 128 /* two 64-column buffers */, cdK = 256, cdV = 384;
 
-  long long* tl = (blockIdx.x == 0 && blockIdx.y == 0 && (warp == 0 || warp == 9)) ? g_bwd_timeline : nullptr;
-  long long tl_t = clock64();
+  long long* tl = (kTL && blockIdx.x == 0 && blockIdx.y == 0 && (warp == 0 || warp == 9)) ? g_bwd_timeline : nullptr;
+  long long tl_t = kTL ? clock64() : 0;
   if (warp == 8) {
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
@@ -206,6 +210,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           uint64_t b_q = make_sdesc_sw128(q_addr + k * 2048, kQHalf, 1024);
           umma_ss(tmem + cdK, a_ds, b_q, idesc_acc, (t > 0 || k > 0) ? 1u : 0u);
         }
+        // Q and dO are not read after this point: hand the stage back to the producer now, so the
+        // next-but-one item loads while dQ^T is still being computed
+        umma_commit(&sm.qdo_empty[st]);
 #pragma unroll
         for (int k = 0; k < 8; ++k) {  // 16 keys per step; same dS^T bytes read as the MN-major B operand
           uint64_t a_kt = make_sdesc_sw128(k_addr + k * 2048, kKvHalf, 1024);
@@ -213,7 +220,6 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           umma_ss(tmem + cdQ + (t & 1) * 64, a_kt, b_ds, idesc_dq, k > 0 ? 1u : 0u);
         }
         umma_commit(&sm.dq_full);
-        umma_commit(&sm.qdo_empty[st]);
       }
       __syncwarp();
       TL_ADD(10, tl_t);
@@ -302,11 +308,14 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       st.m = make_int4(0, 0, 0, 0);
       if (qv && !it.full) st.m = masks[it.mask_row + qi];
     };
-    BwdItem nxt{};
+    // descriptors run two items ahead of the math and statistics one ahead, so neither the
+    // descriptor load nor the loads that depend on it are waited for
+    BwdItem nxt{}, nxt2{};
     Stats nst{};
     if (n_items > 0) {
       nxt = load_item(my_items, 0, group, kv_head);
       fetch_stats(nxt, nst);
+      if (n_items > 1) nxt2 = load_item(my_items, 1, group, kv_head);
     }
     for (int t = 0; t < n_items && ok; ++t) {
       const BwdItem itx = nxt;
@@ -320,8 +329,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       }
       __syncwarp();
       if (t + 1 < n_items) {
-        nxt = load_item(my_items, t + 1, group, kv_head);
+        nxt = nxt2;
         fetch_stats(nxt, nst);
+        if (t + 2 < n_items) nxt2 = load_item(my_items, t + 2, group, kv_head);
       }
       TL_ADD(0, tl_t);
       ok = mbar_wait(&sm.sdp_full, t & 1, abort_word);
@@ -470,7 +480,8 @@ __global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ o, const __n
   if (lane == 0) delta[size_t(h) * stat_stride + row0 + row] = acc;
 }
 
-static int g_bwd_attr_set = 0;
+static int g_bwd_attr_set[2] = {0, 0};
+static long long* g_bwd_timeline_host = nullptr;  // non-null selects the instrumented build of the kernel
 
 }  // namespace dcpk
 
@@ -491,6 +502,7 @@ extern "C" int dcpk_attn_delta(const void* o, const void* d_o, float* delta, int
 // Points the kernel's cycle-counter timeline at `buf` (>= 16 int64, device memory) or disables it (null).
 extern "C" int dcpk_attn_bwd_set_timeline(void* buf) {
   long long* p = static_cast<long long*>(buf);
+  g_bwd_timeline_host = p;
   return cudaMemcpyToSymbol(g_bwd_timeline, &p, sizeof(p)) == cudaSuccess ? 0 : -5;
 }
 
@@ -513,12 +525,13 @@ extern "C" int dcpk_attn_bwd(const void* q_arena, const void* do_arena, long q_r
     pp.dkv[i] = i < n_dst ? dkv_ptrs[i] : nullptr;
   }
   const int smem = int(sizeof(BwdSmem)) + 1024;
-  if (!g_bwd_attr_set) {
-    if (cudaFuncSetAttribute(attn_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
-      return -4;
-    g_bwd_attr_set = 1;
+  const int v = g_bwd_timeline_host ? 1 : 0;
+  auto kernel = v ? attn_bwd_kernel<true> : attn_bwd_kernel<false>;
+  if (!g_bwd_attr_set[v]) {
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return -4;
+    g_bwd_attr_set[v] = 1;
   }
-  attn_bwd_kernel<<<dim3(hkv, n_ctas), kBwdThreads, smem, static_cast<cudaStream_t>(stream)>>>(
+  kernel<<<dim3(hkv, n_ctas), kBwdThreads, smem, static_cast<cudaStream_t>(stream)>>>(
       tm_q, tm_do, tm_kv, tm_dq, static_cast<const BwdCta*>(ctas), static_cast<const BwdItemDesc*>(items),
       static_cast<const int4*>(masks), lse, delta, pp, hq, hkv, stat_stride, scale, status);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;

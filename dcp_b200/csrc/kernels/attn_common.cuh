@@ -59,20 +59,31 @@ struct KvTileIter {
   int row, pos0, n_valid;  // current tile
   bool full;         // current tile needs no per-element masking
 
+  KvEntry cur, ahead;  // entry under the cursor and the one after it, held in registers
+
   __device__ __forceinline__ void init(const KvEntry* ents, int n, int bs, const TileBounds& tb) {
     entries = ents; n_kv = n; block_size = bs; b = tb; e = 0; t = -1;
+    cur = KvEntry{0, 0};
+    if (n > 0) cur = ents[0];
+    ahead = cur;
+    if (n > 1) ahead = ents[1];
   }
+  // The table entry is read one block ahead of its use, so a call never waits on global memory.
   __device__ __forceinline__ bool next() {
     while (e < n_kv) {
-      KvEntry ke = entries[e];
-      int n_sub = (ke.n_tok + kTileN - 1) / kTileN;
+      const int n_sub = (cur.n_tok + kTileN - 1) / kTileN;
       ++t;
-      if (t >= n_sub) { ++e; t = -1; continue; }
-      int p0 = e * block_size + t * kTileN;
-      int nv = min(kTileN, ke.n_tok - t * kTileN);
-      bool need = (p0 < b.u0e && p0 + nv > b.u0s) || (p0 < b.u1e && p0 + nv > b.u1s);
+      if (t >= n_sub) {
+        ++e; t = -1;
+        cur = ahead;
+        if (e + 1 < n_kv) ahead = entries[e + 1];
+        continue;
+      }
+      const int p0 = e * block_size + t * kTileN;
+      const int nv = min(kTileN, cur.n_tok - t * kTileN);
+      const bool need = (p0 < b.u0e && p0 + nv > b.u0s) || (p0 < b.u1e && p0 + nv > b.u1s);
       if (!need) continue;
-      row = ke.row + t * kTileN; pos0 = p0; n_valid = nv;
+      row = cur.row + t * kTileN; pos0 = p0; n_valid = nv;
       full = (nv == kTileN) && ((b.i0s <= p0 && b.i0e >= p0 + nv) || (b.i1s <= p0 && b.i1e >= p0 + nv));
       return true;
     }

@@ -33,7 +33,7 @@ struct __align__(1024) FwdSmem {
   uint8_t k[2][kTileBytes];
   uint8_t v[2][kTileBytes];
   uint8_t p[kTileBytes];  // only touched by the smem-P variant
-  uint64_t q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], p_ready[2], o_done;
+  uint64_t q_full, q_tmem, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], p_ready[2], o_done;
   uint32_t tmem_base;
   int abort_word;
   int red[4][8];
@@ -75,7 +75,18 @@ __device__ __forceinline__ void reduce_row_ranges(int (*red)[8], int warp, int l
   }
 }
 
-template <bool kPSmem>
+// Optional per-phase cycle counters of CTA 0 (set with dcpk_attn_fwd_set_timeline; null = off):
+// phases 0-5 softmax warp 0, 6-7 probe-cost calibration, 8-12 UMMA warp.  The counters live in a
+// separately instantiated kernel (kTL): the probes are branches, and branches at phase boundaries
+// stop the compiler from overlapping the phases, so the production kernel carries none.  Every
+// phase includes the cost of one probe (phase 6 measures it: about 110 cycles).
+__device__ long long* g_fwd_timeline = nullptr;
+#define FTL_ADD(idx, t_prev)                                                       \
+  do {                                                                             \
+    if constexpr (kTL) if (tl) { long long now_ = clock64(); if (lane == 0) atomicAdd(reinterpret_cast<unsigned long long*>(tl + (idx)), (unsigned long long)(now_ - (t_prev))); (t_prev) = now_; } \
+  } while (0)
+
+template <bool kPSmem, bool kTL>
 __global__ void __launch_bounds__(kFwdThreads, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_kv,
                 const AttnTile* __restrict__ tiles, const KvEntry* __restrict__ kv_entries,
@@ -91,6 +102,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     tma_prefetch_desc(&tm_q);
     tma_prefetch_desc(&tm_kv);
     mbar_init(&sm.q_full, 1);
+    mbar_init(&sm.q_tmem, 128);
     for (int i = 0; i < 2; ++i) {
       mbar_init(&sm.k_full[i], 1);  mbar_init(&sm.k_empty[i], 1);
       mbar_init(&sm.v_full[i], 1);  mbar_init(&sm.v_empty[i], 1);
@@ -123,6 +135,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   KvTileIter it;
   it.init(kv_entries + tile.kv_off, tile.n_kv, block_size, bounds);
 
+  long long* tl = (kTL && blockIdx.x == 0 && (warp == 0 || warp == 5)) ? g_fwd_timeline : nullptr;
+  long long tl_t = kTL ? clock64() : 0;
   if (warp == 4) {
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
@@ -163,12 +177,17 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     constexpr uint32_t idesc_qk = make_idesc_bf16(128, 128, 0, 0);
     constexpr uint32_t idesc_pv = make_idesc_bf16(128, 128, 0, 1);  // B = V is MN-major
     const uint32_t q_addr = smem_u32(sm.q), p_addr = smem_u32(sm.p);
-    bool ok = mbar_wait(&sm.q_full, 0, abort_word);
+    // Q is the stationary A operand of every S = Q K^T: the softmax threads park it in TMEM once
+    // (columns [384, 448), packed bf16 pairs), so those UMMAs read only the K tile from shared memory
+    bool ok = mbar_wait(&sm.q_tmem, 0, abort_word);
     int j = 0;
     auto issue_pv = [&](int i) -> bool {
       const int st = i & 1, u = i >> 1;
+      FTL_ADD(8, tl_t);
       if (!mbar_wait(&sm.p_ready[st], u & 1, abort_word)) return false;
+      FTL_ADD(9, tl_t);
       if (!mbar_wait(&sm.v_full[st], u & 1, abort_word)) return false;
+      FTL_ADD(10, tl_t);
       tc_fence_after();
       if (lane == 0) {
         const uint32_t v_addr = smem_u32(sm.v[st]);
@@ -187,20 +206,21 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         umma_commit(&sm.v_empty[st]);
       }
       __syncwarp();
+      FTL_ADD(11, tl_t);
       return true;
     };
     while (ok && it.next()) {
       const int st = j & 1, u = j >> 1;
       ok = mbar_wait(&sm.k_full[st], u & 1, abort_word);
       if (!ok) break;
+      FTL_ADD(12, tl_t);
       tc_fence_after();
       if (lane == 0) {
         const uint32_t k_addr = smem_u32(sm.k[st]);
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
-          uint64_t adesc = make_sdesc_sw128(q_addr + (k >> 2) * kHalfBytes + (k & 3) * 32, 16, 1024);
           uint64_t bdesc = make_sdesc_sw128(k_addr + (k >> 2) * kHalfBytes + (k & 3) * 32, 16, 1024);
-          umma_ss(tmem + st * 128, adesc, bdesc, idesc_qk, k > 0 ? 1u : 0u);
+          umma_ts(tmem + st * 128, tmem + 384 + k * 8, bdesc, idesc_qk, k > 0 ? 1u : 0u);
         }
         umma_commit(&sm.s_full[st]);
         umma_commit(&sm.k_empty[st]);
@@ -222,21 +242,45 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     const int len0 = e0 - s0, len1 = e1 - s1;
     float m_run = -INFINITY, l_run = 0.f;
     int j = 0;
-    bool ok = true;
+    bool ok = mbar_wait(&sm.q_full, 0, abort_word);
+    ok = __all_sync(0xffffffffu, ok);
+    if (ok) {
+      // this thread's query row: 16 swizzled 16-byte chunks per 64-channel half -> 64 packed columns
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        uint32_t qreg[32];
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          const uint4 v = *reinterpret_cast<const uint4*>(sm.q + h * kHalfBytes + r * 128 + ((c ^ (r & 7)) << 4));
+          qreg[4 * c] = v.x; qreg[4 * c + 1] = v.y; qreg[4 * c + 2] = v.z; qreg[4 * c + 3] = v.w;
+        }
+        tmem_st32(tmem + lane_base + 384 + h * 32, qreg);
+      }
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(&sm.q_tmem);
+    }
     while (ok && it.next()) {
       const int st = j & 1, u = j >> 1;
+      FTL_ADD(0, tl_t);
       ok = mbar_wait(&sm.s_full[st], u & 1, abort_word);
       if (!ok) break;
+      FTL_ADD(1, tl_t);
       tc_fence_after();
       uint32_t sreg[128];
       const uint32_t s_addr = tmem + lane_base + st * 128;
 #pragma unroll
       for (int c = 0; c < 4; ++c) tmem_ld32(s_addr + c * 32, sreg + c * 32);
       tmem_wait_ld();
-      float mx = -INFINITY;
+      FTL_ADD(2, tl_t);
+      // Row maximum and row sum are reduced through 8 independent partial chains: a single running
+      // value would be a 128-long dependent chain with nothing to hide its latency behind.
+      float mxp[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) mxp[i] = -INFINITY;
       if (it.full) {
 #pragma unroll
-        for (int c = 0; c < 128; ++c) mx = fmaxf(mx, __uint_as_float(sreg[c]));
+        for (int c = 0; c < 128; ++c) mxp[c & 7] = fmaxf(mxp[c & 7], __uint_as_float(sreg[c]));
       } else {
         const int rel0 = it.pos0 - s0, rel1 = it.pos0 - s1;
 #pragma unroll
@@ -245,23 +289,27 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           allow = allow && (c < it.n_valid);
           float sv = allow ? __uint_as_float(sreg[c]) : -INFINITY;
           sreg[c] = __float_as_uint(sv);
-          mx = fmaxf(mx, sv);
+          mxp[c & 7] = fmaxf(mxp[c & 7], sv);
         }
       }
+      const float mx = fmaxf(fmaxf(fmaxf(mxp[0], mxp[1]), fmaxf(mxp[2], mxp[3])),
+                             fmaxf(fmaxf(mxp[4], mxp[5]), fmaxf(mxp[6], mxp[7])));
       const float m_new = fmaxf(m_run, mx);
       const float m_sub = (m_new == -INFINITY) ? 0.f : m_new * sl2;
       const float alpha = (m_new == -INFINITY) ? 1.f : fast_exp2(m_run * sl2 - m_sub);
-      float psum = 0.f;
+      float psp[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
       uint32_t preg[64];
 #pragma unroll
       for (int c = 0; c < 64; ++c) {
         float p0 = fast_exp2(fmaf(__uint_as_float(sreg[2 * c]), sl2, -m_sub));
         float p1 = fast_exp2(fmaf(__uint_as_float(sreg[2 * c + 1]), sl2, -m_sub));
-        psum += p0 + p1;
+        psp[c & 7] += p0 + p1;
         preg[c] = pack_bf16x2(p0, p1);
       }
+      const float psum = ((psp[0] + psp[1]) + (psp[2] + psp[3])) + ((psp[4] + psp[5]) + (psp[6] + psp[7]));
       l_run = l_run * alpha + psum;
       m_run = m_new;
+      FTL_ADD(3, tl_t);
       if (kPSmem) {
         // the single P buffer is free once the previous accumulate retired
         if (j > 0) {
@@ -285,6 +333,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           tc_fence_after();
         }
       }
+      FTL_ADD(4, tl_t);
       if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
         const uint32_t o_addr = tmem + lane_base + 256;
 #pragma unroll
@@ -300,6 +349,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(&sm.p_ready[st]);
+      FTL_ADD(5, tl_t);
+      FTL_ADD(6, tl_t);                                    // empty phase: cost of the probe itself
+      if (kTL && tl) { (void)mbar_try_wait(&sm.q_full, 0); }       // a barrier that completed long ago
+      FTL_ADD(7, tl_t);
       ++j;
     }
     // epilogue
@@ -349,11 +402,18 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   if (threadIdx.x == 0 && sm.abort_word) atomicExch(status, kStatusBarrierTimeout);
 }
 
-static int g_fwd_attr_set[2] = {0, 0};
+static int g_fwd_attr_set[4] = {0, 0, 0, 0};
+static long long* g_fwd_timeline_host = nullptr;  // non-null selects the instrumented build of the kernel
 
 }  // namespace dcpk
 
 using namespace dcpk;
+
+extern "C" int dcpk_attn_fwd_set_timeline(void* buf) {
+  long long* p = static_cast<long long*>(buf);
+  g_fwd_timeline_host = p;
+  return cudaMemcpyToSymbol(g_fwd_timeline, &p, sizeof(p)) == cudaSuccess ? 0 : -5;
+}
 
 // Destinations [0, n_dst_a) have LSE row stride lse_stride_a (partial arenas), the rest lse_stride_b.
 // Launches the forward kernel over `n_tiles` tiles.  `variant` 0 keeps P in TMEM (TS
@@ -374,21 +434,17 @@ extern "C" int dcpk_attn_fwd(const void* q_arena, long q_rows, const void* kv_ar
     pp.lse[i] = i < n_dst ? lse_ptrs[i] : nullptr;
   }
   const int smem = int(sizeof(FwdSmem)) + 1024;
-  const int v = variant ? 1 : 0;
+  const int v = (variant ? 1 : 0) + (g_fwd_timeline_host ? 2 : 0);
+  using KernelFn = void (*)(const CUtensorMap, const CUtensorMap, const AttnTile*, const KvEntry*, const int4*, PeerPtrs,
+                            int, int, int, int, int, int, float, int*);
+  static const KernelFn kernels[4] = {attn_fwd_kernel<false, false>, attn_fwd_kernel<true, false>,
+                                      attn_fwd_kernel<false, true>, attn_fwd_kernel<true, true>};
   if (!g_fwd_attr_set[v]) {
-    cudaError_t e = v ? cudaFuncSetAttribute(attn_fwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)
-                      : cudaFuncSetAttribute(attn_fwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    if (e != cudaSuccess) return -4;
+    if (cudaFuncSetAttribute(kernels[v], cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return -4;
     g_fwd_attr_set[v] = 1;
   }
-  cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (v)
-    attn_fwd_kernel<true><<<n_tiles, kFwdThreads, smem, s>>>(
-        tm_q, tm_kv, static_cast<const AttnTile*>(tiles), static_cast<const KvEntry*>(kv_entries),
-        static_cast<const int4*>(masks), pp, hq, hkv, lse_stride_a, lse_stride_b, n_dst_a, block_size, scale, status);
-  else
-    attn_fwd_kernel<false><<<n_tiles, kFwdThreads, smem, s>>>(
-        tm_q, tm_kv, static_cast<const AttnTile*>(tiles), static_cast<const KvEntry*>(kv_entries),
-        static_cast<const int4*>(masks), pp, hq, hkv, lse_stride_a, lse_stride_b, n_dst_a, block_size, scale, status);
+  kernels[v]<<<n_tiles, kFwdThreads, smem, static_cast<cudaStream_t>(stream)>>>(
+      tm_q, tm_kv, static_cast<const AttnTile*>(tiles), static_cast<const KvEntry*>(kv_entries),
+      static_cast<const int4*>(masks), pp, hq, hkv, lse_stride_a, lse_stride_b, n_dst_a, block_size, scale, status);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
