@@ -115,7 +115,7 @@ def bench_attention(kind, args):
             torch.cuda.synchronize()
             _lib.load().dcpk_attn_bwd_set_timeline(None)
             n_vis = int(bt.ctas[0, 3].item()) * (hq // hkv)
-            names = ["stats->smem", "wait S/dP", "ld S,dP", "wait dQ(t-1)", "drain dQ", "math", "store P,dS + arrive", "-",
+            names = ["wait item + stats", "wait S/dP", "ld S,dP", "wait dQ(t-1)", "drain dQ(t-1) first half", "math", "store P,dS + arrive", "drain dQ(t-1) second half",
                      "umma: issue S/dP", "umma: wait P ready", "umma: issue acc", "umma: wait Q,dO + S free"]
             print("timeline of CTA (0,0), cycles per visit (", n_vis, "visits ):",
                   {n: round(v / max(n_vis, 1)) for n, v in zip(names, tl.tolist()) if n != "-"})

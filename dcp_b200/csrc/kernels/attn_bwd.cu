@@ -32,6 +32,7 @@ namespace dcpk {
 
 static constexpr int kBwdThreads = 320;  // 8 gradient warps + TMA producer + UMMA issuer
 static constexpr int kQTile = 64;
+static constexpr int kStages = 3;  // depth of the Q / dO / statistics ring
 static constexpr int kKvHalf = 128 * 64 * 2;  // [128 x 64] bf16 half tile, 16 KB
 static constexpr int kQHalf = 64 * 64 * 2;    // [64 x 64] bf16 half tile, 8 KB
 
@@ -76,19 +77,21 @@ struct BwdPtrs {
 struct __align__(1024) BwdSmem {
   uint8_t k[2 * kKvHalf];
   uint8_t v[2 * kKvHalf];
-  uint8_t q[2][2 * kQHalf];
-  uint8_t dout[2][2 * kQHalf];
+  uint8_t q[kStages][2 * kQHalf];
+  uint8_t dout[kStages][2 * kQHalf];
   uint8_t ds[kKvHalf];     // dS^T: [128 keys x 64 queries]
   uint8_t p[kKvHalf];      // P^T:  [128 keys x 64 queries]
-  // dQ staging, one private [64 queries x 32 channels] fp32 tile per gradient warp; drained to the
+  // dQ staging, one private [16 queries x 32 channels] fp32 tile per gradient warp; drained to the
   // fp32 accumulator with bulk reduce-add copies (L2 handles those a line at a time, scalar
   // red.add is limited to one element per L2 slice per clock)
-  float dq_stage[8][32 * 32];
-  // per-warp private copies: the four gradient warps never synchronise with each other
-  float lse2[8][32];
-  float delta[8][32];
-  int4 rng[8][32];
-  uint64_t kv_full, qdo_full[2], qdo_empty[2], sdp_full, s_free, p_ready, dq_full;
+  float dq_stage[8][16 * 32];
+  // per-stage item descriptor and per-query statistics, staged by the producer warp next to Q / dO
+  // so the gradient warps never touch global memory on their critical path
+  BwdItem item[kStages];
+  float lse2[kStages][kQTile];   // lse * log2(e); +inf for rows past the tile
+  float delta[kStages][kQTile];
+  int4 rng[kStages][kQTile];     // normalised ranges (end >= start)
+  uint64_t kv_full, qdo_full[kStages], qdo_empty[kStages], stats_full[kStages], sdp_full, s_free, p_ready, dq_full;
   uint32_t tmem_base;
   int abort_word;
 };
@@ -134,7 +137,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     tma_prefetch_desc(&tm_kv);
     tma_prefetch_desc(&tm_dq);
     mbar_init(&sm.kv_full, 1);
-    for (int i = 0; i < 2; ++i) { mbar_init(&sm.qdo_full[i], 1); mbar_init(&sm.qdo_empty[i], 1); }
+    for (int i = 0; i < kStages; ++i) { mbar_init(&sm.qdo_full[i], 1); mbar_init(&sm.qdo_empty[i], 1); mbar_init(&sm.stats_full[i], 1); }
     mbar_init(&sm.sdp_full, 1);
     mbar_init(&sm.s_free, 256);
     mbar_init(&sm.p_ready, 256);
@@ -163,25 +166,56 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       tma_load_3d(sm.k + kKvHalf, &tm_kv, &sm.kv_full, 64, kv_head, cta.kv_row);
       tma_load_3d(sm.v, &tm_kv, &sm.kv_full, 0, hkv + kv_head, cta.kv_row);
       tma_load_3d(sm.v + kKvHalf, &tm_kv, &sm.kv_full, 64, hkv + kv_head, cta.kv_row);
-      bool ok = true;
-      int pending[2] = {-1, -1};
-      for (int i = 0; i < n_items && ok; ++i) {
-        const int st = i & 1, u = i >> 1;
-        const BwdItem itx = load_item(my_items, i, group, kv_head);
-        ok = mbar_wait(&sm.qdo_empty[st], (u & 1) ^ 1, abort_word);
-        if (!ok) break;
+    }
+    bool ok = true;
+    int pending[kStages];
+#pragma unroll
+    for (int i = 0; i < kStages; ++i) pending[i] = -1;
+    int st = 0, u = 0;  // ring slot and its use count
+    for (int i = 0; i < n_items && ok; ++i, st = (st + 1 == kStages ? 0 : st + 1), u += (st == 0)) {
+      const BwdItem itx = load_item(my_items, i, group, kv_head);
+      // the statistics are fetched before the stage is waited for: their latency hides behind the wait
+      float l[2], d[2];
+      int4 m[2];
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int qi = lane + 32 * h;
+        const bool qv = qi < itx.n_rows;
+        const size_t si = size_t(itx.head) * stat_stride + itx.q_row + qi;
+        l[h] = qv ? lse[si] : INFINITY;
+        d[h] = qv ? delta[si] : 0.f;
+        m[h] = make_int4(0, 0, 0, 0);
+        if (qv && !itx.full) m[h] = masks[itx.mask_row + qi];
+      }
+      ok = mbar_wait(&sm.qdo_empty[st], (u & 1) ^ 1, abort_word);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      if (lane == 0) {
         mbar_expect_tx(&sm.qdo_full[st], 4 * kQHalf);
         tma_load_3d(sm.q[st], &tm_q, &sm.qdo_full[st], 0, itx.head, itx.q_row);
         tma_load_3d(sm.q[st] + kQHalf, &tm_q, &sm.qdo_full[st], 64, itx.head, itx.q_row);
         tma_load_3d(sm.dout[st], &tm_do, &sm.qdo_full[st], 0, itx.head, itx.q_row);
         tma_load_3d(sm.dout[st] + kQHalf, &tm_do, &sm.qdo_full[st], 64, itx.head, itx.q_row);
         pending[st] = u & 1;
+        sm.item[st] = itx;
       }
-      if (!ok) {
-        for (int st = 0; st < 2; ++st)
-          if (pending[st] >= 0)
-            for (int spin = 0; spin < 200000 && !mbar_try_wait(&sm.qdo_full[st], pending[st]); ++spin) {}
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int qi = lane + 32 * h;
+        sm.lse2[st][qi] = (l[h] == -INFINITY) ? INFINITY : l[h] * 1.4426950408889634f;
+        sm.delta[st][qi] = d[h];
+        int4 mm = m[h];
+        mm.y = max(mm.y, mm.x); mm.w = max(mm.w, mm.z);
+        sm.rng[st][qi] = mm;
       }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&sm.stats_full[st]);  // release: the stores above are visible to waiters
+    }
+    if (!ok && lane == 0) {
+#pragma unroll
+      for (int s2 = 0; s2 < kStages; ++s2)
+        if (pending[s2] >= 0)
+          for (int spin = 0; spin < 200000 && !mbar_try_wait(&sm.qdo_full[s2], pending[s2]); ++spin) {}
     }
   } else if (warp == 9) {
     // ------------------------------------------------------------ UMMA issuer
@@ -191,7 +225,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     const uint32_t k_addr = smem_u32(sm.k), v_addr = smem_u32(sm.v), ds_addr = smem_u32(sm.ds), p_addr = smem_u32(sm.p);
     bool ok = mbar_wait(&sm.kv_full, 0, abort_word);
     auto issue_acc = [&](int t) -> bool {
-      const int st = t & 1;
+      const int st = t % kStages;
       TL_ADD(8, tl_t);
       if (!mbar_wait(&sm.p_ready, t & 1, abort_word)) return false;
       TL_ADD(9, tl_t);
@@ -226,7 +260,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       return true;
     };
     for (int i = 0; i < n_items && ok; ++i) {
-      const int st = i & 1, u = i >> 1;
+      const int st = i % kStages, u = i / kStages;
       ok = mbar_wait(&sm.qdo_full[st], u & 1, abort_word);
       if (ok && i > 0) ok = mbar_wait(&sm.s_free, (i - 1) & 1, abort_word);
       if (!ok) break;
@@ -263,32 +297,34 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     const bool key_valid = r < cta.n_valid;
     bool ok = true;
     BwdItem prev{};
-    // adds this warp's [32 d x 32 q] part of dQ^T of the previous item into the fp32 accumulator:
-    // transpose through the warp's staging tile, then one TMA reduce-add of the [32 q x 32 d] tile
-    auto flush_dq = [&](const BwdItem& itx, int buf) {
+    // adds half (16 queries) of this warp's [32 d x 32 q] part of dQ^T of an item into the fp32
+    // accumulator: transpose through the warp's staging tile, then one TMA reduce-add of the
+    // [16 q x 32 d] tile (local accumulator) or one 128-byte bulk reduce per query row (peer)
+    auto flush_dq = [&](const BwdItem& itx, int buf, int half) {
       if (itx.dq_dev < 0) return;  // dQ not wanted (used to measure the cost of the drain)
       float* stage = sm.dq_stage[warp];
-      asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");  // earlier drains have left smem
+      asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");  // the earlier drain has left smem
       __syncwarp();
-      uint32_t reg[32];
-      tmem_ld32(tmem + lane_base + cdQ + buf * 64 + hf * 32, reg);
+      uint32_t reg[16];
+      tmem_ld16(tmem + lane_base + cdQ + buf * 64 + hf * 32 + half * 16, reg);
       tmem_wait_ld();
 #pragma unroll
-      for (int i = 0; i < 32; ++i) stage[i * 32 + lane] = __uint_as_float(reg[i]);
+      for (int i = 0; i < 16; ++i) stage[i * 32 + lane] = __uint_as_float(reg[i]);
       fence_proxy_async_smem();
       __syncwarp();
+      const int q0 = hf * 32 + half * 16;
       if (itx.dq_dev == 0) {
         // rows past n_rows hold exact zeros (their probabilities are masked to 0): adding them is harmless
         if (lane == 0) {
           asm volatile(
               "cp.reduce.async.bulk.tensor.3d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3, %4}], [%1];"
               ::"l"(reinterpret_cast<uint64_t>(&tm_dq)), "r"(smem_u32(stage)), "r"(quad * 32), "r"(itx.head),
-              "r"(itx.dq_row + hf * 32)
+              "r"(itx.dq_row + q0)
               : "memory");
         }
       } else {
-        const int qi = hf * 32 + lane;
-        if (qi < itx.n_rows) {
+        const int qi = q0 + lane;
+        if (lane < 16 && qi < itx.n_rows) {
           float* dq = ptrs.dq[itx.dq_dev] + (size_t(itx.dq_row + qi) * hq + itx.head) * kHeadDim + quad * 32;
           asm volatile("cp.reduce.async.bulk.global.shared::cta.bulk_group.add.f32 [%0], [%1], %2;"
                        ::"l"(dq), "r"(smem_u32(stage + lane * 32)), "r"(128)
@@ -297,63 +333,40 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       }
       asm volatile("cp.async.bulk.commit_group;" ::: "memory");
     };
-    // the descriptor and per-query statistics of item t+1 are fetched while item t is processed, so
-    // their global-memory latency never sits on the critical path
-    struct Stats { float l, d; int4 m; };
-    auto fetch_stats = [&](const BwdItem& it, Stats& st) {
-      const int qi = hf * 32 + lane;
-      const bool qv = qi < it.n_rows;
-      st.l = qv ? lse[size_t(it.head) * stat_stride + it.q_row + qi] : INFINITY;
-      st.d = qv ? delta[size_t(it.head) * stat_stride + it.q_row + qi] : 0.f;
-      st.m = make_int4(0, 0, 0, 0);
-      if (qv && !it.full) st.m = masks[it.mask_row + qi];
-    };
-    // descriptors run two items ahead of the math and statistics one ahead, so neither the
-    // descriptor load nor the loads that depend on it are waited for
-    BwdItem nxt{}, nxt2{};
-    Stats nst{};
-    if (n_items > 0) {
-      nxt = load_item(my_items, 0, group, kv_head);
-      fetch_stats(nxt, nst);
-      if (n_items > 1) nxt2 = load_item(my_items, 1, group, kv_head);
-    }
-    for (int t = 0; t < n_items && ok; ++t) {
-      const BwdItem itx = nxt;
-      __syncwarp();
-      {
-        sm.lse2[warp][lane] = (nst.l == -INFINITY) ? INFINITY : nst.l * 1.4426950408889634f;
-        sm.delta[warp][lane] = nst.d;
-        int4 m = nst.m;
-        m.y = max(m.y, m.x); m.w = max(m.w, m.z);
-        sm.rng[warp][lane] = m;
-      }
-      __syncwarp();
-      if (t + 1 < n_items) {
-        nxt = nxt2;
-        fetch_stats(nxt, nst);
-        if (t + 2 < n_items) nxt2 = load_item(my_items, t + 2, group, kv_head);
-      }
-      TL_ADD(0, tl_t);
-      ok = mbar_wait(&sm.sdp_full, t & 1, abort_word);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
+    // S^T / dP^T of an item are pulled into registers as early as possible (right after the
+    // previous item's operands were handed to the tensor core), which frees their TMEM columns for
+    // the next-but-one item while this warp still drains dQ and does the math
+    uint32_t sreg[32], dreg[32];
+    auto load_sdp = [&](int t) -> bool {
+      bool k = mbar_wait(&sm.sdp_full, t & 1, abort_word);
+      k = __all_sync(0xffffffffu, k);
+      if (!k) return false;
       TL_ADD(1, tl_t);
       tc_fence_after();
-      uint32_t sreg[32], dreg[32];
       tmem_ld32(tmem + lane_base + cS + hf * 32, sreg);
       tmem_ld32(tmem + lane_base + cdP + hf * 32, dreg);
       tmem_wait_ld();
       tc_fence_before();
       mbar_arrive(&sm.s_free);
       TL_ADD(2, tl_t);
+      return true;
+    };
+    if (n_items > 0) ok = load_sdp(0);
+    for (int t = 0; t < n_items && ok; ++t) {
+      const int st = t % kStages;
+      ok = mbar_wait(&sm.stats_full[st], (t / kStages) & 1, abort_word);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      const BwdItem itx = sm.item[st];
+      TL_ADD(0, tl_t);
       const int kpos = itx.kv_pos0 + r;
       const int n_rows_h = itx.n_rows - hf * 32;  // valid queries inside this warp's column half
       uint32_t preg[16], dsreg[16];
       // The tile-level "no masking needed" switch is taken once, outside the element loop: with a
       // branch per element every element becomes its own basic block and the compiler cannot
       // interleave the independent exp / multiply chains.
-      const float* lse2_w = sm.lse2[warp];
-      const float* delta_w = sm.delta[warp];
+      const float* lse2_w = sm.lse2[st] + hf * 32;
+      const float* delta_w = sm.delta[st] + hf * 32;
       if (itx.full) {
 #pragma unroll
         for (int c = 0; c < 16; ++c) {
@@ -370,7 +383,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           dsreg[c] = pack_bf16x2(dv[0], dv[1]);
         }
       } else {
-        const int4* rng_w = sm.rng[warp];
+        const int4* rng_w = sm.rng[st] + hf * 32;
 #pragma unroll
         for (int c = 0; c < 16; ++c) {
           float pv[2], dv[2];
@@ -408,10 +421,13 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       tc_fence_before();
       mbar_arrive(&sm.p_ready);
       TL_ADD(6, tl_t);
-      // dQ^T of the previous item sits in the other TMEM buffer: drain it while the tensor core
-      // already accumulates this item
-      if (t > 0) flush_dq(prev, (t - 1) & 1);
+      // dQ^T of the previous item sits in the other TMEM buffer: drain it, in two halves around the
+      // early load of the next S^T / dP^T, while the tensor core already accumulates this item
+      if (t > 0) flush_dq(prev, (t - 1) & 1, 0);
       TL_ADD(4, tl_t);
+      if (t + 1 < n_items) ok = load_sdp(t + 1);
+      if (ok && t > 0) flush_dq(prev, (t - 1) & 1, 1);
+      TL_ADD(7, tl_t);
       prev = itx;
     }
     ok = __all_sync(0xffffffffu, ok);
@@ -420,7 +436,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       ok = __all_sync(0xffffffffu, ok);
       if (ok) {
         tc_fence_after();
-        flush_dq(prev, (n_items - 1) & 1);
+        flush_dq(prev, (n_items - 1) & 1, 0);
+        flush_dq(prev, (n_items - 1) & 1, 1);
         // dK / dV: lane = key row; this warp adds channels 64*hf .. 64*hf+63 of both
         float* dk = ptrs.dkv[cta.dkv_dev] + ((size_t(cta.dkv_row + r) * 2 + 0) * hkv + kv_head) * kHeadDim + hf * 64;
         float* dv = ptrs.dkv[cta.dkv_dev] + ((size_t(cta.dkv_row + r) * 2 + 1) * hkv + kv_head) * kHeadDim + hf * 64;
@@ -515,7 +532,7 @@ extern "C" int dcpk_attn_bwd(const void* q_arena, const void* do_arena, long q_r
   if (n_ctas <= 0) return 0;
   if (n_dst > kMaxPeers || hq % hkv != 0) return -3;
   CUtensorMap tm_q, tm_do, tm_kv, tm_dq;
-  if (encode_f32_tile_map(&tm_dq, dq_ptrs[0], uint64_t(q_rows), uint32_t(hq), kHeadDim, 32, 32)) return -1;
+  if (encode_f32_tile_map(&tm_dq, dq_ptrs[0], uint64_t(q_rows), uint32_t(hq), kHeadDim, 16, 32)) return -1;
   if (encode_arena_map(&tm_q, q_arena, uint64_t(q_rows), uint32_t(hq), kHeadDim, kQTile)) return -1;
   if (encode_arena_map(&tm_do, do_arena, uint64_t(q_rows), uint32_t(hq), kHeadDim, kQTile)) return -1;
   if (encode_arena_map(&tm_kv, kv_arena, uint64_t(kv_rows), uint32_t(2 * hkv), kHeadDim, 128)) return -1;
