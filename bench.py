@@ -140,6 +140,9 @@ def main() -> None:
 
     # ---- region A: device-timed, inputs staged beforehand (tables are per step, so each step's
     # program is uploaded before its own timing window opens and the windows are summed)
+    profiling = os.environ.get("DCP_B200_PROFILE", "0") == "1"
+    if profiling:
+        eng.executor.profile_summary()          # drop the warm-up marks
     sampler = ClockSampler(os.path.join(ROOT, "gpurun_out", f"clocks_rank{rank}.csv") if os.path.isdir(
         os.path.join(ROOT, "gpurun_out")) else f"/tmp/clocks_rank{rank}.csv")
     if rank == 0:
@@ -160,6 +163,11 @@ def main() -> None:
         dev_ms += e0.elapsed_time(e1)
         tokens_timed += plan.n_global_tokens
     launches = _lib.LAUNCHES - launches0
+    if profiling:
+        # per-step milliseconds of the attention executor's phases on this rank (stderr, every rank)
+        phases = {k: round(v / K, 1) for k, v in eng.executor.profile_summary().items()}
+        print(f"[profile rank {rank}] step {dev_ms / K:.1f} ms; attention phases per step: {json.dumps(phases)}",
+              file=sys.stderr, flush=True)
     clocks = sampler.stop() if rank == 0 else {}
     eng.executor.check_status()
 

@@ -49,8 +49,8 @@ class TrainingSpec:
     pipeline_parallel_size: int = 1
     n_microbatches: int = 1
     use_block_size_heuristic: int = 1
-    mem_imbalance_epsilon: float = 0.2
-    comp_imbalance_epsilon: float = 0.2
+    mem_imbalance_epsilon: float = 0.03
+    comp_imbalance_epsilon: float = 0.03
     inter_node_comp_imbalance_factor: float = 5.0
 
 
@@ -80,7 +80,8 @@ class ExecutionPlanner:
         ctx = ts.exec_context
         bs = ts.block_size
         if ts.use_block_size_heuristic:
-            bs = block_size_heuristic(raw_seqlens, ctx.n_devices, ts.mem_imbalance_epsilon, min_block_size=256,
+            # the heuristic bounds the imbalance of a block-cyclic deal, not of the solver: reference tolerance
+            bs = block_size_heuristic(raw_seqlens, ctx.n_devices, max(ts.mem_imbalance_epsilon, 0.2), min_block_size=256,
                                       max_block_size=max(ts.block_size, 256))
         self.block_size = bs
         padded = pad_seqlens(raw_seqlens, bs)

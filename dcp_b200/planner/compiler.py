@@ -24,8 +24,13 @@ from .scheduler import convert_forward_to_backward, schedule
 
 @dataclass
 class CompilerConfig:
-    mem_imbalance_epsilon: float = 0.2
-    comp_imbalance_epsilon: float = 0.2
+    # Balance tolerances of the placement.  The reference defaults to 0.2 / 0.2
+    # (dcp/core/compiler.py:62-110), trading balance for less traffic over InfiniBand.  On one
+    # NVSwitch node a pulled block costs ~1% of the attention time it feeds, while every percent
+    # of imbalance is a percent of step time (the slowest rank sets the pace at each barrier), so
+    # the defaults here are tight; an infeasible tolerance is relaxed automatically by the solver.
+    mem_imbalance_epsilon: float = 0.03
+    comp_imbalance_epsilon: float = 0.03
     inter_node_comp_imbalance_factor: float = 5.0
     reduction_schedule_algo: str = "delayed"
     solver: str = HGPSolver.NATIVE

@@ -115,9 +115,7 @@ def _capacities(vw_comp, vw_mem, k, mem_eps, comp_eps):
     return [cap_c] * k, [cap_m] * k
 
 
-def _solve(vw_comp, vw_mem, offsets, pins, weights, k, mem_eps, comp_eps, seed, n_tries, initial=None):
-    if k == 1:
-        return [0] * len(vw_comp), 0
+def _solve_once(vw_comp, vw_mem, offsets, pins, weights, k, mem_eps, comp_eps, seed, n_tries, initial=None):
     cap_c, cap_m = _capacities(vw_comp, vw_mem, k, mem_eps, comp_eps)
     res = _native().partition_hypergraph(len(vw_comp), vw_comp, vw_mem, offsets, pins, weights, k, cap_c, cap_m,
                                          seed, n_tries, [], [])
@@ -128,7 +126,34 @@ def _solve(vw_comp, vw_mem, offsets, pins, weights, k, mem_eps, comp_eps, seed, 
                                              seed, 1, [], list(initial))
         if (alt["balanced"], -alt["km1"]) > (res["balanced"], -res["km1"]):
             res = alt
-    return res["part"], res["km1"]
+    return res
+
+
+def _overload(res, vw_comp, vw_mem, k) -> float:
+    """Worst load / mean load over both constraints (1.0 = perfectly even)."""
+    mc, mm = max(sum(vw_comp) / k, 1e-9), max(sum(vw_mem) / k, 1e-9)
+    return max(max(res["load_comp"]) / mc, max(res["load_mem"]) / mm)
+
+
+def _solve(vw_comp, vw_mem, offsets, pins, weights, k, mem_eps, comp_eps, seed, n_tries, initial=None):
+    """k-way placement under the two balance constraints.  Tight tolerances are not always
+    reachable (few large blocks); instead of accepting whatever an infeasible run left behind,
+    the tolerances are relaxed step by step until a run meets them, and if none does the least
+    overloaded result is kept."""
+    if k == 1:
+        return [0] * len(vw_comp), 0
+    best, best_over, scale = None, float("inf"), 1.0
+    while True:
+        res = _solve_once(vw_comp, vw_mem, offsets, pins, weights, k, mem_eps * scale, comp_eps * scale, seed, n_tries,
+                          initial)
+        if res["balanced"]:
+            return res["part"], res["km1"]
+        over = _overload(res, vw_comp, vw_mem, k)
+        if over < best_over:
+            best, best_over = res, over
+        if max(mem_eps, comp_eps) * scale >= 0.3:
+            return best["part"], best["km1"]
+        scale *= 1.6
 
 
 def construct_and_partition_graph_multiconstraint(

@@ -15,6 +15,8 @@ No NCCL call is made on these paths.  Takes the role of AttentionExecutor
 """
 from __future__ import annotations
 
+import os
+
 from typing import List, Optional
 
 import numpy as np
@@ -45,6 +47,8 @@ class FusedAttentionExecutor:
         self.arena_epoch = 0          # bumped whenever q/kv local regions are rewritten
         self._staging_valid = False   # remote Q/KV rows in staging match the current local data on peers
         self.kernel_launches = 0
+        self.profile = os.environ.get("DCP_B200_PROFILE", "0") == "1"
+        self._marks = []
 
     def _allocate(self, rows) -> None:
         """(Re)create the symmetric arenas for (q rows, kv rows, partial rows).  Collective: every
@@ -120,12 +124,35 @@ class FusedAttentionExecutor:
             self.kernel_launches += 3 * (self.q_pulls[s].shape[0] > 0)
 
     # ---- forward
+    # ---- optional phase timing (DCP_B200_PROFILE=1): CUDA events on the main stream around the
+    # barriers and the kernels of every call; read with profile_summary() after a synchronize
+    def _mark(self, key: str) -> None:
+        if self.profile:
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record(torch.cuda.current_stream(self.device))
+            self._marks.append((key, ev))
+
+    def profile_summary(self) -> dict:
+        """Total milliseconds per phase since the last call ("fwd:kernels", "bwd:wait peers", ...)."""
+        torch.cuda.synchronize(self.device)
+        tot, prev = {}, None
+        for key, ev in self._marks:
+            if key.endswith(":start"):
+                prev = ev
+                continue
+            tot[key] = tot.get(key, 0.0) + prev.elapsed_time(ev)
+            prev = ev
+        self._marks = []
+        return tot
+
     def forward(self):
         """Attention over the Q/KV already present in ``q_local()`` / ``kv_local()``.
         Returns views (out [rows, hq, d] bf16, lse [hq, rows] fp32) of this rank's own tokens."""
         p, a = self.program, self.arena
         main = torch.cuda.current_stream(self.device)
+        self._mark("fwd:start")
         a.barrier()                                   # every rank's inputs are in place
+        self._mark("fwd:wait inputs of peers")
         ready = []
         if self.world > 1:
             self.side.wait_stream(main)
@@ -144,11 +171,14 @@ class FusedAttentionExecutor:
             if t is None:
                 continue
             self._launch_fwd(t, out_dsts, lse_dsts)
+        self._mark("fwd:pulls + kernels")
         if self.world > 1:
             a.barrier()                               # all partials have landed at their owners
+        self._mark("fwd:wait partials of peers")
         if self.merge_ops.shape[0]:
             block_ops.merge_out_lse(self.merge_ops, self.merge_src, self.part_out, self.part_lse, self.out, self.lse)
             self.kernel_launches += 1
+        self._mark("fwd:merge")
         self._staging_valid = True
         return self.out_local(), self.lse_local()
 
@@ -165,12 +195,15 @@ class FusedAttentionExecutor:
         p, a = self.program, self.arena
         main = torch.cuda.current_stream(self.device)
         n = p.q_local_rows
+        self._mark("bwd:start")
         self.dout[:n].copy_(dout_local.reshape(n, self.hq, HEAD_DIM))
         attn_ops.attn_delta(self.out, self.dout, self.delta, 0, n)
         self.dq[:p.q_rows].zero_()
         self.dkv[:p.kv_rows].zero_()
         self.kernel_launches += 1
+        self._mark("bwd:dout copy, delta, zero accumulators")
         a.barrier()
+        self._mark("bwd:wait inputs of peers")
         ready = []
         if self.world > 1:
             self.side.wait_stream(main)
@@ -189,11 +222,14 @@ class FusedAttentionExecutor:
             attn_ops.attn_bwd(self.q, self.dout, self.kv, self.lse, self.delta, t, [self.dq], [self.dkv], self.scale,
                               a_status(self))
             self.kernel_launches += 1
+        self._mark("bwd:pulls + kernels")
         if self.world > 1:
             block_ops.push_add_rows(self.dq_push, self.dq, a.peer_ptrs("dq"), self.hq * HEAD_DIM)
             block_ops.push_add_rows(self.dkv_push, self.dkv, a.peer_ptrs("dkv"), 2 * self.hkv * HEAD_DIM)
             self.kernel_launches += 2
+            self._mark("bwd:push gradients to owners")
             a.barrier()
+            self._mark("bwd:wait gradients of peers")
         return self.dq[:n], self.dkv[:p.kv_local_rows]
 
     def check_status(self) -> None:
