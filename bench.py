@@ -102,6 +102,9 @@ def main() -> None:
     ap.add_argument("--tokens-per-gpu", type=int, default=32768)
     ap.add_argument("--block-size", type=int, default=2048)
     ap.add_argument("--stages", type=int, default=None)
+    ap.add_argument("--activation-budget-gb", type=float, default=None,
+                    help="extra activation memory for the hand-written layer backward (default: from free memory; "
+                         "0: keep nothing extra; -1: autograd + checkpoint path)")
     args = ap.parse_args()
     if args.impl == "reference":
         reference_arm()
@@ -123,7 +126,7 @@ def main() -> None:
         tokens, dist_, mask, scaling = 131072, synth.LOGNORMAL_8K, "causal", "strong"
     else:
         tokens, dist_, mask, scaling = 131072, synth.LOGNORMAL_16K, "mixed", "strong"
-    cfg = EngineConfig(model, tokens, args.dcp_size, args.block_size, mask, dist_, n_stages=args.stages,
+    cfg = EngineConfig(model, tokens, args.dcp_size, args.block_size, mask, dist_, n_stages=args.stages, activation_budget_gb=args.activation_budget_gb,
                        planner_workers=2, lookahead=args.steps + 1)
     eng = TrainEngine(cfg, dev, group)
     W, K = args.warmup, args.steps
@@ -188,6 +191,10 @@ def main() -> None:
         dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group)
     dev_ms, e2e_s = float(t[0]), float(t[1])
     eng.close()
+    lv = eng.activation_levels
+    recompute_desc = "full per layer (autograd checkpoint)" if lv is None else (
+        "per layer, hand-written backward: %d layers recompute QKV/O/gate-up GEMMs, %d recompute gate-up only, "
+        "%d recompute no GEMM (chosen from free memory)" % (lv.count(0), lv.count(1), lv.count(2)))
     if rank == 0:
         value = tokens_timed / (dev_ms / 1e3)
         dcp = cfg.dcp_size or world
@@ -201,7 +208,7 @@ def main() -> None:
                        "global_batch": tokens, "seq_len": "variable, <= 131072", "parallelism": par,
                        "tokens_per_gpu": tokens // world, "mask": mask, "length_dist": dist_.kind,
                        "dcp_block_size": args.block_size, "optimizer": "AdamW (sharded fp32 state), grad clip 1.0",
-                       "recompute": "full per layer",
+                       "recompute": recompute_desc,
                        "l2": "inputs change every step and exceed L2 (16 GB of weights streamed per pass)",
                        "baseline_number": "46.3k tokens/s: DCP on 64 x A100, GPT-8B, LongAlign 131072 causal"},
             "clocks": clocks,

@@ -50,7 +50,7 @@ class TrainingSpec:
     n_microbatches: int = 1
     use_block_size_heuristic: int = 1
     mem_imbalance_epsilon: float = 0.03
-    comp_imbalance_epsilon: float = 0.03
+    comp_imbalance_epsilon: float = 0.015
     inter_node_comp_imbalance_factor: float = 5.0
 
 

@@ -101,6 +101,116 @@ class _AttentionFn(torch.autograd.Function):
         return dqkv, None, None, None, None
 
 
+class _DecoderLayerFn(torch.autograd.Function):
+    """One decoder layer with a hand-written backward and an explicit activation budget.
+
+    Saved per layer, by level: 0 keeps the layer input and the attention result (every dense
+    product the backward needs is recomputed, except the down projection, which nothing in the
+    backward reads); 1 also keeps the packed QKV projection and the post-attention residual, so
+    only the gate/up projection is recomputed; 2 also keeps the gate/up projection, so no GEMM
+    is recomputed.  Weight gradients are written straight into the flat gradient buffer by the
+    GEMM (or added to it when ``model.accumulate_grads``), with no separate accumulation pass.
+    The reference gets the same effect from Megatron's activation-recompute granularity flags
+    (benchmark/mlm/run_experiments.py:460-520).
+    """
+
+    @staticmethod
+    def forward(ctx, x, model, l, cos, sin, level):
+        p, cfg, ex = model.p, model.cfg, model.executor
+        T = x.shape[0]
+        h1, rstd1 = model_ops.rmsnorm_fwd_raw(x, p[f"l{l}.norm1"], cfg.eps)
+        qkv = torch.mm(h1, p[f"l{l}.wqkv"].t())
+        del h1
+        model_ops.qkv_rope_split(qkv, cos, sin, ex.q, ex.kv, cfg.n_heads, cfg.n_kv_heads)
+        ex.inputs_written()
+        out, lse = ex.forward()
+        a = out.reshape(T, -1).clone()
+        lse_c = lse.clone()
+        x_mid = torch.addmm(x, a, p[f"l{l}.wo"].t())
+        h2, rstd2 = model_ops.rmsnorm_fwd_raw(x_mid, p[f"l{l}.norm2"], cfg.eps)
+        gu = torch.mm(h2, p[f"l{l}.wgu"].t())
+        del h2
+        act = model_ops.swiglu_fwd_raw(gu)
+        y = torch.addmm(x_mid, act, p[f"l{l}.wd"].t())
+        ctx.model, ctx.l, ctx.level, ctx.epoch = model, l, level, ex.arena_epoch
+        keep = [x, cos, sin, a, lse_c, rstd1]
+        if level >= 1:
+            keep += [qkv, x_mid, rstd2]
+        if level >= 2:
+            keep.append(gu)
+        ctx.save_for_backward(*keep)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        model, l, level = ctx.model, ctx.l, ctx.level
+        p, cfg, ex = model.p, model.cfg, model.executor
+        saved = ctx.saved_tensors
+        x, cos, sin, a, lse_c, rstd1 = saved[:6]
+        T = x.shape[0]
+        dy = dy.contiguous()
+        w1, wqkv, wo = p[f"l{l}.norm1"], p[f"l{l}.wqkv"], p[f"l{l}.wo"]
+        w2, wgu, wd = p[f"l{l}.norm2"], p[f"l{l}.wgu"], p[f"l{l}.wd"]
+
+        def wgrad(param, lhs_t, rhs):
+            if model.accumulate_grads:
+                param.grad.addmm_(lhs_t, rhs)
+            else:
+                torch.mm(lhs_t, rhs, out=param.grad)
+
+        def ngrad(param, dw):
+            if model.accumulate_grads:
+                param.grad.add_(dw.to(param.grad.dtype))
+            else:
+                param.grad.copy_(dw)
+
+        if level >= 1:
+            qkv, x_mid, rstd2 = saved[6:9]
+        else:
+            h1, _ = model_ops.rmsnorm_fwd_raw(x, w1, cfg.eps)
+            qkv = torch.mm(h1, wqkv.t())
+            del h1
+            x_mid = torch.addmm(x, a, wo.t())
+            rstd2 = None
+        # ---- MLP
+        h2, rstd2_new = model_ops.rmsnorm_fwd_raw(x_mid, w2, cfg.eps)
+        rstd2 = rstd2 if rstd2 is not None else rstd2_new
+        gu = saved[9] if level >= 2 else torch.mm(h2, wgu.t())
+        act = model_ops.swiglu_fwd_raw(gu)
+        dact = torch.mm(dy, wd)
+        wgrad(wd, dy.t(), act)
+        del act
+        dgu = model_ops.swiglu_bwd_raw(gu, dact)
+        del dact, gu
+        dh2 = torch.mm(dgu, wgu)
+        wgrad(wgu, dgu.t(), h2)
+        del dgu, h2
+        dx_mid, dw2 = model_ops.rmsnorm_bwd_raw(x_mid, w2, rstd2, dh2)
+        del dh2
+        dx_mid.add_(dy)
+        ngrad(w2, dw2)
+        # ---- attention
+        da = torch.mm(dx_mid, wo)
+        wgrad(wo, dx_mid.t(), a)
+        if ex.arena_epoch != ctx.epoch:
+            # another layer used the arenas since this forward ran: put this layer's operands back
+            model_ops.qkv_rope_split(qkv, cos, sin, ex.q, ex.kv, cfg.n_heads, cfg.n_kv_heads)
+            ex.inputs_written()
+            ex.out_local().copy_(a.view(-1, cfg.n_heads, cfg.head_dim))
+            ex.lse_local().copy_(lse_c)
+        dq, dkv = ex.backward(da.view(-1, cfg.n_heads, cfg.head_dim))
+        del da
+        dqkv = model_ops.qkv_rope_pack_bwd(dq, dkv, cos, sin, T, cfg.n_heads, cfg.n_kv_heads)
+        h1, _ = model_ops.rmsnorm_fwd_raw(x, w1, cfg.eps)
+        dh1 = torch.mm(dqkv, wqkv)
+        wgrad(wqkv, dqkv.t(), h1)
+        del dqkv, h1
+        dx, dw1 = model_ops.rmsnorm_bwd_raw(x, w1, rstd1, dh1)
+        dx.add_(dx_mid)
+        ngrad(w1, dw1)
+        return dx, None, None, None, None, None
+
+
 class _LMHeadLossFn(torch.autograd.Function):
     """Chunked LM head + cross entropy: logits never exist for more than ``chunk`` tokens, and
     the gradients of the hidden states and of the head weight are formed in the same pass."""
@@ -143,6 +253,10 @@ class LlamaModel:
         self.cache_attention = True
         self._attn_stash: Dict[int, tuple] = {}
         self._stash_enabled = False
+        # hand-written layer backward (CUDA only): per-layer activation level 0/1/2, see _DecoderLayerFn;
+        # None keeps the autograd + checkpoint path
+        self.layer_levels: Optional[List[int]] = None
+        self.accumulate_grads = False   # True: weight gradients are added to .grad instead of written
         shapes: List[Tuple[str, Tuple[int, ...]]] = [("embed", (cfg.vocab, cfg.hidden))]
         for l in range(cfg.n_layers):
             shapes += [(f"l{l}.norm1", (cfg.hidden,)), (f"l{l}.wqkv", (cfg.qkv_dim, cfg.hidden)),
@@ -198,6 +312,22 @@ class LlamaModel:
                         seg = flat[s:s + (1 << 26)]
                         seg.copy_(torch.empty(seg.numel(), dtype=torch.float32, device=self.device).normal_(0, std, generator=g))
 
+    def plan_activation_levels(self, tokens: int, budget_bytes: int) -> List[int]:
+        """Per-layer activation levels for the hand-written layer backward that fit ``budget_bytes``
+        of extra activation memory at ``tokens`` tokens per rank: first every layer is raised to
+        level 1 (all or nothing: a mixed 0/1 schedule saves little), then as many layers as fit
+        are raised to level 2, the last layers first (their activations live the shortest)."""
+        cfg = self.cfg
+        lvl1 = tokens * (cfg.qkv_dim + cfg.hidden) * 2 + tokens * 4
+        lvl2 = tokens * 2 * cfg.ffn * 2
+        levels = [0] * cfg.n_layers
+        if budget_bytes >= lvl1 * cfg.n_layers:
+            levels = [1] * cfg.n_layers
+            n2 = min(cfg.n_layers, int((budget_bytes - lvl1 * cfg.n_layers) // lvl2))
+            for l in range(cfg.n_layers - n2, cfg.n_layers):
+                levels[l] = 2
+        return levels
+
     def parameters(self):
         return list(self.p.values())
 
@@ -227,8 +357,11 @@ class LlamaModel:
         self._stash_enabled = self.cache_attention and self.recompute and torch.is_grad_enabled()
         cos, sin = model_ops.rope_tables(positions, cfg.rope_theta, cfg.head_dim)
         x = F.embedding(tokens, self.p["embed"])
+        manual = self.layer_levels is not None and x.is_cuda and torch.is_grad_enabled()
         for l in range(cfg.n_layers):
-            if self.recompute and torch.is_grad_enabled():
+            if manual:
+                x = _DecoderLayerFn.apply(x, self, l, cos, sin, self.layer_levels[l])
+            elif self.recompute and torch.is_grad_enabled():
                 x = checkpoint(self._layer, x, l, cos, sin, use_reentrant=False)
             else:
                 x = self._layer(x, l, cos, sin)

@@ -48,28 +48,37 @@ def cross_entropy_reference(logits: torch.Tensor, labels: torch.Tensor):
 
 
 # --------------------------------------------------------------------------- RMSNorm
+def rmsnorm_fwd_raw(x: torch.Tensor, w: torch.Tensor, eps: float):
+    """(y, rstd) for contiguous 2-D bf16 x; no autograd."""
+    y = torch.empty_like(x)
+    rstd = torch.empty(x.shape[0], dtype=torch.float32, device=x.device)
+    _lib.check(_lib.load().dcpk_rmsnorm_fwd(_lib.ptr(x), _lib.ptr(w), _lib.ptr(y), _lib.ptr(rstd), _c_int(x.shape[0]),
+                                            _c_int(x.shape[1]), _c_float(eps), _lib.stream_handle()), "rmsnorm_fwd")
+    return y, rstd
+
+
+def rmsnorm_bwd_raw(x: torch.Tensor, w: torch.Tensor, rstd: torch.Tensor, dy: torch.Tensor):
+    """(dx bf16, dw fp32) for contiguous 2-D x / dy; no autograd."""
+    dx = torch.empty_like(x)
+    dw = torch.zeros(x.shape[1], dtype=torch.float32, device=x.device)
+    _lib.check(_lib.load().dcpk_rmsnorm_bwd(_lib.ptr(x), _lib.ptr(w), _lib.ptr(dy), _lib.ptr(rstd), _lib.ptr(dx),
+                                            _lib.ptr(dw), _c_int(x.shape[0]), _c_int(x.shape[1]), _lib.stream_handle()),
+               "rmsnorm_bwd")
+    return dx, dw
+
+
 class _RMSNorm(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, w, eps):
-        lib = _lib.load()
         x2 = x.reshape(-1, x.shape[-1]).contiguous()
-        y = torch.empty_like(x2)
-        rstd = torch.empty(x2.shape[0], dtype=torch.float32, device=x.device)
-        _lib.check(lib.dcpk_rmsnorm_fwd(_lib.ptr(x2), _lib.ptr(w), _lib.ptr(y), _lib.ptr(rstd), _c_int(x2.shape[0]),
-                                        _c_int(x2.shape[1]), _c_float(eps), _lib.stream_handle()), "rmsnorm_fwd")
+        y, rstd = rmsnorm_fwd_raw(x2, w, eps)
         ctx.save_for_backward(x2, w, rstd)
         return y.view(x.shape)
 
     @staticmethod
     def backward(ctx, dy):
-        lib = _lib.load()
         x2, w, rstd = ctx.saved_tensors
-        dy2 = dy.reshape(x2.shape).contiguous()
-        dx = torch.empty_like(x2)
-        dw = torch.zeros(x2.shape[1], dtype=torch.float32, device=x2.device)
-        _lib.check(lib.dcpk_rmsnorm_bwd(_lib.ptr(x2), _lib.ptr(w), _lib.ptr(dy2), _lib.ptr(rstd), _lib.ptr(dx),
-                                        _lib.ptr(dw), _c_int(x2.shape[0]), _c_int(x2.shape[1]), _lib.stream_handle()),
-                   "rmsnorm_bwd")
+        dx, dw = rmsnorm_bwd_raw(x2, w, rstd, dy.reshape(x2.shape).contiguous())
         return dx.view(dy.shape), dw.to(w.dtype), None
 
 
@@ -80,28 +89,36 @@ def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float = 1e-5) -> torch.Tensor
 
 
 # --------------------------------------------------------------------------- SwiGLU
+def swiglu_fwd_raw(gu: torch.Tensor) -> torch.Tensor:
+    """silu(gate) * up for contiguous 2-D bf16 [T, 2F] laid out gate | up; no autograd."""
+    f = gu.shape[1] // 2
+    y = torch.empty(gu.shape[0], f, dtype=gu.dtype, device=gu.device)
+    _lib.check(_lib.load().dcpk_swiglu_fwd(_lib.ptr(gu), _lib.ptr(y), _c_long(gu.shape[0]), _c_int(f),
+                                           _lib.stream_handle()), "swiglu_fwd")
+    return y
+
+
+def swiglu_bwd_raw(gu: torch.Tensor, dy: torch.Tensor) -> torch.Tensor:
+    f = gu.shape[1] // 2
+    dgu = torch.empty_like(gu)
+    _lib.check(_lib.load().dcpk_swiglu_bwd(_lib.ptr(gu), _lib.ptr(dy), _lib.ptr(dgu), _c_long(gu.shape[0]), _c_int(f),
+                                           _lib.stream_handle()), "swiglu_bwd")
+    return dgu
+
+
 class _SwiGLU(torch.autograd.Function):
     @staticmethod
     def forward(ctx, gu):
-        lib = _lib.load()
         f = gu.shape[-1] // 2
         g2 = gu.reshape(-1, 2 * f).contiguous()
-        y = torch.empty(g2.shape[0], f, dtype=gu.dtype, device=gu.device)
-        _lib.check(lib.dcpk_swiglu_fwd(_lib.ptr(g2), _lib.ptr(y), _c_long(g2.shape[0]), _c_int(f),
-                                       _lib.stream_handle()), "swiglu_fwd")
         ctx.save_for_backward(g2)
-        return y.view(*gu.shape[:-1], f)
+        return swiglu_fwd_raw(g2).view(*gu.shape[:-1], f)
 
     @staticmethod
     def backward(ctx, dy):
-        lib = _lib.load()
         (g2,) = ctx.saved_tensors
         f = g2.shape[1] // 2
-        dy2 = dy.reshape(-1, f).contiguous()
-        dgu = torch.empty_like(g2)
-        _lib.check(lib.dcpk_swiglu_bwd(_lib.ptr(g2), _lib.ptr(dy2), _lib.ptr(dgu), _c_long(g2.shape[0]), _c_int(f),
-                                       _lib.stream_handle()), "swiglu_bwd")
-        return dgu.view(*dy.shape[:-1], 2 * f)
+        return swiglu_bwd_raw(g2, dy.reshape(-1, f).contiguous()).view(*dy.shape[:-1], 2 * f)
 
 
 def swiglu(gate_up: torch.Tensor) -> torch.Tensor:

@@ -30,7 +30,7 @@ class CompilerConfig:
     # of imbalance is a percent of step time (the slowest rank sets the pace at each barrier), so
     # the defaults here are tight; an infeasible tolerance is relaxed automatically by the solver.
     mem_imbalance_epsilon: float = 0.03
-    comp_imbalance_epsilon: float = 0.03
+    comp_imbalance_epsilon: float = 0.015
     inter_node_comp_imbalance_factor: float = 5.0
     reduction_schedule_algo: str = "delayed"
     solver: str = HGPSolver.NATIVE

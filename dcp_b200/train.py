@@ -39,6 +39,10 @@ class EngineConfig:
     weight_decay: float = 0.1
     clip_grad: Optional[float] = 1.0
     recompute: bool = True
+    # extra activation memory the hand-written layer backward may keep to skip recomputing GEMMs:
+    # None = decide from the free device memory at start-up, 0 = keep nothing extra, < 0 = use the
+    # autograd + checkpoint path instead of the hand-written backward
+    activation_budget_gb: Optional[float] = None
     seed: int = 0
     planner_workers: int = 2
     lookahead: int = 3
@@ -75,12 +79,34 @@ class TrainEngine:
         self.executor = FusedAttentionExecutor(m.n_heads, m.n_kv_heads, cap, cap, 2 * cap, device,
                                                self.dcp_group if dcp > 1 else None)
         self.model.set_executor(self.executor)
+        self.activation_levels = self._plan_activations(group_tokens // dcp)
         self.spec = PlanSpec(self.world, dcp, cfg.tokens_per_step, m.n_heads, m.n_kv_heads, m.head_dim, cfg.block_size,
                              0, cfg.mask, cfg.length_dist or synth.LOGNORMAL_8K, m.vocab, cfg.seed, cfg.n_stages)
         self.plans = PlanService(self.spec, self.rank, cfg.planner_workers, cfg.lookahead)
         self.iteration = 0
         self.h2d_bytes = 0
         self.d2h_bytes = 0
+
+    def _plan_activations(self, tokens_per_rank: int):
+        """Choose how much each layer keeps for its backward (see LlamaModel.plan_activation_levels)."""
+        cfg, m = self.cfg, self.cfg.model
+        if not cfg.recompute or (cfg.activation_budget_gb is not None and cfg.activation_budget_gb < 0):
+            return None
+        tokens = int(tokens_per_rank * 1.15) + cfg.block_size
+        if cfg.activation_budget_gb is not None:
+            budget = int(cfg.activation_budget_gb * 1e9)
+        else:
+            free, _ = torch.cuda.mem_get_info(self.device)
+            # what a step needs besides the optional activations: level-0 activations of every layer,
+            # one layer's transients (gate/up, its gradient, two FFN-wide temporaries), the LM-head
+            # chunk (logits + fp32 loss temporaries, weight gradient), allocator slack
+            level0 = m.n_layers * tokens * (2 * m.hidden * 2 + m.n_heads * 4)
+            transient = tokens * (2 * 2 * m.ffn * 2 + 2 * m.ffn * 2 + 6 * m.hidden * 2)
+            lm_head = cfg.lm_head_chunk * m.vocab * 8 + m.vocab * m.hidden * 2 + 2 * tokens * m.hidden * 2
+            budget = free - level0 - transient - lm_head - int(16e9)
+        levels = self.model.plan_activation_levels(tokens, max(0, budget))
+        self.model.layer_levels = levels
+        return levels
 
     # ---- one iteration
     def stage_inputs(self, plan: RankPlan):

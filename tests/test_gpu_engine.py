@@ -34,7 +34,10 @@ def test_fused_executor_two_gpus():
     assert res.returncode == 0 and "FUSED_OK" in res.stdout, res.stdout[-3000:]
 
 
-def test_tiny_model_step_matches_pytorch():
+@pytest.mark.parametrize("layer_path", ["autograd", "level0", "level1+2", "auto"])
+def test_tiny_model_step_matches_pytorch(layer_path):
+    """Every layer implementation (autograd + checkpoint, hand-written backward at each activation
+    level) must give the gradients of the fp32 PyTorch model."""
     _need_gpu()
     from dcp_b200.data import synth
     from dcp_b200.models.llama import tiny_config
@@ -44,8 +47,17 @@ def test_tiny_model_step_matches_pytorch():
     cfg = EngineConfig(tiny_config(n_layers=2, hidden=1024, n_heads=8, n_kv_heads=2, ffn=2048, vocab=2048),
                        tokens_per_step=1536, block_size=256,
                        length_dist=synth.LengthDist("lognormal", 400.0, 0.6, 64, 1536), planner_workers=0,
-                       clip_grad=None)
+                       clip_grad=None,
+                       activation_budget_gb={"autograd": -1.0, "level0": 0.0, "level1+2": 0.0, "auto": None}[layer_path])
     eng = TrainEngine(cfg, dev)
+    if layer_path == "autograd":
+        assert eng.model.layer_levels is None
+    elif layer_path == "level0":
+        assert eng.model.layer_levels == [0, 0]
+    elif layer_path == "level1+2":
+        eng.model.layer_levels = [1, 2]
+    else:
+        assert eng.model.layer_levels == [2, 2]     # a tiny model fits entirely
     plan = eng.plans.get(0)
     toks, labels, pos = eng.stage_inputs(plan)
     eng.model.zero_grad()
