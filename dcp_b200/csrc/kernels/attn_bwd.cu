@@ -120,7 +120,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                 const __grid_constant__ CUtensorMap tm_kv, const __grid_constant__ CUtensorMap tm_dq,
                 const BwdCta* __restrict__ ctas, const BwdItemDesc* __restrict__ items, const int4* __restrict__ masks,
                 const float* __restrict__ lse, const float* __restrict__ delta, BwdPtrs ptrs, int hq, int hkv,
-                int stat_stride, float scale, int* __restrict__ status) {
+                int stat_stride, int n_dst, int q_rows, int kv_rows, float scale, int* __restrict__ status) {
   extern __shared__ uint8_t smem_raw[];
   BwdSmem& sm = *reinterpret_cast<BwdSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -130,6 +130,17 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   const int group = hq / hkv;
   const BwdItemDesc* my_items = items + cta.item_off;
   const int n_items = cta.n_items * group;  // visits
+  {
+    // table sanity before anything is allocated: a key tile whose gradient rows would fall outside
+    // the accumulator is reported and skipped (items are checked one by one by the producer warp)
+    const bool bad = cta.dkv_dev < 0 || cta.dkv_dev >= n_dst || cta.dkv_row < 0 || cta.n_valid < 0 ||
+                     cta.n_valid > 128 || cta.dkv_row + cta.n_valid > kv_rows || cta.kv_row < 0 ||
+                     cta.kv_row + cta.n_valid > kv_rows || cta.n_items < 0 || cta.item_off < 0;
+    if (bad) {
+      if (threadIdx.x == 0) atomicExch(status, kStatusBadArgs);
+      return;
+    }
+  }
 
   if (threadIdx.x == 256) {
     tma_prefetch_desc(&tm_q);
@@ -174,6 +185,13 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     int st = 0, u = 0;  // ring slot and its use count
     for (int i = 0; i < n_items && ok; ++i, st = (st + 1 == kStages ? 0 : st + 1), u += (st == 0)) {
       const BwdItem itx = load_item(my_items, i, group, kv_head);
+      if (itx.n_rows < 0 || itx.n_rows > kQTile || itx.q_row < 0 || itx.q_row + itx.n_rows > q_rows ||
+          itx.q_row + itx.n_rows > stat_stride || itx.dq_dev >= n_dst ||
+          (itx.dq_dev >= 0 && (itx.dq_row < 0 || itx.dq_row + itx.n_rows > q_rows))) {
+        sm.abort_word = kStatusBadArgs;  // every waiter unwinds; the code is reported as the status
+        ok = false;
+        break;
+      }
       // the statistics are fetched before the stage is waited for: their latency hides behind the wait
       float l[2], d[2];
       int4 m[2];
@@ -472,7 +490,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     tc_fence_after();
     tmem_dealloc(tmem, 512);
   }
-  if (threadIdx.x == 0 && sm.abort_word) atomicExch(status, kStatusBarrierTimeout);
+  if (threadIdx.x == 0 && sm.abort_word) atomicExch(status, sm.abort_word);  // 1 = wait timeout, 3 = bad table
 }
 
 // delta[h][row] = sum_d dO[row][h][d] * O[row][h][d]; one warp per (row, head)
@@ -550,6 +568,7 @@ extern "C" int dcpk_attn_bwd(const void* q_arena, const void* do_arena, long q_r
   }
   kernel<<<dim3(hkv, n_ctas), kBwdThreads, smem, static_cast<cudaStream_t>(stream)>>>(
       tm_q, tm_do, tm_kv, tm_dq, static_cast<const BwdCta*>(ctas), static_cast<const BwdItemDesc*>(items),
-      static_cast<const int4*>(masks), lse, delta, pp, hq, hkv, stat_stride, scale, status);
+      static_cast<const int4*>(masks), lse, delta, pp, hq, hkv, stat_stride, n_dst, int(q_rows), int(kv_rows), scale,
+      status);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }

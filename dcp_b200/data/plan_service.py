@@ -48,6 +48,12 @@ class PlanSpec:
     n_stages: Optional[int] = None
     build_backward: bool = True
     build_instruction_plans: bool = False   # also emit ExecutionPlans (plan-interpreting executors)
+    # planner knobs (None = the defaults of CompilerConfig / the cost models)
+    mem_imbalance_epsilon: Optional[float] = None
+    comp_imbalance_epsilon: Optional[float] = None
+    inter_node_comp_imbalance_factor: Optional[float] = None
+    use_block_size_heuristic: bool = False
+    cost_model: Optional[dict] = None       # intra/inter node latency + bandwidth, max_tflops, max_mem_bw
 
 
 @dataclass
@@ -101,16 +107,31 @@ def plan_batch(spec: PlanSpec, iteration: int, rank: int, seqlens: Sequence[int]
     raw = [seqlens[i] for i in members]
     cu_all = seq_token_offsets(seqlens)
     bs = spec.block_size
+    if spec.use_block_size_heuristic:
+        from ..planner.workload import block_size_heuristic
+        bs = block_size_heuristic(raw, spec.dcp_size, 0.2, min_block_size=256, max_block_size=max(bs, 256))
     pad = pad_seqlens(raw, bs)
     info = [mask_fn_info[i] for i in members] if mask_fn_info is not None else None
     fn = mask_fn or mask_lib.get_mask_fn(spec.mask)
     mask = fn(raw, pad, torch.int32, info)
     ctx = get_default_execution_context(spec.dcp_size, 1)
+    if spec.cost_model:
+        from ..core.cost_model import AttnRooflineCostModel, CommunicationCostModel
+        cm, c0, a0 = spec.cost_model, CommunicationCostModel(), AttnRooflineCostModel()
+        pick = lambda key, default: default if cm.get(key) is None else cm[key]
+        ctx.comm_cost_model = CommunicationCostModel(
+            pick("inter_node_lat", c0.inter_node_latency), pick("inter_node_bw", c0.inter_node_bandwidth),
+            pick("intra_node_lat", c0.intra_node_latency), pick("intra_node_bw", c0.intra_node_bandwidth))
+        ctx.comp_cost_model = AttnRooflineCostModel(pick("max_tflops", a0.max_tflops), pick("max_mem_bw", a0.max_mem_bw))
     hbs = spec.head_block_size or spec.n_heads
     d = spec.head_dim
     wl = generate_workload((sum(pad), spec.n_heads, d), (sum(pad), 2, spec.n_kv_heads, d), raw, pad, bs, hbs,
                            ctx.comp_cost_model, mask, torch.bfloat16)
-    compiler = InstrCompiler(ctx, CompilerConfig(n_stages=spec.n_stages))
+    ccfg = CompilerConfig(n_stages=spec.n_stages)
+    for name in ("mem_imbalance_epsilon", "comp_imbalance_epsilon", "inter_node_comp_imbalance_factor"):
+        if getattr(spec, name) is not None:
+            setattr(ccfg, name, getattr(spec, name))
+    compiler = InstrCompiler(ctx, ccfg)
     fw_wl, bw_wl, fw_plans, bw_plans = compiler.compile(wl, generate_backward=spec.build_instruction_plans)
     dev = (0, group_rank)
     program = lower_all(ctx, fw_wl, spec.build_backward, only=dev)[dev]

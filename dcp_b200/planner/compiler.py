@@ -96,6 +96,29 @@ class InstrCompiler:
                                       workload.output_to_device_map)}, f)
         return res
 
+    def _debug_placement(self, workload: WorkloadSpec, d2w, d2i) -> None:
+        """DCP_LOG_WORKLOAD_SPEC: workload summary; DCP_LOG_GRAPH_PARTITION: per-device compute and
+        memory load of the placement; DCP_DEBUG_VISUALIZE_WORKLOAD_SPEC: block -> device map as
+        text in the log and as a figure description under DCP_DEBUG_VISUALIZE_WORKLOAD_SPEC_DIR."""
+        if read_env_bool("DCP_LOG_WORKLOAD_SPEC"):
+            self.logger.info("workload: %d work units, %d input blocks, %d output blocks, total cost %.3f ms",
+                             len(workload.workloads), len(workload.input_sizes), len(workload.output_sizes),
+                             float(sum(workload.workloads)))
+        if read_env_bool("DCP_LOG_GRAPH_PARTITION"):
+            for d in sorted(d2w):
+                self.logger.info("placement device %s: %d work units, cost %.3f ms, %d input blocks, %.1f MB", d,
+                                 len(d2w[d]), float(sum(workload.workloads[w] for w in d2w[d])), len(d2i[d]),
+                                 sum(workload.input_sizes[i] for i in d2i[d]) / 1e6)
+        if read_env_bool("DCP_DEBUG_VISUALIZE_WORKLOAD_SPEC"):
+            from ..utils.visualization import visualize_workload_spec_figure, visualize_workload_spec_tty
+            self.logger.info("block -> device map\n%s",
+                             visualize_workload_spec_tty(workload, self.context.n_devices_per_node))
+            out_dir = os.environ.get("DCP_DEBUG_VISUALIZE_WORKLOAD_SPEC_DIR",
+                                     os.environ.get("DCP_LOGGING_DEBUG_DIR", "./debug"))
+            os.makedirs(out_dir, exist_ok=True)
+            visualize_workload_spec_figure(workload, os.path.join(out_dir, f"workload_iter{self.iteration_idx}.json"),
+                                           self.context.n_devices_per_node)
+
     def compile(self, workload: WorkloadSpec, generate_backward: bool = True) -> Tuple[
             WorkloadSpec, Optional[WorkloadSpec], Dict[Device, ExecutionPlan], Optional[Dict[Device, ExecutionPlan]]]:
         load_plans = os.environ.get("DCP_DEBUG_LOAD_EXEC_PLANS_FILE") if read_env_bool("DCP_DEBUG_LOAD_EXEC_PLANS") else None
@@ -106,6 +129,7 @@ class InstrCompiler:
         t0 = time.time()
         d2w, d2i, d2o = self._partition(workload)
         t1 = time.time()
+        self._debug_placement(workload, d2w, d2i)
         cu = assign_local_buffer_indices(workload, d2i, d2o)
         fw_plans, _ = schedule(self.context, workload, self.context.comm_cost_model, self.logger, True,
                                cfg.pipeline_algo, cfg.n_stages)

@@ -11,6 +11,9 @@ on their order.
 """
 from __future__ import annotations
 
+import json
+import os
+
 from collections import defaultdict
 from typing import Dict, List, Optional, Sequence, Tuple
 
@@ -24,7 +27,7 @@ from ..core.cost_model import CommunicationCostModel
 from ..core.instructions import (AttnBackwardInstr, AttnInstr, AttnReductionInstr, BarrierInstr, BufferBlock,
                                  BufferInfo, BufferType, CommLaunchInstr, CommOp, CommType, CommWaitInstr, DType,
                                  ExecutionPlan, MemcpyInstr, ReductionOp, SumInstr, SumOp)
-from .stages import default_n_stages, generate_pipelines_n_stages
+from .stages import default_n_stages, generate_pipelines_n_stages, pipeline_chrome_trace, summarize_pipeline
 
 # block type -> (local buffer, paged buffer)
 _BUFFERS = {
@@ -115,6 +118,7 @@ def schedule(context: ExecutionContext, workload: WorkloadSpec, comm_cost_model:
                                      wl.input_sizes, wl.work_to_device_map, wl.input_to_device_map,
                                      not is_forward, logger)
     n_total = len(work_ps)
+    _debug_pipeline(work_ps, comm_ps, wl, comm_cost_model, logger, is_forward)
     work_to_stage = {w: s for s, per_dev in enumerate(work_ps) for ws in per_dev.values() for w in ws}
     wl.work_to_stage_map = dict(work_to_stage)
     builders = {d: _DeviceBuilder(d) for d in devices}
@@ -205,7 +209,62 @@ def schedule(context: ExecutionContext, workload: WorkloadSpec, comm_cost_model:
     plans = {}
     for d in devices:
         plans[d] = _finish_plan(context, wl, d, builders[d], n_total, is_forward, block_size)
+    _debug_plans(plans, logger, is_forward)
     return plans, work_to_stage
+
+
+# ------------------------------------------------------------------------------------ debug output
+def _env_on(name: str) -> bool:
+    return os.environ.get(name, "0") not in ("0", "", "false", "False")
+
+
+def _debug_dir() -> str:
+    d = os.environ.get("DCP_LOGGING_DEBUG_DIR", "./debug")
+    os.makedirs(d, exist_ok=True)
+    return d
+
+
+def _debug_pipeline(work_ps, comm_ps, wl, comm_cost_model, logger, is_forward: bool) -> None:
+    """DCP_LOG_PIPELINE: per-stage summary in the log; DCP_DUMP_PIPELINE: chrome trace of the
+    modelled timeline (dcp/core/pipeline.py:349-510)."""
+    tag = "fw" if is_forward else "bw"
+    if _env_on("DCP_LOG_PIPELINE") and logger is not None:
+        for row in summarize_pipeline(work_ps, comm_ps, wl.workloads, wl.input_sizes):
+            logger.info("pipeline %s %s", tag, row)
+    if _env_on("DCP_DUMP_PIPELINE") and comm_cost_model is not None:
+        path = os.path.join(_debug_dir(), f"pipeline_{tag}.json")
+        with open(path, "w") as f:
+            json.dump({"traceEvents": pipeline_chrome_trace(work_ps, comm_ps, wl.workloads, wl.input_sizes,
+                                                            comm_cost_model)}, f)
+
+
+def _debug_plans(plans, logger, is_forward: bool) -> None:
+    """DCP_LOG_SCHEDULE / DCP_LOG_INSTRS: instruction listing per device; DCP_LOG_BUFFER_INFO: buffer
+    sizes per device; DCP_DEBUG_DUMP_EP_STATS: instruction and byte counts as json (file prefix
+    DCP_DEBUG_DUMP_EP_STATS_PREFIX)."""
+    tag = "fw" if is_forward else "bw"
+    if logger is not None and (_env_on("DCP_LOG_SCHEDULE") or _env_on("DCP_LOG_INSTRS")):
+        for d, plan in sorted(plans.items()):
+            logger.info("plan %s device %s: %d instructions", tag, d, len(plan.instructions))
+            for k, ins in enumerate(plan.instructions):
+                logger.info("  [%03d] %s", k, ins)
+    if logger is not None and _env_on("DCP_LOG_BUFFER_INFO"):
+        for d, plan in sorted(plans.items()):
+            logger.info("buffers %s device %s: %s", tag, d, plan.buffer_info)
+    if _env_on("DCP_DEBUG_DUMP_EP_STATS"):
+        stats = {}
+        for d, plan in sorted(plans.items()):
+            kinds: Dict[str, int] = defaultdict(int)
+            sent = 0
+            for ins in plan.instructions:
+                kinds[type(ins).__name__] += 1
+                if isinstance(ins, CommLaunchInstr):
+                    sent += sum(op.buffer_block.n_tokens for op in ins.comm_ops if op.comm_type == CommType.SEND)
+            stats[f"{d[0]}.{d[1]}"] = {"instructions": dict(kinds), "tokens_sent": sent,
+                                      "serialized_bytes": len(plan.serialize())}
+        prefix = os.environ.get("DCP_DEBUG_DUMP_EP_STATS_PREFIX", os.path.join(_debug_dir(), "ep_stats"))
+        with open(f"{prefix}_{tag}.json", "w") as f:
+            json.dump(stats, f, indent=1)
 
 
 # --------------------------------------------------------------------------------------- attention rows

@@ -49,6 +49,13 @@ class FusedAttentionExecutor:
         self.kernel_launches = 0
         self.profile = os.environ.get("DCP_B200_PROFILE", "0") == "1"
         self._marks = []
+        # debugging aids: synchronous = wait for the device and read the status word after every
+        # phase (the reference executor's synchronous mode, dcp/core/executor.py:55-57); poison =
+        # fill every staging region with a large sentinel before a call, so a block that is read
+        # without having been pulled or written this call blows up the result instead of silently
+        # reusing last call's bytes
+        self.synchronous = os.environ.get("DCP_B200_SYNCHRONOUS", "0") == "1"
+        self.poison = os.environ.get("DCP_B200_POISON", "0") == "1"
 
     def _allocate(self, rows) -> None:
         """(Re)create the symmetric arenas for (q rows, kv rows, partial rows).  Collective: every
@@ -127,10 +134,33 @@ class FusedAttentionExecutor:
     # ---- optional phase timing (DCP_B200_PROFILE=1): CUDA events on the main stream around the
     # barriers and the kernels of every call; read with profile_summary() after a synchronize
     def _mark(self, key: str) -> None:
+        # phase boundary: an NVTX marker for any attached profiler, the synchronous-mode check, and
+        # (when profiling) a CUDA event
+        start = key.endswith(":start")
+        if start:
+            torch.cuda.nvtx.range_push("dcp.attention." + key.split(":")[0])
+        else:
+            torch.cuda.nvtx.mark(key)
+        if self.synchronous and not start:
+            torch.cuda.synchronize(self.device)
+            self.check_status()
         if self.profile:
             ev = torch.cuda.Event(enable_timing=True)
             ev.record(torch.cuda.current_stream(self.device))
             self._marks.append((key, ev))
+
+    def _poison_staging(self, with_grads: bool) -> None:
+        # a large finite sentinel, not NaN: rows of a tile past a block's valid tokens are read and
+        # multiplied by exact zeros, which a NaN would survive
+        p = self.program
+        nan = 30000.0
+        self.q[p.q_local_rows:].fill_(nan)
+        self.kv[p.kv_local_rows:].fill_(nan)
+        if with_grads:
+            self.dout[p.q_local_rows:].fill_(nan)
+        else:
+            self.part_out.fill_(nan)
+            self.part_lse.fill_(nan)
 
     def profile_summary(self) -> dict:
         """Total milliseconds per phase since the last call ("fwd:kernels", "bwd:wait peers", ...)."""
@@ -151,6 +181,8 @@ class FusedAttentionExecutor:
         p, a = self.program, self.arena
         main = torch.cuda.current_stream(self.device)
         self._mark("fwd:start")
+        if self.poison:
+            self._poison_staging(False)
         a.barrier()                                   # every rank's inputs are in place
         self._mark("fwd:wait inputs of peers")
         ready = []
@@ -179,6 +211,7 @@ class FusedAttentionExecutor:
             block_ops.merge_out_lse(self.merge_ops, self.merge_src, self.part_out, self.part_lse, self.out, self.lse)
             self.kernel_launches += 1
         self._mark("fwd:merge")
+        torch.cuda.nvtx.range_pop()
         self._staging_valid = True
         return self.out_local(), self.lse_local()
 
@@ -196,6 +229,8 @@ class FusedAttentionExecutor:
         main = torch.cuda.current_stream(self.device)
         n = p.q_local_rows
         self._mark("bwd:start")
+        if self.poison and not self._staging_valid:
+            self._poison_staging(True)
         self.dout[:n].copy_(dout_local.reshape(n, self.hq, HEAD_DIM))
         attn_ops.attn_delta(self.out, self.dout, self.delta, 0, n)
         self.dq[:p.q_rows].zero_()
@@ -230,6 +265,7 @@ class FusedAttentionExecutor:
             self._mark("bwd:push gradients to owners")
             a.barrier()
             self._mark("bwd:wait gradients of peers")
+        torch.cuda.nvtx.range_pop()
         return self.dq[:n], self.dkv[:p.kv_local_rows]
 
     def check_status(self) -> None:

@@ -47,6 +47,12 @@ class EngineConfig:
     planner_workers: int = 2
     lookahead: int = 3
     lm_head_chunk: int = 4096
+    head_block_size: int = 0
+    use_block_size_heuristic: bool = False
+    mem_imbalance_epsilon: Optional[float] = None
+    comp_imbalance_epsilon: Optional[float] = None
+    inter_node_comp_imbalance_factor: Optional[float] = None
+    cost_model: Optional[dict] = None
 
 
 class TrainEngine:
@@ -81,7 +87,11 @@ class TrainEngine:
         self.model.set_executor(self.executor)
         self.activation_levels = self._plan_activations(group_tokens // dcp)
         self.spec = PlanSpec(self.world, dcp, cfg.tokens_per_step, m.n_heads, m.n_kv_heads, m.head_dim, cfg.block_size,
-                             0, cfg.mask, cfg.length_dist or synth.LOGNORMAL_8K, m.vocab, cfg.seed, cfg.n_stages)
+                             cfg.head_block_size, cfg.mask, cfg.length_dist or synth.LOGNORMAL_8K, m.vocab, cfg.seed,
+                             cfg.n_stages, mem_imbalance_epsilon=cfg.mem_imbalance_epsilon,
+                             comp_imbalance_epsilon=cfg.comp_imbalance_epsilon,
+                             inter_node_comp_imbalance_factor=cfg.inter_node_comp_imbalance_factor,
+                             use_block_size_heuristic=cfg.use_block_size_heuristic, cost_model=cfg.cost_model)
         self.plans = PlanService(self.spec, self.rank, cfg.planner_workers, cfg.lookahead)
         self.iteration = 0
         self.h2d_bytes = 0
@@ -203,25 +213,66 @@ def init_distributed():
     return rank, world, local, group
 
 
+def add_dcp_args(ap: argparse.ArgumentParser) -> None:
+    """The reference's ``--dcp-*`` training flags (benchmark/mlm/dcp_args.py:1-42), same names and
+    meanings.  Cost-model and tolerance flags default to None = this framework's B200 defaults."""
+    g = ap.add_argument_group("dcp")
+    g.add_argument("--disable-dcp", action="store_true",
+                   help="no context parallelism: every rank is its own group (pure data parallel)")
+    g.add_argument("--dcp-intra-node-lat", type=float, default=None, help="ms")
+    g.add_argument("--dcp-intra-node-bw", type=float, default=None, help="Gbps")
+    g.add_argument("--dcp-inter-node-lat", type=float, default=None, help="ms")
+    g.add_argument("--dcp-inter-node-bw", type=float, default=None, help="Gbps")
+    g.add_argument("--dcp-max-tflops", type=float, default=None)
+    g.add_argument("--dcp-max-mem-bw", type=float, default=None, help="GB/s")
+    g.add_argument("--dcp-prefetch-planner-num-workers", type=int, default=2)
+    g.add_argument("--dcp-prefetch-listener-num-workers", type=int, default=1,
+                   help="accepted for compatibility: plans are computed per rank, nothing is listened for")
+    g.add_argument("--dcp-block-size", type=int, default=2048)
+    g.add_argument("--dcp-head-block-size", type=int, default=0, help="0 = all heads of a rank in one block")
+    g.add_argument("--dcp-use-block-size-heuristic", type=int, default=0)
+    g.add_argument("--dcp-mem-imbalance-epsilon", type=float, default=None)
+    g.add_argument("--dcp-comp-imbalance-epsilon", type=float, default=None)
+    g.add_argument("--dcp-inter-node-comp-imbalance-factor", type=float, default=None)
+    g.add_argument("--dcp-global-batch-size-in-tokens", type=int, default=131072)
+    g.add_argument("--dcp-dataset-split", default="train", help="used by dataset-backed loaders; synthetic data ignores it")
+    g.add_argument("--dcp-dataset-text-key", default="text")
+    g.add_argument("--dcp-use-cudagraph", action="store_true",
+                   help="accepted for compatibility: per-iteration kernel tables make every step's launch list "
+                        "different, and the fused executor already issues only a handful of launches per layer")
+    g.add_argument("--dcp-mask-type", default="causal")
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser(description="Synthetic-data DCP training loop")
     ap.add_argument("--model", default="llama3-8b", choices=["llama3-8b", "tiny"])
     ap.add_argument("--iters", type=int, default=10)
-    ap.add_argument("--tokens-per-step", type=int, default=131072)
-    ap.add_argument("--dcp-size", type=int, default=0)
-    ap.add_argument("--dcp-block-size", type=int, default=2048)
-    ap.add_argument("--dcp-mask-type", default="causal")
+    ap.add_argument("--tokens-per-step", type=int, default=None, help="alias of --dcp-global-batch-size-in-tokens")
+    ap.add_argument("--dcp-size", type=int, default=0, help="ranks per context-parallel group (0 = all ranks)")
     ap.add_argument("--length-dist", default="lognormal8k", choices=["lognormal8k", "lognormal16k", "mixture"])
     ap.add_argument("--lr", type=float, default=3e-4)
     ap.add_argument("--log-interval", type=int, default=1)
     ap.add_argument("--save", default=None)
     ap.add_argument("--load", default=None)
+    ap.add_argument("--activation-budget-gb", type=float, default=None)
+    add_dcp_args(ap)
     args = ap.parse_args(argv)
     rank, world, local, group = init_distributed()
     dists = {"lognormal8k": synth.LOGNORMAL_8K, "lognormal16k": synth.LOGNORMAL_16K, "mixture": synth.MIXTURE}
     model = LLAMA3_8B if args.model == "llama3-8b" else tiny_config()
-    cfg = EngineConfig(model, args.tokens_per_step, args.dcp_size, args.dcp_block_size, args.dcp_mask_type,
-                       dists[args.length_dist], lr=args.lr)
+    tokens = args.tokens_per_step or args.dcp_global_batch_size_in_tokens
+    cost = {"intra_node_lat": args.dcp_intra_node_lat, "intra_node_bw": args.dcp_intra_node_bw,
+            "inter_node_lat": args.dcp_inter_node_lat, "inter_node_bw": args.dcp_inter_node_bw,
+            "max_tflops": args.dcp_max_tflops, "max_mem_bw": args.dcp_max_mem_bw}
+    cfg = EngineConfig(model, tokens, 1 if args.disable_dcp else args.dcp_size, args.dcp_block_size, args.dcp_mask_type,
+                       dists[args.length_dist], lr=args.lr, planner_workers=args.dcp_prefetch_planner_num_workers,
+                       head_block_size=args.dcp_head_block_size,
+                       use_block_size_heuristic=bool(args.dcp_use_block_size_heuristic),
+                       mem_imbalance_epsilon=args.dcp_mem_imbalance_epsilon,
+                       comp_imbalance_epsilon=args.dcp_comp_imbalance_epsilon,
+                       inter_node_comp_imbalance_factor=args.dcp_inter_node_comp_imbalance_factor,
+                       cost_model=cost if any(v is not None for v in cost.values()) else None,
+                       activation_budget_gb=args.activation_budget_gb)
     eng = TrainEngine(cfg, torch.device("cuda", local), group)
     if args.load:
         eng.load_checkpoint(args.load)

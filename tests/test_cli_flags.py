@@ -1,0 +1,47 @@
+"""The reference's --dcp-* flag set is accepted with the same names, and the planner knobs they
+carry reach the plans."""
+import argparse
+
+import numpy as np
+
+from dcp_b200.data import synth
+from dcp_b200.data.plan_service import PlanSpec, plan_iteration
+from dcp_b200.train import add_dcp_args
+
+REFERENCE_FLAGS = [
+    "--disable-dcp", "--dcp-intra-node-lat", "--dcp-intra-node-bw", "--dcp-inter-node-lat", "--dcp-inter-node-bw",
+    "--dcp-max-tflops", "--dcp-max-mem-bw", "--dcp-prefetch-planner-num-workers",
+    "--dcp-prefetch-listener-num-workers", "--dcp-block-size", "--dcp-head-block-size",
+    "--dcp-use-block-size-heuristic", "--dcp-mem-imbalance-epsilon", "--dcp-comp-imbalance-epsilon",
+    "--dcp-inter-node-comp-imbalance-factor", "--dcp-global-batch-size-in-tokens", "--dcp-dataset-split",
+    "--dcp-dataset-text-key", "--dcp-use-cudagraph", "--dcp-mask-type",
+]
+
+
+def test_every_reference_flag_is_accepted():
+    ap = argparse.ArgumentParser()
+    add_dcp_args(ap)
+    known = {s for a in ap._actions for s in a.option_strings}
+    assert not [f for f in REFERENCE_FLAGS if f not in known]
+    a = ap.parse_args(["--dcp-block-size", "512", "--dcp-mask-type", "lambda", "--dcp-comp-imbalance-epsilon", "0.1",
+                       "--dcp-max-tflops", "900", "--dcp-use-block-size-heuristic", "1", "--disable-dcp"])
+    assert (a.dcp_block_size, a.dcp_mask_type, a.dcp_comp_imbalance_epsilon, a.dcp_max_tflops) == (512, "lambda", 0.1, 900.0)
+    assert a.disable_dcp and a.dcp_use_block_size_heuristic == 1
+
+
+def _spec(**kw):
+    return PlanSpec(world=4, dcp_size=4, tokens_per_step=16384, n_heads=8, n_kv_heads=2, block_size=512,
+                    length_dist=synth.LengthDist("lognormal", 3000.0, 0.8, 128, 16384), vocab=1000, **kw)
+
+
+def test_planner_knobs_reach_the_plans():
+    loose = [plan_iteration(_spec(mem_imbalance_epsilon=0.5, comp_imbalance_epsilon=0.5), 1, r) for r in range(4)]
+    tight = [plan_iteration(_spec(mem_imbalance_epsilon=0.02, comp_imbalance_epsilon=0.02), 1, r) for r in range(4)]
+    for plans in (loose, tight):
+        assert sum(p.tokens.numel() for p in plans) == plans[0].n_global_tokens
+    spread = lambda plans: np.ptp([p.tokens.numel() for p in plans])
+    assert spread(tight) <= spread(loose)
+    # cost-model overrides and the block-size heuristic are accepted and still give a complete plan
+    alt = [plan_iteration(_spec(cost_model={"max_tflops": 500.0, "intra_node_bw": 2400.0},
+                                use_block_size_heuristic=True), 1, r) for r in range(4)]
+    assert sum(p.tokens.numel() for p in alt) == alt[0].n_global_tokens

@@ -29,8 +29,10 @@ def test_fused_executor_two_gpus():
         pytest.skip("needs two GPUs")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
            "127.0.0.1", "--master-port", "29541", os.path.join(ROOT, "tests", "fused_worker.py")]
+    # also exercises the executor's debugging modes: a status check after every phase, and staging
+    # regions filled with a sentinel before every call (an un-pulled block would wreck the result)
     res = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=900,
-                         env=dict(os.environ, PYTHONPATH=ROOT))
+                         env=dict(os.environ, PYTHONPATH=ROOT, DCP_B200_SYNCHRONOUS="1", DCP_B200_POISON="1"))
     assert res.returncode == 0 and "FUSED_OK" in res.stdout, res.stdout[-3000:]
 
 

@@ -207,6 +207,37 @@ def test_gather_push_cast(dev):
     assert torch.equal(bf, acc.bfloat16())
 
 
+def test_corrupt_tables_are_reported_not_executed(dev):
+    """A table entry that points outside its arena makes the kernel set the bad-arguments status
+    and skip the work; nothing is stored out of range and the context stays usable."""
+    torch.manual_seed(0)
+    nq, bs, hq, hkv = 256, 256, 4, 2
+    q = torch.randn(nq + 128, hq, 128, device=dev).bfloat16()
+    kv = torch.randn(bs + 128, 2, hkv, 128, device=dev).bfloat16()
+    dout = torch.randn_like(q)
+    out = torch.zeros_like(q)
+    lse = torch.zeros(hq, nq + 128, device=dev)
+    delta = torch.zeros_like(lse)
+    rng = _ranges("causal", nq, 0)
+    row = A.AttnRow(0, nq, list(range(hq)), [(0, bs)], rng)
+    tabs = A.build_fwd_tables([row], bs, dev)
+    tabs.tiles[0, 7] = 1 << 28                       # out_row far past the destination
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    A.attn_fwd(q, kv, tabs, [out], [lse], 128 ** -0.5, status, 0)
+    torch.cuda.synchronize()
+    assert status.item() == 3
+    bt = A.build_bwd_tables([row], bs, hq, hkv, dev)
+    bt.items[0, 5] = 1 << 28                         # dq_row far past the accumulator
+    status.zero_()
+    dq = torch.zeros(nq + 128, hq, 128, device=dev)
+    dkv = torch.zeros(bs + 128, 2, hkv, 128, device=dev)
+    A.attn_bwd(q, dout, kv, lse, delta, bt, [dq], [dkv], 128 ** -0.5, status)
+    torch.cuda.synchronize()
+    assert status.item() == 3
+    assert torch.isfinite(dq).all() and torch.isfinite(dkv).all()
+    assert torch.ones(4, device=dev).sum().item() == 4
+
+
 def test_barrier_wait_is_bounded(dev):
     """A peer flag nobody sets: the barrier kernel gives up after its deadline and reports it."""
     flags = torch.zeros(64, dtype=torch.int32, device=dev)

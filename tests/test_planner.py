@@ -196,3 +196,25 @@ def test_block_size_heuristic_and_cost_models():
     assert (c.n_nodes, c.n_devices_per_node) == (2, 4) and rest == b""
     ms, _ = ModelSpec.deserialize(ModelSpec(128, 32, 8).serialize())
     assert ms == ModelSpec(128, 32, 8)
+
+
+def test_debug_env_flags_write_their_artifacts(tmp_path, monkeypatch):
+    """The planner's DCP_* debug switches: pipeline chrome trace, plan statistics, block map."""
+    import json
+    for name in ("DCP_DUMP_PIPELINE", "DCP_LOG_PIPELINE", "DCP_LOG_SCHEDULE", "DCP_LOG_BUFFER_INFO",
+                 "DCP_DEBUG_DUMP_EP_STATS", "DCP_LOG_GRAPH_PARTITION", "DCP_LOG_WORKLOAD_SPEC",
+                 "DCP_DEBUG_VISUALIZE_WORKLOAD_SPEC"):
+        monkeypatch.setenv(name, "1")
+    monkeypatch.setenv("DCP_LOGGING_DEBUG_DIR", str(tmp_path))
+    monkeypatch.setenv("DCP_DEBUG_DUMP_EP_STATS_PREFIX", str(tmp_path / "ep"))
+    ctx = get_default_execution_context(4, 1)
+    wl, _, _ = _workload([1500, 700, 400, 130], 128, hbs=4, ctx=ctx)
+    fw_wl, bw_wl, fw, bw = InstrCompiler(ctx, iteration_idx=7).compile(wl)
+    for tag in ("fw", "bw"):
+        trace = json.load(open(tmp_path / f"pipeline_{tag}.json"))["traceEvents"]
+        assert trace and all(e["ph"] == "X" for e in trace)
+        stats = json.load(open(tmp_path / f"ep_{tag}.json"))
+        assert set(stats) == {"0.0", "0.1", "0.2", "0.3"}
+        assert all(v["serialized_bytes"] > 0 and v["instructions"] for v in stats.values())
+    fig = json.load(open(tmp_path / "workload_iter7.json"))
+    assert any(n["kind"] == "WORK" for n in fig["nodes"]) and fig["edges"]
