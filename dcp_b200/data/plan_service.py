@@ -88,14 +88,26 @@ def split_batch_over_groups(seqlens: Sequence[int], n_groups: int) -> List[List[
 def plan_iteration(spec: PlanSpec, iteration: int, rank: int) -> RankPlan:
     """Synthesise iteration ``iteration``'s batch from the spec's length distribution and plan it."""
     seed = spec.seed * 1000003 + iteration
-    seqlens = synth.sample_seqlens(spec.tokens_per_step, spec.length_dist, seed)
+    n_groups = spec.world // spec.dcp_size
+    members = None
+    if n_groups > 1:
+        # data parallel over context-parallel groups: every group draws its own sub-batch with an
+        # equal token budget (equal dense work per rank), as independent data-parallel replicas do
+        seqlens, members = [], []
+        for g in range(n_groups):
+            part = synth.sample_seqlens(spec.tokens_per_step // n_groups, spec.length_dist, seed * 64 + g + 1)
+            members.append(list(range(len(seqlens), len(seqlens) + len(part))))
+            seqlens += part
+    else:
+        seqlens = synth.sample_seqlens(spec.tokens_per_step, spec.length_dist, seed)
     batch = synth.make_token_batch(seqlens, spec.vocab, seed)
     info = synth.assign_mask_kinds(seqlens, seed) if spec.mask == "mixed" else None
-    return plan_batch(spec, iteration, rank, seqlens, batch, info)
+    return plan_batch(spec, iteration, rank, seqlens, batch, info, group_members=members)
 
 
 def plan_batch(spec: PlanSpec, iteration: int, rank: int, seqlens: Sequence[int], batch: Dict[str, np.ndarray],
-               mask_fn_info: Optional[List[dict]] = None, mask_fn=None) -> RankPlan:
+               mask_fn_info: Optional[List[dict]] = None, mask_fn=None,
+               group_members: Optional[List[List[int]]] = None) -> RankPlan:
     """Plan one packed batch (``batch`` holds per-token arrays over the concatenated sequences) and
     return rank ``rank``'s share: its fused program, its tokens in local buffer order and, when
     requested, its instruction plans."""
@@ -103,7 +115,10 @@ def plan_batch(spec: PlanSpec, iteration: int, rank: int, seqlens: Sequence[int]
     seqlens = [int(x) for x in seqlens]
     n_groups = spec.world // spec.dcp_size
     group_id, group_rank = divmod(rank, spec.dcp_size)
-    members = split_batch_over_groups(seqlens, n_groups)[group_id] if n_groups > 1 else list(range(len(seqlens)))
+    if group_members is not None:
+        members = group_members[group_id]
+    else:
+        members = split_batch_over_groups(seqlens, n_groups)[group_id] if n_groups > 1 else list(range(len(seqlens)))
     raw = [seqlens[i] for i in members]
     cu_all = seq_token_offsets(seqlens)
     bs = spec.block_size
