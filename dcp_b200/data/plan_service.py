@@ -13,6 +13,7 @@ from __future__ import annotations
 
 import concurrent.futures as cf
 import multiprocessing as mp
+import os
 import time
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Sequence
@@ -54,6 +55,7 @@ class PlanSpec:
     inter_node_comp_imbalance_factor: Optional[float] = None
     use_block_size_heuristic: bool = False
     cost_model: Optional[dict] = None       # intra/inter node latency + bandwidth, max_tflops, max_mem_bw
+    cache_dir: Optional[str] = None         # plans are stored here by batch signature and reused (e.g. after a resume)
 
 
 @dataclass
@@ -102,7 +104,39 @@ def plan_iteration(spec: PlanSpec, iteration: int, rank: int) -> RankPlan:
         seqlens = synth.sample_seqlens(spec.tokens_per_step, spec.length_dist, seed)
     batch = synth.make_token_batch(seqlens, spec.vocab, seed)
     info = synth.assign_mask_kinds(seqlens, seed) if spec.mask == "mixed" else None
+    if spec.cache_dir:
+        return _cached_plan(spec, iteration, rank, seqlens, batch, info, members)
     return plan_batch(spec, iteration, rank, seqlens, batch, info, group_members=members)
+
+
+def batch_signature(spec: PlanSpec, rank: int, seqlens: Sequence[int], mask_fn_info, group_members) -> str:
+    """Stable key of everything a rank's plan depends on (the iteration number is not part of it:
+    the same batch planned at another step gives the same plan)."""
+    import hashlib
+    fields = {k: v for k, v in vars(spec).items() if k not in ("cache_dir", "seed")}
+    fields["length_dist"] = vars(spec.length_dist) if hasattr(spec.length_dist, "__dict__") else str(spec.length_dist)
+    text = repr((sorted(fields.items(), key=lambda kv: kv[0]), rank, list(map(int, seqlens)), mask_fn_info, group_members))
+    return hashlib.sha1(text.encode()).hexdigest()
+
+
+def _cached_plan(spec, iteration, rank, seqlens, batch, mask_fn_info, group_members):
+    """Plan-cache lookup / fill around ``plan_batch``; token arrays are re-derived from the batch on
+    every call, so only planning work is saved."""
+    import pickle
+    key = batch_signature(spec, rank, seqlens, mask_fn_info, group_members)
+    path = os.path.join(spec.cache_dir, f"plan_{key}.pkl")
+    if os.path.exists(path):
+        with open(path, "rb") as f:
+            plan = pickle.load(f)
+        plan.iteration = iteration
+        return plan
+    plan = plan_batch(spec, iteration, rank, seqlens, batch, mask_fn_info, group_members=group_members)
+    os.makedirs(spec.cache_dir, exist_ok=True)
+    tmp = f"{path}.{os.getpid()}.tmp"
+    with open(tmp, "wb") as f:
+        pickle.dump(plan, f)
+    os.replace(tmp, path)            # atomic: a concurrent reader never sees a partial file
+    return plan
 
 
 def plan_batch(spec: PlanSpec, iteration: int, rank: int, seqlens: Sequence[int], batch: Dict[str, np.ndarray],

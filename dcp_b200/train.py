@@ -53,6 +53,7 @@ class EngineConfig:
     comp_imbalance_epsilon: Optional[float] = None
     inter_node_comp_imbalance_factor: Optional[float] = None
     cost_model: Optional[dict] = None
+    plan_cache_dir: Optional[str] = None     # reuse plans by batch signature (saved next to checkpoints on resume)
 
 
 class TrainEngine:
@@ -91,7 +92,8 @@ class TrainEngine:
                              cfg.n_stages, mem_imbalance_epsilon=cfg.mem_imbalance_epsilon,
                              comp_imbalance_epsilon=cfg.comp_imbalance_epsilon,
                              inter_node_comp_imbalance_factor=cfg.inter_node_comp_imbalance_factor,
-                             use_block_size_heuristic=cfg.use_block_size_heuristic, cost_model=cfg.cost_model)
+                             use_block_size_heuristic=cfg.use_block_size_heuristic, cost_model=cfg.cost_model,
+                             cache_dir=cfg.plan_cache_dir)
         self.plans = PlanService(self.spec, self.rank, cfg.planner_workers, cfg.lookahead)
         self.iteration = 0
         self.h2d_bytes = 0
@@ -167,6 +169,8 @@ class TrainEngine:
         path = os.path.join(directory, f"rank{self.rank:03d}.pt")
         state = {"iteration": self.iteration, "optimizer": self.optimizer.state_dict(),
                  "model_cfg": self.cfg.model.__dict__, "world": self.world, "seed": self.cfg.seed,
+                 "plan_spec": {k: v for k, v in vars(self.spec).items() if k != "length_dist"},
+                 "length_dist": vars(self.spec.length_dist),
                  "rng": torch.get_rng_state(), "cuda_rng": torch.cuda.get_rng_state(self.device)}
         if self.rank == 0:
             state["params_bf16"] = self.bufs.params

@@ -171,3 +171,26 @@ def test_visualization_and_logger(tmp_path, monkeypatch):
     assert "hello" in (tmp_path / "x" / "y.log").read_text()
     monkeypatch.setenv("N", "7")
     assert read_env_int("N") == 7 and read_env_int("NOPE", 3) == 3 and "Tensor(shape=(2,)" in trepr(torch.zeros(2))
+
+
+def test_plan_cache_reuses_plans_by_batch_signature(tmp_path):
+    from dcp_b200.data import synth
+    from dcp_b200.data.plan_service import PlanSpec, batch_signature, plan_iteration
+    mk = lambda **kw: PlanSpec(world=2, dcp_size=2, tokens_per_step=8192, n_heads=8, n_kv_heads=2, block_size=512,
+                               length_dist=synth.LengthDist("lognormal", 2000.0, 0.8, 128, 8192), vocab=1000, **kw)
+    spec = mk(cache_dir=str(tmp_path))
+    first = plan_iteration(spec, 3, 1)
+    files = sorted(p.name for p in tmp_path.iterdir())
+    assert len(files) == 1 and files[0].startswith("plan_")
+    again = plan_iteration(spec, 3, 1)
+    assert len(list(tmp_path.iterdir())) == 1
+    assert torch.equal(first.tokens, again.tokens) and torch.equal(first.positions, again.positions)
+    for a, b in zip(first.program.q_pulls + first.program.kv_pulls, again.program.q_pulls + again.program.kv_pulls):
+        assert (a == b).all()
+    uncached = plan_iteration(mk(), 3, 1)
+    assert torch.equal(uncached.tokens, first.tokens)
+    # another rank, another batch or another block size is another key
+    s0 = batch_signature(spec, 0, [100, 200], None, None)
+    assert s0 != batch_signature(spec, 1, [100, 200], None, None)
+    assert s0 != batch_signature(spec, 0, [100, 201], None, None)
+    assert s0 != batch_signature(mk(cache_dir=str(tmp_path), mem_imbalance_epsilon=0.2), 0, [100, 200], None, None)
