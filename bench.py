@@ -99,6 +99,7 @@ def main() -> None:
     ap.add_argument("--config", default="scaling", choices=["scaling", "causal131k", "masks"])
     ap.add_argument("--model", default="llama3-8b", choices=["llama3-8b", "tiny"])
     ap.add_argument("--dcp-size", type=int, default=0, help="ranks per context-parallel group (0 = all)")
+    ap.add_argument("--tp-size", type=int, default=1, help="tensor-parallel ranks per model replica")
     ap.add_argument("--tokens-per-gpu", type=int, default=32768)
     ap.add_argument("--block-size", type=int, default=2048)
     ap.add_argument("--stages", type=int, default=None)
@@ -126,7 +127,7 @@ def main() -> None:
         tokens, dist_, mask, scaling = 131072, synth.LOGNORMAL_8K, "causal", "strong"
     else:
         tokens, dist_, mask, scaling = 131072, synth.LOGNORMAL_16K, "mixed", "strong"
-    cfg = EngineConfig(model, tokens, args.dcp_size, args.block_size, mask, dist_, n_stages=args.stages, activation_budget_gb=args.activation_budget_gb,
+    cfg = EngineConfig(model, tokens, args.dcp_size, args.block_size, mask, dist_, n_stages=args.stages, activation_budget_gb=args.activation_budget_gb, tp_size=args.tp_size,
                        planner_workers=2, lookahead=args.steps + 1)
     eng = TrainEngine(cfg, dev, group)
     W, K = args.warmup, args.steps
@@ -197,8 +198,9 @@ def main() -> None:
         "%d recompute no GEMM (chosen from free memory)" % (lv.count(0), lv.count(1), lv.count(2)))
     if rank == 0:
         value = tokens_timed / (dev_ms / 1e3)
-        dcp = cfg.dcp_size or world
-        par = f"cp{dcp}" if dcp == world else f"cp{dcp}xdp{world // dcp}"
+        tp = max(1, cfg.tp_size)
+        dcp = cfg.dcp_size or world // tp
+        par = f"cp{dcp}" + (f"xdp{world // tp // dcp}" if dcp * tp != world else "") + (f"xtp{tp}" if tp > 1 else "")
         out = {
             "metric": "training tokens/s (device-timed, max over ranks)", "value": round(value, 1), "unit": "tokens/s",
             "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": round(dev_ms / K, 2), "higher_is_better": True,

@@ -51,6 +51,15 @@ class LlamaConfig:
         return 2 * self.vocab * self.hidden + self.n_layers * per_layer + self.hidden
 
 
+    def shard(self, tp: int) -> "LlamaConfig":
+        """The slice of the model one tensor-parallel rank holds: 1/tp of the query heads, KV heads
+        and FFN channels; hidden size, vocabulary and layer count unchanged."""
+        assert self.n_heads % tp == 0 and self.n_kv_heads % tp == 0 and self.ffn % tp == 0, \
+            "tensor parallelism must divide the head counts and the FFN width"
+        return LlamaConfig(self.n_layers, self.hidden, self.n_heads // tp, self.n_kv_heads // tp, self.head_dim,
+                           self.ffn // tp, self.vocab, self.rope_theta, self.eps, self.init_std)
+
+
 LLAMA3_8B = LlamaConfig()
 
 
@@ -126,12 +135,12 @@ class _DecoderLayerFn(torch.autograd.Function):
         out, lse = ex.forward()
         a = out.reshape(T, -1).clone()
         lse_c = lse.clone()
-        x_mid = torch.addmm(x, a, p[f"l{l}.wo"].t())
+        x_mid = model.row_parallel(x, a, p[f"l{l}.wo"])
         h2, rstd2 = model_ops.rmsnorm_fwd_raw(x_mid, p[f"l{l}.norm2"], cfg.eps)
         gu = torch.mm(h2, p[f"l{l}.wgu"].t())
         del h2
         act = model_ops.swiglu_fwd_raw(gu)
-        y = torch.addmm(x_mid, act, p[f"l{l}.wd"].t())
+        y = model.row_parallel(x_mid, act, p[f"l{l}.wd"])
         ctx.model, ctx.l, ctx.level, ctx.epoch = model, l, level, ex.arena_epoch
         keep = [x, cos, sin, a, lse_c, rstd1]
         if level >= 1:
@@ -170,7 +179,7 @@ class _DecoderLayerFn(torch.autograd.Function):
             h1, _ = model_ops.rmsnorm_fwd_raw(x, w1, cfg.eps)
             qkv = torch.mm(h1, wqkv.t())
             del h1
-            x_mid = torch.addmm(x, a, wo.t())
+            x_mid = model.row_parallel(x, a, wo)
             rstd2 = None
         # ---- MLP
         h2, rstd2_new = model_ops.rmsnorm_fwd_raw(x_mid, w2, cfg.eps)
@@ -182,7 +191,7 @@ class _DecoderLayerFn(torch.autograd.Function):
         del act
         dgu = model_ops.swiglu_bwd_raw(gu, dact)
         del dact, gu
-        dh2 = torch.mm(dgu, wgu)
+        dh2 = model.tp_sum(torch.mm(dgu, wgu))     # the norm output feeds every rank's gate/up shard
         wgrad(wgu, dgu.t(), h2)
         del dgu, h2
         dx_mid, dw2 = model_ops.rmsnorm_bwd_raw(x_mid, w2, rstd2, dh2)
@@ -202,7 +211,7 @@ class _DecoderLayerFn(torch.autograd.Function):
         del da
         dqkv = model_ops.qkv_rope_pack_bwd(dq, dkv, cos, sin, T, cfg.n_heads, cfg.n_kv_heads)
         h1, _ = model_ops.rmsnorm_fwd_raw(x, w1, cfg.eps)
-        dh1 = torch.mm(dqkv, wqkv)
+        dh1 = model.tp_sum(torch.mm(dqkv, wqkv))
         wgrad(wqkv, dqkv.t(), h1)
         del dqkv, h1
         dx, dw1 = model_ops.rmsnorm_bwd_raw(x, w1, rstd1, dh1)
@@ -243,8 +252,10 @@ class LlamaModel:
 
     def __init__(self, cfg: LlamaConfig, device: torch.device, params_flat: Optional[torch.Tensor] = None,
                  grads_flat: Optional[torch.Tensor] = None, seed: int = 0, recompute: bool = True,
-                 lm_head_chunk: int = 4096):
+                 lm_head_chunk: int = 4096, tp_group=None, tp_rank: int = 0, tp_size: int = 1):
         self.cfg, self.device = cfg, device
+        self.set_tensor_parallel(tp_group, tp_rank, tp_size)
+        self.n_replicated = 0
         self.recompute = recompute
         self.lm_head_chunk = lm_head_chunk
         self.executor = None
@@ -257,12 +268,9 @@ class LlamaModel:
         # None keeps the autograd + checkpoint path
         self.layer_levels: Optional[List[int]] = None
         self.accumulate_grads = False   # True: weight gradients are added to .grad instead of written
-        shapes: List[Tuple[str, Tuple[int, ...]]] = [("embed", (cfg.vocab, cfg.hidden))]
-        for l in range(cfg.n_layers):
-            shapes += [(f"l{l}.norm1", (cfg.hidden,)), (f"l{l}.wqkv", (cfg.qkv_dim, cfg.hidden)),
-                       (f"l{l}.wo", (cfg.hidden, cfg.n_heads * cfg.head_dim)), (f"l{l}.norm2", (cfg.hidden,)),
-                       (f"l{l}.wgu", (2 * cfg.ffn, cfg.hidden)), (f"l{l}.wd", (cfg.hidden, cfg.ffn))]
-        shapes += [("norm_f", (cfg.hidden,)), ("lm_head", (cfg.vocab, cfg.hidden))]
+        # flat layout: parameters every tensor-parallel rank holds in full come first, the sharded
+        # matrices after them, so "the replicated part" is one contiguous range of the buffers
+        shapes: List[Tuple[str, Tuple[int, ...]]] = self.param_shapes(cfg)
         self.shapes = shapes
         total = 0
         self.offsets: Dict[str, Tuple[int, int]] = {}
@@ -270,6 +278,8 @@ class LlamaModel:
             n = math.prod(shp)
             self.offsets[name] = (total, n)
             total += -(-n // 8) * 8
+            if name == self.LAST_REPLICATED:
+                self.n_replicated = total
         self.n_flat = -(-total // 1024) * 1024
         self.params_flat = params_flat if params_flat is not None else torch.empty(self.n_flat, dtype=torch.bfloat16,
                                                                                    device=device)
@@ -285,21 +295,52 @@ class LlamaModel:
             self.p[name] = t
         self.init_weights(seed)
 
+    LAST_REPLICATED = "lm_head"
+
+    @staticmethod
+    def param_shapes(cfg: LlamaConfig) -> List[Tuple[str, Tuple[int, ...]]]:
+        rep = [("embed", (cfg.vocab, cfg.hidden))]
+        for l in range(cfg.n_layers):
+            rep += [(f"l{l}.norm1", (cfg.hidden,)), (f"l{l}.norm2", (cfg.hidden,))]
+        rep += [("norm_f", (cfg.hidden,)), ("lm_head", (cfg.vocab, cfg.hidden))]
+        sharded = []
+        for l in range(cfg.n_layers):
+            sharded += [(f"l{l}.wqkv", (cfg.qkv_dim, cfg.hidden)), (f"l{l}.wo", (cfg.hidden, cfg.n_heads * cfg.head_dim)),
+                        (f"l{l}.wgu", (2 * cfg.ffn, cfg.hidden)), (f"l{l}.wd", (cfg.hidden, cfg.ffn))]
+        return rep + sharded
+
     @staticmethod
     def flat_size(cfg: LlamaConfig) -> int:
-        total = 0
-        per_layer = [cfg.hidden, cfg.qkv_dim * cfg.hidden, cfg.hidden * cfg.n_heads * cfg.head_dim, cfg.hidden,
-                     2 * cfg.ffn * cfg.hidden, cfg.hidden * cfg.ffn]
-        for n in [cfg.vocab * cfg.hidden] + per_layer * cfg.n_layers + [cfg.hidden, cfg.vocab * cfg.hidden]:
-            total += -(-n // 8) * 8
+        total = sum(-(-math.prod(shp) // 8) * 8 for _, shp in LlamaModel.param_shapes(cfg))
         return -(-total // 1024) * 1024
 
+    # ---- tensor parallelism: this object holds one rank's shard (``cfg`` is the sharded config)
+    def set_tensor_parallel(self, group, rank: int, size: int) -> None:
+        self.tp_group, self.tp_rank, self.tp_size = (group if size > 1 else None), rank, size
+
+    def tp_sum(self, t: torch.Tensor) -> torch.Tensor:
+        if self.tp_group is not None:
+            import torch.distributed as dist
+            dist.all_reduce(t, group=self.tp_group)
+        return t
+
+    def row_parallel(self, residual: torch.Tensor, inp: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+        """residual + sum over tensor-parallel ranks of inp @ weight^T (weight holds this rank's input columns)."""
+        if self.tp_group is None:
+            return torch.addmm(residual, inp, weight.t())
+        return self.tp_sum(torch.mm(inp, weight.t())).add_(residual)
+
     def init_weights(self, seed: int) -> None:
-        g = torch.Generator(device=self.device).manual_seed(seed)
+        """Replicated parameters come from ``seed`` alone (identical on every tensor-parallel rank),
+        sharded ones from a stream that also depends on the rank."""
+        g_rep = torch.Generator(device=self.device).manual_seed(seed)
+        g_shard = torch.Generator(device=self.device).manual_seed(seed * 7919 + 104729 * (self.tp_rank + 1))
+        replicated = True
         with torch.no_grad():
             self.params_flat.zero_()
             for name, shp in self.shapes:
                 t = self.p[name]
+                g = g_rep if replicated else g_shard
                 if name.endswith(("norm1", "norm2", "norm_f")):
                     t.fill_(1.0)
                 else:
@@ -311,6 +352,8 @@ class LlamaModel:
                     for s in range(0, flat.numel(), 1 << 26):
                         seg = flat[s:s + (1 << 26)]
                         seg.copy_(torch.empty(seg.numel(), dtype=torch.float32, device=self.device).normal_(0, std, generator=g))
+                if name == self.LAST_REPLICATED:
+                    replicated = False
 
     def plan_activation_levels(self, tokens: int, budget_bytes: int) -> List[int]:
         """Per-layer activation levels for the hand-written layer backward that fit ``budget_bytes``
@@ -343,6 +386,7 @@ class LlamaModel:
         h = model_ops.rmsnorm(x, p[f"l{l}.norm1"], cfg.eps)
         qkv = F.linear(h, p[f"l{l}.wqkv"])
         a = _AttentionFn.apply(qkv, self, cos, sin, l)
+        assert self.tp_group is None, "tensor parallelism needs the hand-written layer backward (CUDA)"
         x = x + F.linear(a, p[f"l{l}.wo"])
         h = model_ops.rmsnorm(x, p[f"l{l}.norm2"], cfg.eps)
         gu = F.linear(h, p[f"l{l}.wgu"])

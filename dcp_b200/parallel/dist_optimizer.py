@@ -34,8 +34,15 @@ class FlatBuffers:
 
 class ShardedAdamW:
     def __init__(self, bufs: FlatBuffers, lr: float = 3e-4, betas=(0.9, 0.95), eps: float = 1e-8,
-                 weight_decay: float = 0.1, clip_grad: Optional[float] = 1.0, group=None):
+                 weight_decay: float = 0.1, clip_grad: Optional[float] = 1.0, group=None, tp_group=None,
+                 n_replicated: int = 0):
+        """``group`` = the ranks that hold the same parameters (they share the sharded state and
+        their gradients are summed).  With tensor parallelism ``tp_group`` links the ranks that hold
+        different shards of one model replica and ``n_replicated`` is the length of the leading
+        part of the flat buffers that every one of them holds in full: the clipping norm counts
+        that part once and the sharded part once per tensor-parallel rank."""
         self.bufs, self.group = bufs, group
+        self.tp_group, self.n_replicated = tp_group, n_replicated
         self.lr, self.betas, self.eps, self.wd, self.clip = lr, betas, eps, weight_decay, clip_grad
         world, rank = bufs.world, bufs.rank
         per = -(-bufs.n_flat // world)
@@ -47,6 +54,7 @@ class ShardedAdamW:
         self.m = torch.zeros_like(self.master)
         self.v = torch.zeros_like(self.master)
         self.sq_norm = torch.zeros(1, dtype=torch.float32, device=dev)
+        self.sq_parts = torch.zeros(2, dtype=torch.float32, device=dev)   # [replicated, sharded] with tensor parallelism
         self.clip_coef = torch.ones(1, dtype=torch.float32, device=dev)
         self.step_count = 0
         self.kernel_launches = 0
@@ -69,13 +77,27 @@ class ShardedAdamW:
         grads, params = _ptr_array(a.peer_ptrs("grads")), _ptr_array(a.peer_ptrs("params"))
         off, n = ctypes.c_long(self.shard_off), ctypes.c_long(self.shard_len)
         clip_ptr = ctypes.c_void_p(0)
-        if self.clip is not None:
+        if self.clip is not None and self.tp_group is not None:
+            import torch.distributed as dist
+            rep = max(0, min(self.n_replicated - self.shard_off, self.shard_len))
+            self.sq_parts.zero_()
+            for k, (o, ln) in enumerate(((self.shard_off, rep), (self.shard_off + rep, self.shard_len - rep))):
+                if ln > 0:
+                    _lib.check(lib.dcpk_grad_sqnorm(grads, ctypes.c_int(b.world), ctypes.c_long(o), ctypes.c_long(ln),
+                                                    ctypes.c_float(grad_scale), _lib.ptr(self.sq_parts[k:]),
+                                                    _lib.stream_handle()), "grad_sqnorm")
+            if b.world > 1:
+                dist.all_reduce(self.sq_parts, group=self.group)
+            dist.all_reduce(self.sq_parts[1:], group=self.tp_group)
+            self.sq_norm.copy_(self.sq_parts.sum().reshape(1))
+        elif self.clip is not None:
             self.sq_norm.zero_()
             _lib.check(lib.dcpk_grad_sqnorm(grads, ctypes.c_int(b.world), off, n, ctypes.c_float(grad_scale),
                                             _lib.ptr(self.sq_norm), _lib.stream_handle()), "grad_sqnorm")
             if b.world > 1:
                 import torch.distributed as dist
                 dist.all_reduce(self.sq_norm, group=self.group)
+        if self.clip is not None:
             torch.clamp(self.clip / (self.sq_norm.sqrt() + 1e-6), max=1.0, out=self.clip_coef)
             clip_ptr = _lib.ptr(self.clip_coef)
         _lib.check(lib.dcpk_fused_rs_adamw_ag(grads, params, ctypes.c_int(b.world), off, n, ctypes.c_float(grad_scale),

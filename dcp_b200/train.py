@@ -30,7 +30,8 @@ from .runtime.executor_fused import FusedAttentionExecutor
 class EngineConfig:
     model: LlamaConfig
     tokens_per_step: int
-    dcp_size: int = 0               # 0 -> all ranks form one context-parallel group
+    dcp_size: int = 0               # 0 -> all (non tensor-parallel) ranks form one context-parallel group
+    tp_size: int = 1                # tensor-parallel ranks per model replica (adjacent ranks)
     block_size: int = 2048
     mask: str = "causal"
     length_dist: synth.LengthDist = None
@@ -63,45 +64,67 @@ class TrainEngine:
         self.world = dist.get_world_size(world_group) if world_group is not None else 1
         self.rank = dist.get_rank(world_group) if world_group is not None else 0
         self.world_group = world_group
-        dcp = cfg.dcp_size or self.world
-        assert self.world % dcp == 0
-        self.dcp_size = dcp
-        self.dcp_group = world_group
-        if world_group is not None and dcp != self.world:
-            # one subgroup per context-parallel group; every rank has to create all of them
-            for g in range(self.world // dcp):
-                ranks = list(range(g * dcp, (g + 1) * dcp))
-                grp = dist.new_group(ranks)
-                if self.rank in ranks:
-                    self.dcp_group = grp
-        m = cfg.model
+        # rank layout: tensor-parallel rank fastest, then the rank inside its context-parallel group,
+        # then the data-parallel replica:  rank = (replica * dcp + cp_rank) * tp + tp_rank
+        tp = max(1, cfg.tp_size)
+        assert self.world % tp == 0, "tp_size must divide the world size"
+        n_cp = self.world // tp                 # ranks as the planner sees them
+        dcp = cfg.dcp_size or n_cp
+        assert n_cp % dcp == 0
+        self.tp_size, self.tp_rank, self.cp_index = tp, self.rank % tp, self.rank // tp
+        self.n_cp_ranks, self.dcp_size = n_cp, dcp
+        self.dcp_group, self.tp_group, self.opt_group = world_group, None, world_group
+        if world_group is not None and (tp > 1 or dcp != n_cp):
+            # every rank creates every subgroup, in the same order (new_group is collective)
+            self.dcp_group = None
+            for g in range(n_cp // dcp):
+                for t in range(tp):
+                    ranks = [(g * dcp + c) * tp + t for c in range(dcp)]
+                    grp = dist.new_group(ranks) if len(ranks) > 1 else None
+                    if self.rank in ranks:
+                        self.dcp_group = grp
+            if tp > 1:
+                for c in range(n_cp):
+                    ranks = [c * tp + t for t in range(tp)]
+                    grp = dist.new_group(ranks)
+                    if self.rank in ranks:
+                        self.tp_group = grp
+                self.opt_group = None
+                for t in range(tp):
+                    ranks = [c * tp + t for c in range(n_cp)]
+                    grp = dist.new_group(ranks) if len(ranks) > 1 else None
+                    if self.rank in ranks:
+                        self.opt_group = grp
+        m = cfg.model.shard(tp)                 # this rank's slice of the model
+        self.local_model = m
         n_flat = LlamaModel.flat_size(m)
-        self.bufs = FlatBuffers(n_flat, device, world_group if self.world > 1 else None)
+        self.bufs = FlatBuffers(n_flat, device, self.opt_group if n_cp > 1 else None)
         self.model = LlamaModel(m, device, self.bufs.params, self.bufs.grads, seed=cfg.seed, recompute=cfg.recompute,
-                                lm_head_chunk=cfg.lm_head_chunk)
+                                lm_head_chunk=cfg.lm_head_chunk, tp_group=self.tp_group, tp_rank=self.tp_rank, tp_size=tp)
         self.optimizer = ShardedAdamW(self.bufs, cfg.lr, weight_decay=cfg.weight_decay, clip_grad=cfg.clip_grad,
-                                      group=world_group)
-        group_tokens = cfg.tokens_per_step // (self.world // dcp)
+                                      group=self.opt_group if n_cp > 1 else None, tp_group=self.tp_group,
+                                      n_replicated=self.model.n_replicated)
+        group_tokens = cfg.tokens_per_step // (n_cp // dcp)
         cap = int(group_tokens * 1.3) + 4 * cfg.block_size
         self.executor = FusedAttentionExecutor(m.n_heads, m.n_kv_heads, cap, cap, 2 * cap, device,
                                                self.dcp_group if dcp > 1 else None)
         self.model.set_executor(self.executor)
         self.activation_levels = self._plan_activations(group_tokens // dcp)
-        self.spec = PlanSpec(self.world, dcp, cfg.tokens_per_step, m.n_heads, m.n_kv_heads, m.head_dim, cfg.block_size,
+        self.spec = PlanSpec(n_cp, dcp, cfg.tokens_per_step, m.n_heads, m.n_kv_heads, m.head_dim, cfg.block_size,
                              cfg.head_block_size, cfg.mask, cfg.length_dist or synth.LOGNORMAL_8K, m.vocab, cfg.seed,
                              cfg.n_stages, mem_imbalance_epsilon=cfg.mem_imbalance_epsilon,
                              comp_imbalance_epsilon=cfg.comp_imbalance_epsilon,
                              inter_node_comp_imbalance_factor=cfg.inter_node_comp_imbalance_factor,
                              use_block_size_heuristic=cfg.use_block_size_heuristic, cost_model=cfg.cost_model,
                              cache_dir=cfg.plan_cache_dir)
-        self.plans = PlanService(self.spec, self.rank, cfg.planner_workers, cfg.lookahead)
+        self.plans = PlanService(self.spec, self.cp_index, cfg.planner_workers, cfg.lookahead)
         self.iteration = 0
         self.h2d_bytes = 0
         self.d2h_bytes = 0
 
     def _plan_activations(self, tokens_per_rank: int):
         """Choose how much each layer keeps for its backward (see LlamaModel.plan_activation_levels)."""
-        cfg, m = self.cfg, self.cfg.model
+        cfg, m = self.cfg, self.local_model
         if not cfg.recompute or (cfg.activation_budget_gb is not None and cfg.activation_budget_gb < 0):
             return None
         tokens = int(tokens_per_rank * 1.15) + cfg.block_size
@@ -151,9 +174,9 @@ class TrainEngine:
             plan = self.plans.get(self.iteration)
         toks, labels, pos = self.stage_inputs(plan)
         loss = self.run_step(toks, labels, pos, plan.n_global_tokens)
-        if self.world > 1:
+        if self.n_cp_ranks > 1:
             import torch.distributed as dist
-            dist.all_reduce(loss, group=self.world_group)
+            dist.all_reduce(loss, group=self.opt_group)   # one rank per token (tensor-parallel peers hold copies)
         value = float(loss.item())         # device -> host read of the step's result
         self.d2h_bytes = loss.numel() * loss.element_size()
         self.executor.check_status()
@@ -168,11 +191,12 @@ class TrainEngine:
         os.makedirs(directory, exist_ok=True)
         path = os.path.join(directory, f"rank{self.rank:03d}.pt")
         state = {"iteration": self.iteration, "optimizer": self.optimizer.state_dict(),
-                 "model_cfg": self.cfg.model.__dict__, "world": self.world, "seed": self.cfg.seed,
+                 "model_cfg": self.cfg.model.__dict__, "world": self.world, "tp_size": self.tp_size,
+                 "seed": self.cfg.seed,
                  "plan_spec": {k: v for k, v in vars(self.spec).items() if k != "length_dist"},
                  "length_dist": vars(self.spec.length_dist),
                  "rng": torch.get_rng_state(), "cuda_rng": torch.cuda.get_rng_state(self.device)}
-        if self.rank == 0:
+        if self.cp_index == 0:     # one copy of the bf16 parameters per tensor-parallel shard
             state["params_bf16"] = self.bufs.params
         torch.save(state, path)
         return path
@@ -180,7 +204,8 @@ class TrainEngine:
     def load_checkpoint(self, directory: str) -> None:
         path = os.path.join(directory, f"rank{self.rank:03d}.pt")
         state = torch.load(path, map_location=self.device, weights_only=False)
-        assert state["world"] == self.world, "resume needs the world size the checkpoint was written with"
+        assert state["world"] == self.world and state.get("tp_size", 1) == self.tp_size, \
+            "resume needs the world size and tensor-parallel size the checkpoint was written with"
         self.optimizer.load_state_dict(state["optimizer"])
         self.iteration = int(state["iteration"])
         torch.set_rng_state(state["rng"].cpu())
@@ -189,18 +214,18 @@ class TrainEngine:
         o = self.optimizer
         self.bufs.arena.barrier()
         self.bufs.params[o.shard_off:o.shard_off + o.shard_len].copy_(o.master)
-        if self.world > 1:
+        if self.n_cp_ranks > 1:
             import torch.distributed as dist
-            shards = [torch.empty_like(self.bufs.params[:o.shard_len]) for _ in range(self.world)]
+            shards = [torch.empty_like(self.bufs.params[:o.shard_len]) for _ in range(self.n_cp_ranks)]
             dist.all_gather(shards, self.bufs.params[o.shard_off:o.shard_off + o.shard_len].contiguous(),
-                            group=self.world_group)
+                            group=self.opt_group)
             per = o.shard_len
             for r, s in enumerate(shards):
                 n = min(per, self.bufs.n_flat - r * per)
                 if n > 0:
                     self.bufs.params[r * per:r * per + n].copy_(s[:n])
         self.plans.close()
-        self.plans = PlanService(self.spec, self.rank, self.cfg.planner_workers, self.cfg.lookahead, start=self.iteration)
+        self.plans = PlanService(self.spec, self.cp_index, self.cfg.planner_workers, self.cfg.lookahead, start=self.iteration)
 
 
 def init_distributed():
@@ -253,6 +278,7 @@ def main(argv=None):
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--tokens-per-step", type=int, default=None, help="alias of --dcp-global-batch-size-in-tokens")
     ap.add_argument("--dcp-size", type=int, default=0, help="ranks per context-parallel group (0 = all ranks)")
+    ap.add_argument("--tensor-model-parallel-size", "--tp-size", dest="tp_size", type=int, default=1)
     ap.add_argument("--length-dist", default="lognormal8k", choices=["lognormal8k", "lognormal16k", "mixture"])
     ap.add_argument("--lr", type=float, default=3e-4)
     ap.add_argument("--log-interval", type=int, default=1)
@@ -276,7 +302,7 @@ def main(argv=None):
                        comp_imbalance_epsilon=args.dcp_comp_imbalance_epsilon,
                        inter_node_comp_imbalance_factor=args.dcp_inter_node_comp_imbalance_factor,
                        cost_model=cost if any(v is not None for v in cost.values()) else None,
-                       activation_budget_gb=args.activation_budget_gb)
+                       activation_budget_gb=args.activation_budget_gb, tp_size=args.tp_size)
     eng = TrainEngine(cfg, torch.device("cuda", local), group)
     if args.load:
         eng.load_checkpoint(args.load)

@@ -36,6 +36,19 @@ def test_fused_executor_two_gpus():
     assert res.returncode == 0 and "FUSED_OK" in res.stdout, res.stdout[-3000:]
 
 
+def test_tensor_parallel_step_two_gpus():
+    """Tensor parallelism (heads and FFN split over two ranks): loss and gradients match the fp32
+    model assembled from the shards; replicated parameters stay identical through a step."""
+    _need_gpu()
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
+           "127.0.0.1", "--master-port", "29547", os.path.join(ROOT, "tests", "tp_worker.py")]
+    res = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=900,
+                         env=dict(os.environ, PYTHONPATH=ROOT))
+    assert res.returncode == 0 and "TP_OK" in res.stdout, res.stdout[-3000:]
+
+
 @pytest.mark.parametrize("layer_path", ["autograd", "level0", "level1+2", "auto"])
 def test_tiny_model_step_matches_pytorch(layer_path):
     """Every layer implementation (autograd + checkpoint, hand-written backward at each activation
