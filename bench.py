@@ -45,7 +45,7 @@ QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,c
 def reference_arm() -> None:
     reason = ("reference needs dcp_flash_attn (CUDA fork of flash-attention 2.6.3), kahypar, redis-server, "
               "Megatron-LM and TransformerEngine, none of which are on this offline image; "
-              "`pip install --no-deps` of /root/reference succeeds but `import dcp.graph_partition.graph` and "
+              "`pip install --no-deps` of the reference source tree succeeds but `import dcp.graph_partition.graph` and "
               "`dcp.runtime.flash_attention.executor` fail with ModuleNotFoundError")
     print(json.dumps({"impl": "reference", "unavailable": reason}))
 
@@ -147,8 +147,8 @@ def main() -> None:
     profiling = os.environ.get("DCP_B200_PROFILE", "0") == "1"
     if profiling:
         eng.executor.profile_summary()          # drop the warm-up marks
-    sampler = ClockSampler(os.path.join(ROOT, "gpurun_out", f"clocks_rank{rank}.csv") if os.path.isdir(
-        os.path.join(ROOT, "gpurun_out")) else f"/tmp/clocks_rank{rank}.csv")
+    import tempfile
+    sampler = ClockSampler(os.path.join(os.environ.get("BENCH_CLOCKS_DIR", tempfile.gettempdir()), f"clocks_rank{rank}.csv"))
     if rank == 0:
         sampler.start()
     dev_ms, launches0 = 0.0, _lib.LAUNCHES

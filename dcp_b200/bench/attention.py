@@ -56,7 +56,7 @@ def bench_f(fn, warmup: int, iters: int, group):
 
 def main(argv=None):
     ap = argparse.ArgumentParser()
-    ap.add_argument("--framework", default="dcp", choices=["dcp", "ulysses", "nccl-plan"])
+    ap.add_argument("--framework", default="dcp", choices=["dcp", "ulysses", "ring", "zigzag", "nccl-plan"])
     ap.add_argument("--mask", default="causal")
     ap.add_argument("--tokens", type=int, default=131072)
     ap.add_argument("--batches", type=int, default=3)
@@ -122,6 +122,23 @@ def main(argv=None):
                 if args.mode == "fwdbwd":
                     out.backward(do)
                     q.grad = k.grad = v.grad = None
+        elif args.framework in ("ring", "zigzag"):
+            from .baselines import RingAttention
+            assert args.mask == "causal", "the library attention kernel only knows causal masks"
+            assert group is not None, "ring attention needs at least two ranks"
+            # lengths are rounded down to multiples of 2 x ranks (at most 2P - 1 tokens per sequence)
+            ra = RingAttention(group, RingAttention.adjust_seqlens(plan.seqlens, world), zigzag=args.framework == "zigzag")
+            n = ra.cu[-1]
+            q = torch.randn(n, H, 128, device=dev, generator=g).bfloat16().requires_grad_(True)
+            k = torch.randn(n, Hkv, 128, device=dev, generator=g).bfloat16().requires_grad_(True)
+            v = torch.randn(n, Hkv, 128, device=dev, generator=g).bfloat16().requires_grad_(True)
+            do = torch.randn(n, H, 128, device=dev, generator=g).bfloat16()
+
+            def step():
+                out = ra(q, k, v)
+                if args.mode == "fwdbwd":
+                    out.backward(do)
+                    q.grad = k.grad = v.grad = None
         else:
             from ..runtime.interface import get_executor
             ctx = get_default_execution_context(world, 1)
@@ -159,7 +176,8 @@ def main(argv=None):
         torch.cuda.synchronize()
         ex.check_status()
     if rank == 0:
-        name = {"dcp": "DCP", "ulysses": "Ulysses", "nccl-plan": "NCCLPlan"}[args.framework]
+        name = {"dcp": "DCP", "ulysses": "Ulysses", "ring": "Ring", "zigzag": "ZigzagRing",
+                "nccl-plan": "NCCLPlan"}[args.framework]
         print(f"{name}: total time {total_max_ms:.3f} ms")
         print(json.dumps({"summary": True, "framework": args.framework, "mask": args.mask, "n_gpus": world,
                           "tokens_per_batch": args.tokens, "batches": args.batches, "mode": args.mode,

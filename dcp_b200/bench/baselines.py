@@ -7,6 +7,10 @@ and a stock kernel" implementation looks like on the same box and exist to be be
   transformer_engine.py:82-92): tokens are split evenly over ranks, an all-to-all regroups them so
   each rank holds all tokens of H/P heads, a varlen causal attention runs locally, a second
   all-to-all restores the token split.  Backward is the mirrored pair of all-to-alls.
+* ``RingAttention``     - ring attention, plain or zigzag (ring-flash-attn ``ring`` / ``zigzag``, TE
+  ``p2p``): K/V chunks travel around the ring with NCCL point-to-point while the library kernel
+  attends to the chunk at hand; partial results are merged by log-sum-exp and in the backward
+  dK/dV travel with their chunk.  The ring logic is tested on CPU (gloo) against dense attention.
 * ``NcclPlanAttention`` - the DCP instruction plans interpreted with NCCL point-to-point
   exchanges and torch ops (the plan interpreter, see ``runtime/interface.py``).
 
@@ -96,3 +100,228 @@ class UlyssesAttention:
         vh = _SeqAllToAll.apply(v, self.group, True, self.counts)
         out = _varlen_causal_attention(qh, kh, vh, self.cu.to(q.device), self.max_len, self.scale)
         return _SeqAllToAll.apply(out, self.group, False, self.counts)
+
+
+# ------------------------------------------------------------------------------------------ ring
+# Ring attention (ring-flash-attn `ring` / `zigzag`, TE `p2p` in the reference's baseline set:
+# benchmark/microbenchmark/baselines/ring_flash_attn/ring_flash_attn.py:13-62).  K/V travel around
+# the ring with NCCL point-to-point while a library kernel attends to the chunk at hand; partial
+# results are merged by log-sum-exp; in the backward dK/dV travel with their chunk.
+
+def _dense_block_fwd(q, k, v, cu_q, cu_k, scale, causal):
+    """Packed-sequence attention in plain torch: -> (out [Tq, h, d], lse [h, Tq] fp32)."""
+    g = q.shape[1] // k.shape[1]
+    out = torch.empty_like(q)
+    lse = torch.empty(q.shape[1], q.shape[0], dtype=torch.float32, device=q.device)
+    for (a, b), (c, d_) in zip(zip(cu_q[:-1], cu_q[1:]), zip(cu_k[:-1], cu_k[1:])):
+        qs = q[a:b].float().transpose(0, 1)
+        ks = k[c:d_].float().transpose(0, 1).repeat_interleave(g, dim=0)
+        vs = v[c:d_].float().transpose(0, 1).repeat_interleave(g, dim=0)
+        s = (qs @ ks.transpose(1, 2)) * scale
+        if causal:   # bottom-right aligned, as the library kernel does for unequal lengths
+            nq, nk = b - a, d_ - c
+            keep = torch.ones(nq, nk, dtype=torch.bool, device=q.device).tril(nk - nq)
+            s = s.masked_fill(~keep, float("-inf"))
+        l = torch.logsumexp(s, dim=-1)
+        out[a:b] = (torch.exp(s - l[..., None]) @ vs).transpose(0, 1).to(q.dtype)
+        lse[:, a:b] = l
+    return out, lse
+
+
+def _dense_block_bwd(dout, q, k, v, out, lse, cu_q, cu_k, scale, causal):
+    g = q.shape[1] // k.shape[1]
+    dq = torch.zeros_like(q, dtype=torch.float32)
+    dk = torch.zeros_like(k, dtype=torch.float32)
+    dv = torch.zeros_like(v, dtype=torch.float32)
+    for (a, b), (c, d_) in zip(zip(cu_q[:-1], cu_q[1:]), zip(cu_k[:-1], cu_k[1:])):
+        qs = q[a:b].float().transpose(0, 1)
+        ks = k[c:d_].float().transpose(0, 1).repeat_interleave(g, dim=0)
+        vs = v[c:d_].float().transpose(0, 1).repeat_interleave(g, dim=0)
+        s = (qs @ ks.transpose(1, 2)) * scale
+        if causal:
+            nq, nk = b - a, d_ - c
+            keep = torch.ones(nq, nk, dtype=torch.bool, device=q.device).tril(nk - nq)
+            s = s.masked_fill(~keep, float("-inf"))
+        p = torch.exp(s - lse[:, a:b, None])           # probabilities w.r.t. the GLOBAL normaliser
+        do = dout[a:b].float().transpose(0, 1)
+        delta = (do * out[a:b].float().transpose(0, 1)).sum(-1, keepdim=True)
+        ds = p * (do @ vs.transpose(1, 2) - delta) * scale
+        dq[a:b] = (ds @ ks).transpose(0, 1)
+        hk = k.shape[1]
+        dk[c:d_] = (ds.transpose(1, 2) @ qs).view(hk, g, d_ - c, -1).sum(1).transpose(0, 1)
+        dv[c:d_] = (p.transpose(1, 2) @ do).view(hk, g, d_ - c, -1).sum(1).transpose(0, 1)
+    return dq, dk, dv
+
+
+def _block_fwd(q, k, v, cu_q, cu_k, scale, causal):
+    if q.is_cuda:
+        from flash_attn.flash_attn_interface import _flash_attn_varlen_forward
+        tq = torch.tensor(cu_q, dtype=torch.int32, device=q.device)
+        tk = torch.tensor(cu_k, dtype=torch.int32, device=q.device)
+        mq = max(b - a for a, b in zip(cu_q[:-1], cu_q[1:]))
+        mk = max(b - a for a, b in zip(cu_k[:-1], cu_k[1:]))
+        out, lse, _, _ = _flash_attn_varlen_forward(q, k, v, tq, tk, mq, mk, 0.0, scale, causal)
+        return out, lse.float()
+    return _dense_block_fwd(q, k, v, cu_q, cu_k, scale, causal)
+
+
+def _block_bwd(dout, q, k, v, out, lse, cu_q, cu_k, scale, causal):
+    if q.is_cuda:
+        from flash_attn.flash_attn_interface import _flash_attn_varlen_backward
+        tq = torch.tensor(cu_q, dtype=torch.int32, device=q.device)
+        tk = torch.tensor(cu_k, dtype=torch.int32, device=q.device)
+        mq = max(b - a for a, b in zip(cu_q[:-1], cu_q[1:]))
+        mk = max(b - a for a, b in zip(cu_k[:-1], cu_k[1:]))
+        dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+        _flash_attn_varlen_backward(dout, q, k, v, out, lse.contiguous(), dq, dk, dv, tq, tk, mq, mk, 0.0, scale, causal,
+                                    -1, -1, 0.0, None, False)
+        return dq.float(), dk.float(), dv.float()
+    return _dense_block_bwd(dout, q, k, v, out, lse, cu_q, cu_k, scale, causal)
+
+
+def _merge(out, lse, o2, l2, rows=None):
+    """Fold the partial (o2, l2) into (out fp32, lse) for ``rows`` (index tensor) or all rows."""
+    if rows is None:
+        new = torch.logaddexp(lse, l2)
+        out.mul_(torch.exp(lse - new).transpose(0, 1)[..., None]).add_(o2.float() * torch.exp(l2 - new).transpose(0, 1)[..., None])
+        lse.copy_(new)
+    else:
+        new = torch.logaddexp(lse[:, rows], l2)
+        out[rows] = out[rows] * torch.exp(lse[:, rows] - new).transpose(0, 1)[..., None] + \
+            o2.float() * torch.exp(l2 - new).transpose(0, 1)[..., None]
+        lse[:, rows] = new
+
+
+def _ring_exchange(tensors, group):
+    """Send ``tensors`` to the next rank of the ring and receive the previous rank's (same shapes)."""
+    P, rank = dist.get_world_size(group), dist.get_rank(group)
+    nxt, prv = dist.get_global_rank(group, (rank + 1) % P), dist.get_global_rank(group, (rank - 1) % P)
+    recv = [torch.empty_like(t) for t in tensors]
+    ops = [dist.P2POp(dist.isend, t.contiguous(), nxt, group) for t in tensors] + \
+          [dist.P2POp(dist.irecv, r, prv, group) for r in recv]
+    for w in dist.batch_isend_irecv(ops):
+        w.wait()
+    return recv
+
+
+class _RingFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, ring):
+        P, r = ring.P, ring.rank
+        out = torch.zeros(q.shape, dtype=torch.float32, device=q.device)
+        lse = torch.full((q.shape[1], q.shape[0]), float("-inf"), dtype=torch.float32, device=q.device)
+        kc, vc = k, v
+        for step in range(P):
+            src = (r - step) % P
+            for rows, cu_q, cols, cu_k, causal in ring.step_plan(step, src):
+                qs = q if rows is None else q[rows]
+                ks, vs = (kc, vc) if cols is None else (kc[cols], vc[cols])
+                o2, l2 = _block_fwd(qs, ks, vs, cu_q, cu_k, ring.scale, causal)
+                _merge(out, lse, o2, l2, rows)
+            if step + 1 < P:
+                kc, vc = _ring_exchange([kc, vc], ring.group)
+        res = out.to(q.dtype)
+        ctx.ring = ring
+        ctx.save_for_backward(q, k, v, res, lse)
+        return res
+
+    @staticmethod
+    def backward(ctx, dout):
+        ring = ctx.ring
+        q, k, v, out, lse = ctx.saved_tensors
+        P, r = ring.P, ring.rank
+        dout = dout.contiguous()
+        dq = torch.zeros(q.shape, dtype=torch.float32, device=q.device)
+        kc, vc = k, v
+        dkc = torch.zeros(k.shape, dtype=torch.float32, device=q.device)
+        dvc = torch.zeros_like(dkc)
+        for step in range(P):
+            src = (r - step) % P
+            for rows, cu_q, cols, cu_k, causal in ring.step_plan(step, src):
+                sel = (lambda t: t) if rows is None else (lambda t: t[rows])
+                ks, vs = (kc, vc) if cols is None else (kc[cols], vc[cols])
+                l_rows = lse if rows is None else lse[:, rows].contiguous()
+                gq, gk, gv = _block_bwd(sel(dout), sel(q), ks, vs, sel(out), l_rows, cu_q, cu_k, ring.scale, causal)
+                if rows is None:
+                    dq += gq
+                else:
+                    dq[rows] += gq
+                if cols is None:
+                    dkc += gk; dvc += gv
+                else:
+                    dkc[cols] += gk; dvc[cols] += gv
+            # the chunk and its gradient move on together; after P hops the gradient is home
+            if step + 1 < P:
+                kc, vc, dkc, dvc = _ring_exchange([kc, vc, dkc, dvc], ring.group)
+            else:
+                dkc, dvc = _ring_exchange([dkc, dvc], ring.group)
+        return dq.to(q.dtype), dkc.to(k.dtype), dvc.to(v.dtype), None
+
+
+class RingAttention:
+    """Causal ring attention over packed sequences, plain (rank r holds the r-th contiguous chunk
+    of every sequence) or zigzag (rank r holds chunks r and 2P-1-r, which evens out the causal
+    work).  Sequence lengths must be multiples of 2P (``adjust_seqlens``)."""
+
+    def __init__(self, group, seqlens: Sequence[int], head_dim: int = 128, zigzag: bool = True):
+        self.group, self.zigzag = group, zigzag
+        self.P, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        assert all(n % (2 * self.P) == 0 for n in seqlens), "lengths must be multiples of 2 x ranks"
+        self.seqlens = [int(n) for n in seqlens]
+        self.scale = head_dim ** -0.5
+        self.local = [n // self.P for n in self.seqlens]              # local tokens per sequence
+        self.cu = [0]
+        for n in self.local:
+            self.cu.append(self.cu[-1] + n)
+        half = [n // 2 for n in self.local]
+        self.cu_half = [0]
+        for n in half:
+            self.cu_half.append(self.cu_half[-1] + n)
+        first, second = [], []
+        for off, h in zip(self.cu[:-1], half):
+            first.append(torch.arange(off, off + h))
+            second.append(torch.arange(off + h, off + 2 * h))
+        self._first, self._second = torch.cat(first), torch.cat(second)
+
+    @staticmethod
+    def adjust_seqlens(seqlens: Sequence[int], world: int) -> List[int]:
+        m = 2 * world
+        return [max(m, (int(n) // m) * m) for n in seqlens]
+
+    def local_indices(self) -> torch.Tensor:
+        """Global token indices (into the packed batch) of this rank's tokens, in local order."""
+        idx, off = [], 0
+        for n in self.seqlens:
+            if self.zigzag:
+                c = n // (2 * self.P)
+                idx += [torch.arange(off + self.rank * c, off + (self.rank + 1) * c),
+                        torch.arange(off + (2 * self.P - 1 - self.rank) * c, off + (2 * self.P - self.rank) * c)]
+            else:
+                c = n // self.P
+                idx.append(torch.arange(off + self.rank * c, off + (self.rank + 1) * c))
+            off += n
+        return torch.cat(idx)
+
+    def step_plan(self, step: int, src: int):
+        """Attention calls of one ring step, as (query rows or None = all, cu_q, key rows or None,
+        cu_k, causal)."""
+        dev_rows = lambda t: t
+        if step == 0:
+            if not self.zigzag:
+                return [(None, self.cu, None, self.cu, True)]
+            # local chunks (r, 2P-1-r): the early chunk attends causally to itself; the late chunk
+            # attends fully to the early one and causally to itself = one bottom-right-aligned call
+            return [(self._first, self.cu_half, self._first, self.cu_half, True),
+                    (self._second, self.cu_half, None, self.cu, True)]
+        if not self.zigzag:
+            return [(None, self.cu, None, self.cu, False)] if src < self.rank else []
+        if src < self.rank:
+            # keys from an earlier rank: only its early chunk lies in the past of both local chunks
+            return [(None, self.cu, self._first, self.cu_half, False)]
+        # keys from a later rank: both of its chunks lie in the past of the local late chunk only
+        return [(self._second, self.cu_half, None, self.cu, False)]
+
+    def __call__(self, q, k, v):
+        if self._first.device != q.device:
+            self._first, self._second = self._first.to(q.device), self._second.to(q.device)
+        return _RingFn.apply(q, k, v, self)

@@ -93,7 +93,7 @@ def main(argv=None):
     ap.add_argument("--out", default="results")
     ap.add_argument("--kind", default="attention", choices=["attention", "train"])
     ap.add_argument("--gpus", type=int, default=8)
-    ap.add_argument("--frameworks", nargs="+", default=["dcp", "ulysses"])
+    ap.add_argument("--frameworks", nargs="+", default=["dcp", "ulysses", "zigzag", "ring"])
     ap.add_argument("--masks", nargs="+", default=["causal", "lambda", "causal_blockwise", "shared_question"])
     ap.add_argument("--length-dists", nargs="+", default=["lognormal8k"])
     ap.add_argument("--block-sizes", nargs="+", type=int, default=[1024, 2048, 4096])

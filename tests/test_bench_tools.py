@@ -50,3 +50,16 @@ def test_replay_of_saved_plans(tmp_path):
     pickle.dump(res, open(p, "wb"))
     rep = replay_plans(str(p))
     assert rep["forward"]["attn_units"] == len(res[0].workloads) == rep["backward"]["attn_units"]
+
+
+def test_ring_baselines_match_dense_attention():
+    """Plain and zigzag ring attention (the NCCL point-to-point baselines), forward and backward,
+    as two gloo processes against dense causal attention of the packed batch."""
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
+           "127.0.0.1", "--master-port", "29631", os.path.join(root, "tests", "ring_worker.py")]
+    res = subprocess.run(cmd, env=dict(os.environ, PYTHONPATH=root, OMP_NUM_THREADS="2"), stdout=subprocess.PIPE,
+                         stderr=subprocess.STDOUT, text=True, timeout=600)
+    assert res.returncode == 0 and "RING_OK" in res.stdout, res.stdout[-3000:]
