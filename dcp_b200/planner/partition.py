@@ -159,7 +159,7 @@ def _solve(vw_comp, vw_mem, offsets, pins, weights, k, mem_eps, comp_eps, seed, 
 def construct_and_partition_graph_multiconstraint(
         context: ExecutionContext, workload: WorkloadSpec, mem_epsilon: float = 0.2, comp_epsilon: float = 0.2,
         inter_node_comp_epsilon_factor: float = 5.0, solver: str = HGPSolver.NATIVE, logger=None, seed: int = 42,
-        n_tries: int = 4):
+        n_tries: int = 16):
     """Place every work unit and data block; fills ``workload.*_to_device_map``.
 
     Returns ``(device_to_workload_map, device_to_input_map, device_to_output_map)`` keyed by

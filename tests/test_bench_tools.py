@@ -63,3 +63,19 @@ def test_ring_baselines_match_dense_attention():
     res = subprocess.run(cmd, env=dict(os.environ, PYTHONPATH=root, OMP_NUM_THREADS="2"), stdout=subprocess.PIPE,
                          stderr=subprocess.STDOUT, text=True, timeout=600)
     assert res.returncode == 0 and "RING_OK" in res.stdout, res.stdout[-3000:]
+
+
+def test_dry_run_grid_and_best_config(tmp_path):
+    """Planner-only grid search: every cell reports balance, traffic and a modelled time; ``best``
+    keeps the fastest cell per workload."""
+    from dcp_b200.bench import dry_run
+    out = tmp_path / "dry.json"
+    res = dry_run.main(["--devices", "4", "--nodes", "2", "--tokens", "8192", "--n-heads", "8", "--n-kv-heads", "2",
+                        "--block-sizes", "256", "512", "--batches", "1", "--out", str(out)])
+    assert len(res["cells"]) == 2 and len(res["best"]) == 1
+    for c in res["cells"]:
+        assert c["compute_max_over_mean"] >= 1.0 and c["tokens_max_over_mean"] >= 1.0
+        assert c["modelled_pipeline_ms"] >= c["max_compute_ms"] > 0
+        assert c["inter_node_MB_per_device"] >= 0 and c["n_work_units"] > 0
+    assert res["best"][0]["modelled_pipeline_ms"] == min(c["modelled_pipeline_ms"] for c in res["cells"])
+    assert json.load(open(out))["best"] == res["best"]
