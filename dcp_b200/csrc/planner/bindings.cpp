@@ -1,8 +1,10 @@
 // pybind11 surface of the native planner: hypergraph partitioning and stage selection.
+#include <pybind11/numpy.h>
 #include <pybind11/pybind11.h>
 #include <pybind11/stl.h>
 
 #include "hypergraph.hpp"
+#include "mask_slices.hpp"
 #include "stage_greedy.hpp"
 
 namespace py = pybind11;
@@ -101,6 +103,26 @@ int64_t py_km1(int n_vertices, const std::vector<int>& net_offsets, const std::v
 
 }  // namespace
 
+namespace {
+
+// rng: int64 [T, 2, 2] C-contiguous -> (kv block indices, allowed pair counts, int32 [n, 2, 2, n_q])
+py::tuple py_slice_mask_pairs(py::array_t<int64_t, py::array::c_style | py::array::forcecast> rng, int64_t q_lo,
+                              int64_t q_hi, int n_blk, int64_t block_size) {
+  if (rng.ndim() != 3 || rng.shape(1) != 2 || rng.shape(2) != 2) throw std::invalid_argument("rng must be [T, 2, 2]");
+  if (q_lo < 0 || q_hi > rng.shape(0) || q_hi < q_lo) throw std::invalid_argument("query range outside the mask");
+  MaskSlices r;
+  {
+    py::gil_scoped_release release;
+    r = slice_mask_pairs(rng.data(), q_lo, q_hi, n_blk, block_size);
+  }
+  const py::ssize_t n = py::ssize_t(r.kv_blocks.size()), n_q = q_hi - q_lo;
+  py::array_t<int32_t> local({n, py::ssize_t(2), py::ssize_t(2), n_q});
+  std::copy(r.local.begin(), r.local.end(), local.mutable_data());
+  return py::make_tuple(r.kv_blocks, r.allowed, local);
+}
+
+}  // namespace
+
 PYBIND11_MODULE(_planner, m) {
   m.doc() = "native planner kernels: k-way hypergraph partitioning and per-stage greedy selection";
   m.def("greedy_selection_per_device", &py_greedy, py::arg("devices"), py::arg("scheduled_workloads"),
@@ -113,4 +135,6 @@ PYBIND11_MODULE(_planner, m) {
         py::arg("cap_mem"), py::arg("seed") = 42, py::arg("n_tries") = 4, py::arg("fixed") = std::vector<int>(),
         py::arg("initial") = std::vector<int>());
   m.def("connectivity_minus_one", &py_km1);
+  m.def("slice_mask_pairs", &py_slice_mask_pairs, py::arg("rng"), py::arg("q_lo"), py::arg("q_hi"), py::arg("n_blk"),
+        py::arg("block_size"));
 }

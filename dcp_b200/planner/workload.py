@@ -72,6 +72,25 @@ def _slice_pairs(rng: np.ndarray, q_lo: int, q_hi: int, n_blk: int, block_size: 
     return local, allowed
 
 
+def _native_planner():
+    try:
+        from .. import _planner
+        return _planner if hasattr(_planner, "slice_mask_pairs") else None
+    except ImportError:
+        return None
+
+
+def slice_pairs(rng: np.ndarray, q_lo: int, q_hi: int, n_blk: int, block_size: int, use_native: bool = True):
+    """-> (kv block indices with allowed pairs, allowed counts, local int32 [n, 2(range), 2(bound), n_q]).
+    Native (C++) when the planner extension is built, the array-arithmetic version otherwise."""
+    nat = _native_planner() if use_native else None
+    if nat is not None:
+        return nat.slice_mask_pairs(rng, int(q_lo), int(q_hi), int(n_blk), int(block_size))
+    local, allowed = _slice_pairs(rng, q_lo, q_hi, n_blk, block_size)
+    idx = np.nonzero(allowed > 0)[0]
+    return idx.tolist(), allowed[idx].tolist(), local[idx].astype(np.int32)
+
+
 def generate_workload(q_shape: Tuple[int, ...], kv_shape: Tuple[int, ...], raw_seqlens: Sequence[int],
                       padded_seqlens: Sequence[int], block_size: int, head_block_size: int,
                       comp_cost_model: Optional[AttnRooflineCostModel] = None,
@@ -129,13 +148,13 @@ def generate_workload(q_shape: Tuple[int, ...], kv_shape: Tuple[int, ...], raw_s
         for i in range(n_blk):
             if tok[i] == 0:
                 continue
-            local, allowed = _slice_pairs(rng, i * block_size, i * block_size + tok[i], n_blk, block_size)
-            for jj in np.nonzero(allowed > 0)[0].tolist():
+            kv_idx, allowed, local = slice_pairs(rng, i * block_size, i * block_size + tok[i], n_blk, block_size)
+            for k, jj in enumerate(kv_idx):
                 if tok[jj] == 0:
                     continue
-                m = local[jj]                              # [range, bound, n_q]
+                m = local[k]                               # [range, bound, n_q]
                 mask_t = torch.from_numpy(np.ascontiguousarray(m[0] if single_range else m).astype(np.int32))
-                cost = comp_cost_model.pair_cost(tok[i], tok[jj], float(allowed[jj]), head_block_size,
+                cost = comp_cost_model.pair_cost(tok[i], tok[jj], float(allowed[k]), head_block_size,
                                                  hbs_kv, head_dim, is_forward)
                 for j in range(n_hb_q):
                     wid = len(workloads)

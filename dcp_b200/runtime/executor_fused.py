@@ -162,6 +162,24 @@ class FusedAttentionExecutor:
             self.part_out.fill_(nan)
             self.part_lse.fill_(nan)
 
+    def profile_chrome_trace(self, path: Optional[str] = None, pid: Optional[int] = None) -> list:
+        """The recorded phases as chrome-trace events (microseconds since the first mark), to be laid
+        next to the planner's modelled pipeline trace; consumes the marks like profile_summary()."""
+        torch.cuda.synchronize(self.device)
+        events, prev = [], None
+        origin = self._marks[0][1] if self._marks else None
+        for key, ev in self._marks:
+            if not key.endswith(":start"):
+                events.append({"name": key, "ph": "X", "pid": self.rank if pid is None else pid, "tid": 0,
+                               "ts": origin.elapsed_time(prev) * 1e3, "dur": prev.elapsed_time(ev) * 1e3})
+            prev = ev
+        self._marks = []
+        if path:
+            import json
+            with open(path, "w") as f:
+                json.dump({"traceEvents": events}, f)
+        return events
+
     def profile_summary(self) -> dict:
         """Total milliseconds per phase since the last call ("fwd:kernels", "bwd:wait peers", ...)."""
         torch.cuda.synchronize(self.device)

@@ -44,6 +44,7 @@ def run_case(rank, world, group, raw, bs, H, Hkv, mask_name, hbs, n_stages=None,
     cap = max(max(p.q_rows for p in progs.values()), max(p.kv_rows for p in progs.values()),
               max(p.part_rows for p in progs.values()))
     ex = FusedAttentionExecutor(hq, hkv, cap, cap, cap, dev, group)
+    ex.profile = True          # phase timing on: its marks must line up into a trace (checked below)
     ex.prepare(prog)
     lq = gather_local(q, lay, BufferType.LOCAL_Q, raw, 1).to(dev)
     lkv = gather_local(kv, lay, BufferType.LOCAL_KV, raw, 2).to(dev)
@@ -56,6 +57,10 @@ def run_case(rank, world, group, raw, bs, H, Hkv, mask_name, hbs, n_stages=None,
         dq, dkv = ex.backward(ldo)
         torch.cuda.synchronize()
         ex.check_status()
+    trace = ex.profile_chrome_trace()
+    names = {e["name"] for e in trace}
+    assert {"fwd:pulls + kernels", "bwd:pulls + kernels"} <= names and all(e["dur"] >= 0 for e in trace), names
+    assert ex.profile_summary() == {}      # consumed
     out_g, lse_g = torch.zeros(T, H, d), torch.zeros(H, T)
     dq_g, dkv_g = torch.zeros(T, H, d), torch.zeros(T, 2, Hkv, d)
     scatter_to_global(out.float().cpu(), out_g, lay, BufferType.LOCAL_OUT, raw, 1)

@@ -218,3 +218,28 @@ def test_debug_env_flags_write_their_artifacts(tmp_path, monkeypatch):
         assert all(v["serialized_bytes"] > 0 and v["instructions"] for v in stats.values())
     fig = json.load(open(tmp_path / "workload_iter7.json"))
     assert any(n["kind"] == "WORK" for n in fig["nodes"]) and fig["edges"]
+
+
+@pytest.mark.parametrize("mask", ["causal", "lambda", "shared_question", "causal_blockwise", "chunked_first_chunk"])
+def test_native_mask_slicing_matches_array_version(mask):
+    """The C++ per-query-block mask slicing gives exactly what the array-arithmetic version gives."""
+    from dcp_b200.planner.masks import to_two_range
+    from dcp_b200.planner.workload import _native_planner, slice_pairs
+    if _native_planner() is None:
+        pytest.skip("planner extension not built")
+    raw, bs = [1500, 700, 130], 128
+    pad = pad_seqlens(raw, bs)
+    rng_all = to_two_range(masks.get_mask_fn(mask)(raw, pad, torch.int32))
+    off = 0
+    for n_raw, n_pad in zip(raw, pad):
+        rng = np.ascontiguousarray(rng_all[off:off + n_pad])
+        n_blk = n_pad // bs
+        for i in range(n_blk):
+            n_q = min(bs, max(n_raw - i * bs, 0))
+            if n_q == 0:
+                continue
+            a = slice_pairs(rng, i * bs, i * bs + n_q, n_blk, bs, use_native=True)
+            b = slice_pairs(rng, i * bs, i * bs + n_q, n_blk, bs, use_native=False)
+            assert list(a[0]) == list(b[0]) and list(a[1]) == list(b[1])
+            assert np.array_equal(np.asarray(a[2]), np.asarray(b[2]))
+        off += n_pad
