@@ -293,7 +293,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       for (int i = 0; i < 8; ++i) mxp[i] = -INFINITY;
       if (it.full) {
 #pragma unroll
-        for (int c = 0; c < 128; ++c) mxp[c & 7] = fmaxf(mxp[c & 7], __uint_as_float(sreg[c]));
+        for (int c = 0; c < 64; ++c)
+          mxp[c & 7] = fmax3(mxp[c & 7], __uint_as_float(sreg[2 * c]), __uint_as_float(sreg[2 * c + 1]));
       } else {
         const int rel0 = it.pos0 - s0, rel1 = it.pos0 - s1;
 #pragma unroll
@@ -310,15 +311,22 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       const float m_new = fmaxf(m_run, mx);
       const float m_sub = (m_new == -INFINITY) ? 0.f : m_new * sl2;
       const float alpha = (m_new == -INFINITY) ? 1.f : fast_exp2(m_run * sl2 - m_sub);
-      float psp[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      // packed fp32: one instruction scales two scores, one adds two probabilities to the row sum
+      const uint64_t sl2_2 = pack_f32x2(sl2, sl2), negm_2 = pack_f32x2(-m_sub, -m_sub);
+      uint64_t ps2[4] = {0ull, 0ull, 0ull, 0ull};
       uint32_t preg[64];
 #pragma unroll
       for (int c = 0; c < 64; ++c) {
-        float p0 = fast_exp2(fmaf(__uint_as_float(sreg[2 * c]), sl2, -m_sub));
-        float p1 = fast_exp2(fmaf(__uint_as_float(sreg[2 * c + 1]), sl2, -m_sub));
-        psp[c & 7] += p0 + p1;
+        const uint64_t x2 = fma_f32x2(pack_f32x2(__uint_as_float(sreg[2 * c]), __uint_as_float(sreg[2 * c + 1])), sl2_2, negm_2);
+        float x0, x1;
+        unpack_f32x2(x2, x0, x1);
+        const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
+        ps2[c & 3] = add_f32x2(ps2[c & 3], pack_f32x2(p0, p1));
         preg[c] = pack_bf16x2(p0, p1);
       }
+      float psp[8];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) unpack_f32x2(ps2[i], psp[2 * i], psp[2 * i + 1]);
       const float psum = ((psp[0] + psp[1]) + (psp[2] + psp[3])) + ((psp[4] + psp[5]) + (psp[6] + psp[7]));
       l_run = l_run * alpha + psum;
       m_run = m_new;
