@@ -88,8 +88,10 @@ struct __align__(1024) BwdSmem {
   // per-stage item descriptor and per-query statistics, staged by the producer warp next to Q / dO
   // so the gradient warps never touch global memory on their critical path
   BwdItem item[kStages];
-  float lse2[kStages][kQTile];   // lse * log2(e); +inf for rows past the tile
-  float delta[kStages][kQTile];
+  // statistics are staged in the form the packed-fp32 math consumes them (pairs of queries per
+  // 64-bit load): -lse * log2(e) (-inf for rows past the tile) and -delta * scale
+  alignas(8) float lse2[kStages][kQTile];
+  alignas(8) float delta[kStages][kQTile];
   int4 rng[kStages][kQTile];     // normalised ranges (end >= start)
   uint64_t kv_full, qdo_full[kStages], qdo_empty[kStages], stats_full[kStages], sdp_full, s_free, p_ready, dq_full;
   uint32_t tmem_base;
@@ -220,8 +222,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
         const int qi = lane + 32 * h;
-        sm.lse2[st][qi] = (l[h] == -INFINITY) ? INFINITY : l[h] * 1.4426950408889634f;
-        sm.delta[st][qi] = d[h];
+        sm.lse2[st][qi] = (l[h] == -INFINITY) ? -INFINITY : -(l[h] * 1.4426950408889634f);
+        sm.delta[st][qi] = -d[h] * scale;
         int4 mm = m[h];
         mm.y = max(mm.y, mm.x); mm.w = max(mm.w, mm.z);
         sm.rng[st][qi] = mm;
@@ -385,38 +387,42 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       // interleave the independent exp / multiply chains.
       const float* lse2_w = sm.lse2[st] + hf * 32;
       const float* delta_w = sm.delta[st] + hf * 32;
+      const uint64_t sl2_2 = pack_f32x2(sl2, sl2), scale_2 = pack_f32x2(scale, scale);
+      const uint64_t* nlse_w = reinterpret_cast<const uint64_t*>(lse2_w);
+      const uint64_t* ndel_w = reinterpret_cast<const uint64_t*>(delta_w);
       if (itx.full) {
 #pragma unroll
         for (int c = 0; c < 16; ++c) {
-          float pv[2], dv[2];
-#pragma unroll
-          for (int h = 0; h < 2; ++h) {
-            const int qi = 2 * c + h;
-            const bool allow = key_valid && (qi < n_rows_h);
-            const float e = fast_exp2(fmaf(__uint_as_float(sreg[qi]), sl2, -lse2_w[qi]));
-            pv[h] = allow ? e : 0.f;
-            dv[h] = pv[h] * (__uint_as_float(dreg[qi]) - delta_w[qi]) * scale;
-          }
-          preg[c] = pack_bf16x2(pv[0], pv[1]);
-          dsreg[c] = pack_bf16x2(dv[0], dv[1]);
+          // two queries per instruction: exponent argument and (dP - delta) * scale in packed fp32
+          const uint64_t x2 = fma_f32x2(pack_f32x2(__uint_as_float(sreg[2 * c]), __uint_as_float(sreg[2 * c + 1])), sl2_2, nlse_w[c]);
+          const uint64_t g2 = fma_f32x2(pack_f32x2(__uint_as_float(dreg[2 * c]), __uint_as_float(dreg[2 * c + 1])), scale_2, ndel_w[c]);
+          float x0, x1;
+          unpack_f32x2(x2, x0, x1);
+          const float e0 = fast_exp2(x0), e1 = fast_exp2(x1);
+          const float p0 = (key_valid && (2 * c < n_rows_h)) ? e0 : 0.f;
+          const float p1 = (key_valid && (2 * c + 1 < n_rows_h)) ? e1 : 0.f;
+          float d0, d1;
+          unpack_f32x2(mul_f32x2(pack_f32x2(p0, p1), g2), d0, d1);
+          preg[c] = pack_bf16x2(p0, p1);
+          dsreg[c] = pack_bf16x2(d0, d1);
         }
       } else {
         const int4* rng_w = sm.rng[st] + hf * 32;
 #pragma unroll
         for (int c = 0; c < 16; ++c) {
-          float pv[2], dv[2];
-#pragma unroll
-          for (int h = 0; h < 2; ++h) {
-            const int qi = 2 * c + h;
-            const int4 m = rng_w[qi];
-            const bool allow = key_valid && ((unsigned(kpos - m.x) < unsigned(m.y - m.x)) ||
-                                             (unsigned(kpos - m.z) < unsigned(m.w - m.z)));
-            const float e = fast_exp2(fmaf(__uint_as_float(sreg[qi]), sl2, -lse2_w[qi]));
-            pv[h] = allow ? e : 0.f;
-            dv[h] = pv[h] * (__uint_as_float(dreg[qi]) - delta_w[qi]) * scale;
-          }
-          preg[c] = pack_bf16x2(pv[0], pv[1]);
-          dsreg[c] = pack_bf16x2(dv[0], dv[1]);
+          const uint64_t x2 = fma_f32x2(pack_f32x2(__uint_as_float(sreg[2 * c]), __uint_as_float(sreg[2 * c + 1])), sl2_2, nlse_w[c]);
+          const uint64_t g2 = fma_f32x2(pack_f32x2(__uint_as_float(dreg[2 * c]), __uint_as_float(dreg[2 * c + 1])), scale_2, ndel_w[c]);
+          float x0, x1;
+          unpack_f32x2(x2, x0, x1);
+          const float e0 = fast_exp2(x0), e1 = fast_exp2(x1);
+          const int4 m0 = rng_w[2 * c], m1 = rng_w[2 * c + 1];
+          const bool a0 = key_valid && ((unsigned(kpos - m0.x) < unsigned(m0.y - m0.x)) || (unsigned(kpos - m0.z) < unsigned(m0.w - m0.z)));
+          const bool a1 = key_valid && ((unsigned(kpos - m1.x) < unsigned(m1.y - m1.x)) || (unsigned(kpos - m1.z) < unsigned(m1.w - m1.z)));
+          const float p0 = a0 ? e0 : 0.f, p1 = a1 ? e1 : 0.f;
+          float d0, d1;
+          unpack_f32x2(mul_f32x2(pack_f32x2(p0, p1), g2), d0, d1);
+          preg[c] = pack_bf16x2(p0, p1);
+          dsreg[c] = pack_bf16x2(d0, d1);
         }
       }
       TL_ADD(5, tl_t);
