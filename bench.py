@@ -90,7 +90,7 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
-def main() -> None:
+def parse_args(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=4)
@@ -106,20 +106,14 @@ def main() -> None:
     ap.add_argument("--activation-budget-gb", type=float, default=None,
                     help="extra activation memory for the hand-written layer backward (default: from free memory; "
                          "0: keep nothing extra; -1: autograd + checkpoint path)")
-    args = ap.parse_args()
-    if args.impl == "reference":
-        reference_arm()
-        return
+    return ap.parse_args(argv)
 
-    import torch
+
+def build_engine_config(args, world: int):
+    """-> (EngineConfig, scaling kind) of the selected benchmark configuration."""
     from dcp_b200.data import synth
     from dcp_b200.models.llama import LLAMA3_8B, tiny_config
-    from dcp_b200.ops import _lib
-    from dcp_b200.train import EngineConfig, TrainEngine, init_distributed
-
-    rank, world, local, group = init_distributed()
-    assert world == args.gpus or world == 1 and args.gpus == 1, f"launched with {world} ranks for --gpus {args.gpus}"
-    dev = torch.device("cuda", local)
+    from dcp_b200.train import EngineConfig
     model = LLAMA3_8B if args.model == "llama3-8b" else tiny_config()
     if args.config == "scaling":
         tokens, dist_, mask, scaling = args.tokens_per_gpu * world, synth.MIXTURE, "causal", "weak"
@@ -127,8 +121,27 @@ def main() -> None:
         tokens, dist_, mask, scaling = 131072, synth.LOGNORMAL_8K, "causal", "strong"
     else:
         tokens, dist_, mask, scaling = 131072, synth.LOGNORMAL_16K, "mixed", "strong"
-    cfg = EngineConfig(model, tokens, args.dcp_size, args.block_size, mask, dist_, n_stages=args.stages, activation_budget_gb=args.activation_budget_gb, tp_size=args.tp_size,
-                       planner_workers=2, lookahead=args.steps + 1)
+    cfg = EngineConfig(model=model, tokens_per_step=tokens, dcp_size=args.dcp_size, block_size=args.block_size, mask=mask,
+                       length_dist=dist_, n_stages=args.stages, activation_budget_gb=args.activation_budget_gb,
+                       tp_size=args.tp_size, planner_workers=2, lookahead=args.steps + 1)
+    return cfg, scaling
+
+
+def main() -> None:
+    args = parse_args()
+    if args.impl == "reference":
+        reference_arm()
+        return
+
+    import torch
+    from dcp_b200.ops import _lib
+    from dcp_b200.train import TrainEngine, init_distributed
+
+    rank, world, local, group = init_distributed()
+    assert world == args.gpus or world == 1 and args.gpus == 1, f"launched with {world} ranks for --gpus {args.gpus}"
+    dev = torch.device("cuda", local)
+    cfg, scaling = build_engine_config(args, world)
+    tokens, dist_, mask = cfg.tokens_per_step, cfg.length_dist, cfg.mask
     eng = TrainEngine(cfg, dev, group)
     W, K = args.warmup, args.steps
 

@@ -31,7 +31,6 @@ class EngineConfig:
     model: LlamaConfig
     tokens_per_step: int
     dcp_size: int = 0               # 0 -> all (non tensor-parallel) ranks form one context-parallel group
-    tp_size: int = 1                # tensor-parallel ranks per model replica (adjacent ranks)
     block_size: int = 2048
     mask: str = "causal"
     length_dist: synth.LengthDist = None
@@ -55,6 +54,7 @@ class EngineConfig:
     inter_node_comp_imbalance_factor: Optional[float] = None
     cost_model: Optional[dict] = None
     plan_cache_dir: Optional[str] = None     # reuse plans by batch signature (saved next to checkpoints on resume)
+    tp_size: int = 1                # tensor-parallel ranks per model replica (adjacent ranks)
 
 
 class TrainEngine:
@@ -294,8 +294,8 @@ def main(argv=None):
     cost = {"intra_node_lat": args.dcp_intra_node_lat, "intra_node_bw": args.dcp_intra_node_bw,
             "inter_node_lat": args.dcp_inter_node_lat, "inter_node_bw": args.dcp_inter_node_bw,
             "max_tflops": args.dcp_max_tflops, "max_mem_bw": args.dcp_max_mem_bw}
-    cfg = EngineConfig(model, tokens, 1 if args.disable_dcp else args.dcp_size, args.dcp_block_size, args.dcp_mask_type,
-                       dists[args.length_dist], lr=args.lr, planner_workers=args.dcp_prefetch_planner_num_workers,
+    cfg = EngineConfig(model=model, tokens_per_step=tokens, dcp_size=1 if args.disable_dcp else args.dcp_size,
+                       block_size=args.dcp_block_size, mask=args.dcp_mask_type, length_dist=dists[args.length_dist], lr=args.lr, planner_workers=args.dcp_prefetch_planner_num_workers,
                        head_block_size=args.dcp_head_block_size,
                        use_block_size_heuristic=bool(args.dcp_use_block_size_heuristic),
                        mem_imbalance_epsilon=args.dcp_mem_imbalance_epsilon,

@@ -45,3 +45,25 @@ def test_planner_knobs_reach_the_plans():
     alt = [plan_iteration(_spec(cost_model={"max_tflops": 500.0, "intra_node_bw": 2400.0},
                                 use_block_size_heuristic=True), 1, r) for r in range(4)]
     assert sum(p.tokens.numel() for p in alt) == alt[0].n_global_tokens
+
+
+def test_bench_and_train_build_their_engine_configs():
+    """The argument plumbing of the benchmark and of the training CLI: every value lands in the
+    field it is meant for (guards against positional drift when the config dataclass grows)."""
+    import importlib.util
+    import os
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    spec = importlib.util.spec_from_file_location("bench_entry", os.path.join(root, "bench.py"))
+    bench = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bench)
+    a = bench.parse_args(["--gpus", "8", "--dcp-size", "4", "--block-size", "1024", "--tp-size", "2", "--stages", "3",
+                          "--steps", "5"])
+    cfg, scaling = bench.build_engine_config(a, 8)
+    assert (cfg.tokens_per_step, cfg.dcp_size, cfg.block_size, cfg.tp_size, cfg.n_stages, cfg.mask, cfg.lookahead) == \
+        (8 * 32768, 4, 1024, 2, 3, "causal", 6)
+    assert scaling == "weak" and cfg.length_dist.kind == "mixture" and cfg.model.n_layers == 32
+    cfg, scaling = bench.build_engine_config(bench.parse_args(["--config", "masks", "--model", "tiny"]), 2)
+    assert (cfg.tokens_per_step, cfg.mask, scaling, cfg.tp_size, cfg.dcp_size) == (131072, "mixed", "strong", 1, 0)
+    # the defaults give a run that finishes in minutes on one GPU
+    d = bench.parse_args([])
+    assert (d.gpus, d.impl) == (1, "ours") and d.warmup >= 3 and d.steps >= 1
