@@ -130,7 +130,6 @@ class FusedAttentionExecutor:
             block_ops.gather_stats(self.q_pulls[s], a.peer_ptrs("delta"), self.delta, self.hq, self.cap[0])
             self.kernel_launches += 3 * (self.q_pulls[s].shape[0] > 0)
 
-    # ---- forward
     # ---- optional phase timing (DCP_B200_PROFILE=1): CUDA events on the main stream around the
     # barriers and the kernels of every call; read with profile_summary() after a synchronize
     def _mark(self, key: str) -> None:
@@ -153,14 +152,14 @@ class FusedAttentionExecutor:
         # a large finite sentinel, not NaN: rows of a tile past a block's valid tokens are read and
         # multiplied by exact zeros, which a NaN would survive
         p = self.program
-        nan = 30000.0
-        self.q[p.q_local_rows:].fill_(nan)
-        self.kv[p.kv_local_rows:].fill_(nan)
+        sentinel = 30000.0
+        self.q[p.q_local_rows:].fill_(sentinel)
+        self.kv[p.kv_local_rows:].fill_(sentinel)
         if with_grads:
-            self.dout[p.q_local_rows:].fill_(nan)
+            self.dout[p.q_local_rows:].fill_(sentinel)
         else:
-            self.part_out.fill_(nan)
-            self.part_lse.fill_(nan)
+            self.part_out.fill_(sentinel)
+            self.part_lse.fill_(sentinel)
 
     def profile_chrome_trace(self, path: Optional[str] = None, pid: Optional[int] = None) -> list:
         """The recorded phases as chrome-trace events (microseconds since the first mark), to be laid
@@ -193,6 +192,7 @@ class FusedAttentionExecutor:
         self._marks = []
         return tot
 
+    # ---- forward
     def forward(self):
         """Attention over the Q/KV already present in ``q_local()`` / ``kv_local()``.
         Returns views (out [rows, hq, d] bf16, lse [hq, rows] fp32) of this rank's own tokens."""
