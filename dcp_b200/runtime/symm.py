@@ -94,3 +94,40 @@ class SymmetricArena:
                      2: "a peer never reached a cross-GPU barrier within the deadline", 3: "bad kernel arguments"}
             self.status.zero_()
             raise RuntimeError(f"device-side failure detected (code {code}): {names.get(code, 'unknown')}")
+
+
+class FlagBarrierModel:
+    """Host model of the device barrier protocol (``signal_barrier_kernel``): rank r owns a row of
+    flags, ``flags[r][s]`` is written only by rank s and holds the last epoch s has reached; to
+    pass epoch e a rank publishes e into its slot of every peer's row, then waits until every
+    slot of its own row is >= e (wrap-safe signed difference) or its deadline passes, in which
+    case it records the timeout status and returns instead of hanging.  Used by the CPU tests to
+    check safety (nobody passes epoch e before everyone arrived at e), liveness and the bounded
+    wait with a withheld signal, with real threads and randomised timing."""
+
+    STATUS_OK, STATUS_SIGNAL_TIMEOUT = 0, 2
+
+    def __init__(self, world: int):
+        self.world = world
+        self.flags = [[0] * world for _ in range(world)]
+        self.status = [self.STATUS_OK] * world
+
+    def arrive_and_wait(self, rank: int, epoch: int, timeout_s: float = 1.0, withhold_from=()) -> int:
+        """One barrier call of ``rank``; ``withhold_from`` lists peers that are NOT told (fault injection)."""
+        import time
+        for peer in range(self.world):
+            if peer != rank and peer not in withhold_from:
+                self.flags[peer][rank] = epoch & 0xFFFFFFFF
+        deadline = time.monotonic() + timeout_s
+        for peer in range(self.world):
+            if peer == rank:
+                continue
+            while True:
+                diff = (self.flags[rank][peer] - epoch) & 0xFFFFFFFF
+                if diff < 0x80000000:            # int32(v - epoch) >= 0
+                    break
+                if time.monotonic() > deadline:
+                    self.status[rank] = self.STATUS_SIGNAL_TIMEOUT
+                    return self.status[rank]
+                time.sleep(0)
+        return self.STATUS_OK

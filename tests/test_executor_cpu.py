@@ -80,3 +80,46 @@ def test_dropped_message_times_out():
     hub.dropped.add((0, 1, key))
     with pytest.raises(CommTimeout):
         run_plans_in_process(ctx, fw_wl, fw, q, kv, raw, hub=hub)
+
+
+def test_flag_barrier_protocol_model():
+    """The cross-GPU barrier protocol on a host model with real threads: safety and liveness over
+    many epochs (including 32-bit wrap-around), and a withheld signal ends in a timeout status on
+    the rank that misses it, never in a hang."""
+    import random
+    import threading
+    import time
+    from dcp_b200.runtime.symm import FlagBarrierModel
+    world, n_epochs, base = 4, 40, 0xFFFFFFF0           # epochs run across the uint32 wrap
+    model = FlagBarrierModel(world)
+    for r in range(world):                               # as after base earlier barriers
+        model.flags[r] = [base & 0xFFFFFFFF] * world
+    arrived = [[0.0] * world for _ in range(n_epochs)]
+    passed = [[0.0] * world for _ in range(n_epochs)]
+
+    def run(rank):
+        rnd = random.Random(rank)
+        for e in range(n_epochs):
+            time.sleep(rnd.random() * 0.002)
+            arrived[e][rank] = time.monotonic()
+            assert model.arrive_and_wait(rank, base + 1 + e, timeout_s=5.0) == FlagBarrierModel.STATUS_OK
+            passed[e][rank] = time.monotonic()
+
+    threads = [threading.Thread(target=run, args=(r,)) for r in range(world)]
+    [t.start() for t in threads]
+    [t.join(timeout=60) for t in threads]
+    assert not any(t.is_alive() for t in threads)
+    for e in range(n_epochs):
+        assert min(passed[e]) >= max(arrived[e]) - 1e-6   # nobody left before the last one arrived
+
+    # fault injection: rank 1 never tells rank 0 -> rank 0 times out, the others pass
+    model = FlagBarrierModel(3)
+    out = {}
+    def run2(rank):
+        out[rank] = model.arrive_and_wait(rank, 1, timeout_s=0.3, withhold_from=(0,) if rank == 1 else ())
+    threads = [threading.Thread(target=run2, args=(r,)) for r in range(3)]
+    t0 = time.monotonic()
+    [t.start() for t in threads]
+    [t.join(timeout=10) for t in threads]
+    assert time.monotonic() - t0 < 5 and not any(t.is_alive() for t in threads)
+    assert out == {0: FlagBarrierModel.STATUS_SIGNAL_TIMEOUT, 1: 0, 2: 0}
