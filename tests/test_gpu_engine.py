@@ -91,3 +91,27 @@ def test_tiny_model_step_matches_pytorch(layer_path):
     l2 = eng.train_step(eng.plans.get(1))
     assert l2 == l2
     eng.close()
+
+
+def test_checkpoint_resume_continues_identically(tmp_path):
+    """Save after two steps, resume in a fresh engine: the third step's loss equals the loss of the
+    engine that kept running (optimizer shards, bf16 parameters, iteration counter, batch order)."""
+    _need_gpu()
+    from dcp_b200.data import synth
+    from dcp_b200.models.llama import tiny_config
+    from dcp_b200.train import EngineConfig, TrainEngine
+    dev = torch.device("cuda", 0)
+    mk = lambda: TrainEngine(EngineConfig(tiny_config(n_layers=2, hidden=1024, n_heads=8, n_kv_heads=2, ffn=2048, vocab=2048),
+                                          tokens_per_step=1536, block_size=256,
+                                          length_dist=synth.LengthDist("lognormal", 400.0, 0.6, 64, 1536),
+                                          planner_workers=0, lr=1e-3), dev)
+    a = mk()
+    a.train_step(); a.train_step()
+    a.save_checkpoint(str(tmp_path))
+    want = a.train_step()
+    b = mk()
+    b.load_checkpoint(str(tmp_path))
+    assert b.iteration == 2
+    got = b.train_step()
+    assert abs(got - want) <= 1e-5 * max(1.0, abs(want)), (got, want)
+    a.close(); b.close()
