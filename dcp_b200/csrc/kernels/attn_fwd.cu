@@ -1,14 +1,16 @@
 // Blockwise range-masked attention forward for sm_100a.
 //
 // One CTA = one 128-query tile of one head.  Warp roles:
-//   warps 0-3  softmax: one thread per query row, S read from TMEM with tcgen05.ld,
-//              online-softmax state in registers, P written back (TMEM or smem),
-//              O rescaled in TMEM only when a row maximum moved, epilogue.
+//   warps 0-3  softmax: park Q in TMEM once; then one thread per query row, S read from TMEM
+//              with tcgen05.ld, online-softmax state in registers (packed f32x2 scale / sum,
+//              three-input max), P written back (TMEM or smem), O rescaled in TMEM only when
+//              a row maximum moved, epilogue.
 //   warp 4     TMA producer: Q once, then a 2-deep ring of K tiles and of V tiles.
-//   warp 5     UMMA issuer: S_j = Q K_j^T (SS), O += P_j V_j (TS or SS), software
-//              pipelined so S_{j+1} is in flight while softmax works on S_j.
-// TMEM (512 columns): S0 [0,128) S1 [128,256) O [256,384); P_j aliases the first 64
-// columns of S_j as packed bf16 pairs.
+//   warp 5     UMMA issuer: S_j = Q K_j^T (TS: Q from TMEM, K from smem), O += P_j V_j (TS, or
+//              SS in the smem-P variant), software pipelined so S_{j+1} is in flight while
+//              softmax works on S_j.
+// TMEM (448 of 512 columns): S0 [0,128) S1 [128,256) O [256,384) Q [384,448) (packed bf16
+// pairs); P_j aliases the first 64 columns of S_j as packed bf16 pairs.
 //
 // The partial (out, lse) of a tile is stored straight to its destination arena, which
 // may be a peer GPU's memory (plain st.global over the NVLink mapping).
