@@ -1,0 +1,31 @@
+"""Type stubs of the native planner extension (built from dcp_b200/csrc/planner)."""
+from typing import Any, Dict, List, Optional, Sequence, Set, Tuple
+
+import numpy as np
+
+Device = Tuple[int, int]
+
+def greedy_selection_per_device(
+    devices: Set[Device], scheduled_workloads: Set[int], workload_costs: Sequence[float], input_sizes: Sequence[float],
+    workload_input_map: Sequence[Sequence[int]], input_block_type_map: Sequence[str],
+    device_workload_map: Dict[Device, List[int]], device_local_inputs_map: Dict[Device, Dict[int, int]],
+    target_comm_load_per_node: Dict[Device, float], is_bw: bool, stage_id: int, py_logger: Optional[Any] = None,
+    intra_node_budget: Dict[Device, float] = ...,
+) -> Tuple[Dict[Device, Set[int]], Dict[Device, List[Tuple[int, Device]]], Dict[Device, Dict[int, int]]]:
+    """One stage of work + transfer selection: (unlocked work per device, transfers per device as
+    (input id, source device), updated map of inputs each device holds and since which stage)."""
+
+def partition_hypergraph(
+    n_vertices: int, vw_comp: Sequence[int], vw_mem: Sequence[int], net_offsets: Sequence[int], net_pins: Sequence[int],
+    net_weight: Sequence[int], k: int, cap_comp: Sequence[int], cap_mem: Sequence[int], seed: int = 42, n_tries: int = 4,
+    fixed: Sequence[int] = ..., initial: Sequence[int] = ...,
+) -> Dict[str, Any]:
+    """Multilevel k-way partition minimising connectivity-1 under two per-block weight caps.
+    Returns {"part", "km1", "load_comp", "load_mem", "balanced"}."""
+
+def connectivity_minus_one(n_vertices: int, net_offsets: Sequence[int], net_pins: Sequence[int],
+                           net_weight: Sequence[int], part: Sequence[int], k: int) -> int: ...
+
+def slice_mask_pairs(rng: np.ndarray, q_lo: int, q_hi: int, n_blk: int, block_size: int
+                     ) -> Tuple[List[int], List[int], np.ndarray]:
+    """Per query block: KV blocks with allowed pairs, their pair counts, rebased intervals int32 [n, 2, 2, n_q]."""
