@@ -91,13 +91,85 @@ class AttentionExecutor:
         return {name: t.numel() * t.element_size() for name, t in self.impl.buffers.items()}
 
 
+class FusedPlanExecutor:
+    """The reference executor API (prepare / forward / backward / ...) on top of the fused sm_100a
+    executor: the placed and staged forward workload is lowered to kernel tables for this device
+    and run with in-kernel communication; q / kv / out / lse use the same local buffer layouts as
+    the plan-interpreting executor ([rows, head_block, d], lse [head_block, rows])."""
+
+    def __init__(self, n_heads_per_block: int, head_dim: int, exec_context: ExecutionContext,
+                 fw_exec_plan: Optional[ExecutionPlan] = None, fw_workload: Optional[WorkloadSpec] = None,
+                 bw_exec_plan: Optional[ExecutionPlan] = None, bw_workload: Optional[WorkloadSpec] = None,
+                 process_group=None, synchronous: bool = False, device: Optional[torch.device] = None,
+                 softmax_scale: Optional[float] = None, **_unused):
+        from ..planner.lowering import lower_all
+        from .executor_fused import FusedAttentionExecutor
+        assert head_dim == 128, "the sm_100a attention kernels are built for head_dim 128"
+        dev = (fw_exec_plan.node_id, fw_exec_plan.local_device_id)
+        self.program = lower_all(exec_context, fw_workload, build_backward=True, only=dev)[dev]
+        device = device or torch.device("cuda", torch.cuda.current_device())
+        rq, rkv, rp = self.program.need_all
+        self.impl = FusedAttentionExecutor(self.program.heads_q, self.program.heads_kv, rq, rkv, max(rp, 128), device,
+                                           process_group if exec_context.n_devices > 1 else None, softmax_scale)
+        self.impl.synchronous = self.impl.synchronous or synchronous
+        self.impl.prepare(self.program)
+        self.fw_plan, self.bw_plan, self.fw_workload, self.bw_workload = fw_exec_plan, bw_exec_plan, fw_workload, bw_workload
+        self.is_forward = True
+        self.n_heads_per_block, self.head_dim = n_heads_per_block, head_dim
+        self._epoch = -1
+
+    def prepare(self, forward: bool = True) -> None:
+        self.is_forward = forward
+
+    def switch_to_backward(self) -> None:
+        self.is_forward = False
+
+    def _write_inputs(self, q, kv) -> None:
+        ex = self.impl
+        ex.q_local().copy_(q.reshape(ex.q_local().shape))
+        ex.kv_local().copy_(kv.reshape(ex.kv_local().shape))
+        ex.inputs_written()
+        self._epoch = ex.arena_epoch
+
+    def forward(self, q: torch.Tensor, kv: torch.Tensor):
+        self._write_inputs(q, kv)
+        return self.impl.forward()
+
+    def set_local_out_lse(self, out: torch.Tensor, lse: torch.Tensor) -> None:
+        self.impl.out_local().copy_(out.reshape(self.impl.out_local().shape))
+        self.impl.lse_local().copy_(lse.reshape(self.impl.lse_local().shape))
+
+    def backward(self, q, kv, out, dout, lse):
+        ex = self.impl
+        if ex.arena_epoch != self._epoch or not ex._staging_valid:
+            self._write_inputs(q, kv)
+        self.set_local_out_lse(out, lse)
+        dq, dkv = ex.backward(dout.reshape(ex.q_local().shape))
+        return dq.to(q.dtype), dkv.to(kv.dtype)
+
+    def capture_cudagraph(self, *a, **k) -> None:
+        """Nothing to capture: a call is a handful of launches whose tables change every batch."""
+        return None
+
+    def deallocate_all_buffers(self) -> None:
+        self.impl = None
+
+    def log_memory_usage(self) -> Dict[str, int]:
+        ex = self.impl
+        return {n: getattr(ex, n).numel() * getattr(ex, n).element_size()
+                for n in ("q", "kv", "out", "lse", "dout", "delta", "part_out", "part_lse", "dq", "dkv")}
+
+
 def get_executor(n_heads_per_block: int, head_dim: int, exec_context: ExecutionContext, fw_exec_plan=None,
                  fw_workload=None, bw_exec_plan=None, bw_workload=None, executor_impl: str = "python",
                  process_group=None, synchronous: bool = False, iteration_idx=None, tp_rank=None,
                  use_cudagraph: bool = False, comm=None, device=None) -> AttentionExecutor:
+    if executor_impl == "fused":
+        # the B200-native path behind the same interface (CUDA only, head_dim 128)
+        return FusedPlanExecutor(n_heads_per_block, head_dim, exec_context, fw_exec_plan, fw_workload, bw_exec_plan,
+                                 bw_workload, process_group, synchronous, device)
     if executor_impl not in ("python", "reference"):
-        raise ValueError("plan-interpreting executors are 'python'; the fused sm_100a executor is "
-                         "dcp_b200.runtime.executor_fused.FusedAttentionExecutor (takes a FusedProgram)")
+        raise ValueError("executor_impl is 'python' (plan interpreter) or 'fused' (sm_100a kernels)")
     return AttentionExecutor(n_heads_per_block, head_dim, exec_context, fw_exec_plan, fw_workload, bw_exec_plan,
                              bw_workload, process_group, comm, synchronous, iteration_idx, tp_rank, device)
 
@@ -124,7 +196,8 @@ class DCPAttention(torch.autograd.Function):
 def prepare_dcp_distributed_attn_for_test(raw_seqlens: Sequence[int], n_heads: int, n_query_groups: int, head_dim: int,
                                           block_size: int, head_block_size: int, exec_context: ExecutionContext,
                                           rank: int, mask_type: str = "causal", dtype=torch.bfloat16, seed: int = 0,
-                                          process_group=None, comm=None, device=None):
+                                          process_group=None, comm=None, device=None,
+                                          executor_impl: str = "python"):
     """Plan a batch, build this rank's executor and local operands.  Returns the 9-tuple
     (executor, local_q, local_kv, local_dout, q, kv, dout, (fw_workload, bw_workload), padded_seqlens)."""
     padded = pad_seqlens(raw_seqlens, block_size)
@@ -141,7 +214,7 @@ def prepare_dcp_distributed_attn_for_test(raw_seqlens: Sequence[int], n_heads: i
     kv = torch.randn(T, 2, n_query_groups, head_dim, generator=g).to(dtype)
     dout = torch.randn(T, n_heads, head_dim, generator=g).to(dtype)
     ex = get_executor(head_block_size, head_dim, exec_context, fw[dev], fw_wl, bw[dev], bw_wl,
-                      process_group=process_group, comm=comm, device=device)
+                      executor_impl=executor_impl, process_group=process_group, comm=comm, device=device)
     lay = LocalLayout(fw_wl, dev)
     mv = (lambda t: t.to(device)) if device is not None else (lambda t: t)
     lq, lkv = get_local_q_kv(q, kv, fw_wl, dev, raw_seqlens)
