@@ -11,6 +11,7 @@ solver (``dcp_b200._planner``); multi-node clusters are split nodes-first, then 
 from __future__ import annotations
 
 import math
+import os
 from typing import Dict, List, Optional, Sequence, Tuple
 
 import numpy as np
@@ -176,6 +177,10 @@ def construct_and_partition_graph_multiconstraint(
                            mem_epsilon, comp_epsilon, seed, n_tries, initial=seed_part)
         for v, p in enumerate(part):
             vertex_dev[v] = (0, p)
+        if os.environ.get("DCP_B200_NO_REBALANCE", "0") in ("0", ""):
+            moves = _rebalance_compute(workload, graph, vertex_dev, context.devices())
+            if logger is not None:
+                logger.debug("compute rebalance: %d work units moved", moves)
     else:
         node_part, km1 = _solve(graph.vw_comp, graph.vw_mem, graph.net_offsets, graph.net_pins, graph.net_weight,
                                 n_nodes, mem_epsilon, comp_epsilon * inter_node_comp_epsilon_factor, seed, n_tries)
@@ -190,6 +195,52 @@ def construct_and_partition_graph_multiconstraint(
     if logger is not None:
         logger.debug("placement km1=%d (x%d bytes)", km1, BYTE_UNIT)
     return _materialise(context, workload, graph, vertex_dev)
+
+
+def _rebalance_compute(workload: WorkloadSpec, graph: "PlacementGraph", vertex_dev: List[Device], devices,
+                       tolerance: float = 1.004, max_moves: int = 400) -> int:
+    """Single-node polish after partitioning: move work units (never data) from the busiest device
+    to the idlest one until the busiest is within ``tolerance`` of the mean, each time picking the
+    unit that fits the gap and needs the fewest extra bytes at its new home.  The partitioner
+    packs parts up to their cap because only the cut is its objective; on NVSwitch the last
+    percent of balance is worth more than the few blocks this pulls.  Returns the number of moves."""
+    cost, sizes, w_in = workload.workloads, workload.input_sizes, workload.work_unit_input_map
+    load = {d: 0.0 for d in devices}
+    present = {d: set() for d in devices}
+    on_dev = {d: set() for d in devices}
+    for g, (ins, _outs) in enumerate(graph.groups):
+        present[tuple(vertex_dev[graph.n_work + g])].update(ins)
+    for w in range(graph.n_work):
+        d = tuple(vertex_dev[w])
+        load[d] += cost[w]
+        on_dev[d].add(w)
+        present[d].update(w_in[w])
+    mean = sum(load.values()) / max(len(devices), 1)
+    moves = 0
+    while moves < max_moves and mean > 0:
+        dmax = max(devices, key=lambda d: load[d])
+        dmin = min(devices, key=lambda d: load[d])
+        if load[dmax] <= tolerance * mean:
+            break
+        gap = load[dmax] - load[dmin]
+        best, best_key = None, None
+        for w in on_dev[dmax]:
+            c = cost[w]
+            if c <= 0 or c >= gap:          # moving it would just swap the roles
+                continue
+            extra = sum(sizes[i] for i in w_in[w] if i not in present[dmin])
+            # fewest new bytes per unit of moved work; among equals the unit closest to half the gap
+            key = (extra / c, abs(c - gap / 2))
+            if best_key is None or key < best_key:
+                best, best_key = w, key
+        if best is None:
+            break
+        vertex_dev[best] = dmin
+        on_dev[dmax].discard(best); on_dev[dmin].add(best)
+        load[dmax] -= cost[best]; load[dmin] += cost[best]
+        present[dmin].update(w_in[best])
+        moves += 1
+    return moves
 
 
 def _materialise(context, workload, graph: PlacementGraph, vertex_dev: Sequence[Device]):
