@@ -57,6 +57,28 @@ class EngineConfig:
     tp_size: int = 1                # tensor-parallel ranks per model replica (adjacent ranks)
 
 
+def parallel_layout(world: int, tp: int = 1, dcp_size: int = 0) -> dict:
+    """Rank lists of every process group for ``world`` ranks with ``tp`` tensor-parallel ranks per
+    model replica and ``dcp_size`` ranks per context-parallel group (0 = all).  Tensor-parallel
+    ranks are adjacent; ``rank = (replica * dcp + cp_rank) * tp + tp_rank``.
+
+    * ``dcp_groups``: ranks that run one attention executor together (same replica, same tp rank)
+    * ``tp_groups``:  ranks that hold the shards of one model copy for the same tokens
+    * ``opt_groups``: ranks that hold the same parameters (gradient sum + sharded optimizer state)
+    """
+    tp = max(1, tp)
+    assert world % tp == 0, "tp_size must divide the world size"
+    n_cp = world // tp
+    dcp = dcp_size or n_cp
+    assert n_cp % dcp == 0, "dcp_size must divide the number of non tensor-parallel ranks"
+    return {
+        "n_cp": n_cp, "dcp": dcp,
+        "dcp_groups": [[(g * dcp + c) * tp + t for c in range(dcp)] for g in range(n_cp // dcp) for t in range(tp)],
+        "tp_groups": [[c * tp + t for t in range(tp)] for c in range(n_cp)],
+        "opt_groups": [[c * tp + t for c in range(n_cp)] for t in range(tp)],
+    }
+
+
 class TrainEngine:
     def __init__(self, cfg: EngineConfig, device: torch.device, world_group=None):
         import torch.distributed as dist
@@ -67,34 +89,24 @@ class TrainEngine:
         # rank layout: tensor-parallel rank fastest, then the rank inside its context-parallel group,
         # then the data-parallel replica:  rank = (replica * dcp + cp_rank) * tp + tp_rank
         tp = max(1, cfg.tp_size)
-        assert self.world % tp == 0, "tp_size must divide the world size"
-        n_cp = self.world // tp                 # ranks as the planner sees them
-        dcp = cfg.dcp_size or n_cp
-        assert n_cp % dcp == 0
+        lay = parallel_layout(self.world, tp, cfg.dcp_size)
+        n_cp, dcp = lay["n_cp"], lay["dcp"]
         self.tp_size, self.tp_rank, self.cp_index = tp, self.rank % tp, self.rank // tp
         self.n_cp_ranks, self.dcp_size = n_cp, dcp
         self.dcp_group, self.tp_group, self.opt_group = world_group, None, world_group
         if world_group is not None and (tp > 1 or dcp != n_cp):
             # every rank creates every subgroup, in the same order (new_group is collective)
-            self.dcp_group = None
-            for g in range(n_cp // dcp):
-                for t in range(tp):
-                    ranks = [(g * dcp + c) * tp + t for c in range(dcp)]
+            def make(groups):
+                mine = None
+                for ranks in groups:
                     grp = dist.new_group(ranks) if len(ranks) > 1 else None
                     if self.rank in ranks:
-                        self.dcp_group = grp
+                        mine = grp
+                return mine
+            self.dcp_group = make(lay["dcp_groups"])
             if tp > 1:
-                for c in range(n_cp):
-                    ranks = [c * tp + t for t in range(tp)]
-                    grp = dist.new_group(ranks)
-                    if self.rank in ranks:
-                        self.tp_group = grp
-                self.opt_group = None
-                for t in range(tp):
-                    ranks = [c * tp + t for c in range(n_cp)]
-                    grp = dist.new_group(ranks) if len(ranks) > 1 else None
-                    if self.rank in ranks:
-                        self.opt_group = grp
+                self.tp_group = make(lay["tp_groups"])
+                self.opt_group = make(lay["opt_groups"])
         m = cfg.model.shard(tp)                 # this rank's slice of the model
         self.local_model = m
         n_flat = LlamaModel.flat_size(m)

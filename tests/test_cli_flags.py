@@ -67,3 +67,25 @@ def test_bench_and_train_build_their_engine_configs():
     # the defaults give a run that finishes in minutes on one GPU
     d = bench.parse_args([])
     assert (d.gpus, d.impl) == (1, "ours") and d.warmup >= 3 and d.steps >= 1
+
+
+def test_parallel_layout_groups_partition_the_world():
+    """TP x CP x DP rank layout: every family of groups partitions the ranks, a dcp group and a tp
+    group share exactly one rank, and the optimizer groups are the ranks of equal tp index."""
+    from dcp_b200.train import parallel_layout
+    for world, tp, dcp in [(8, 2, 2), (8, 1, 4), (8, 4, 0), (16, 2, 4), (2, 2, 0), (8, 1, 0), (6, 3, 1)]:
+        lay = parallel_layout(world, tp, dcp)
+        n_cp, d = world // tp, (dcp or world // tp)
+        assert (lay["n_cp"], lay["dcp"]) == (n_cp, d)
+        for name, size in (("dcp_groups", d), ("tp_groups", tp), ("opt_groups", n_cp)):
+            flat = sorted(r for g in lay[name] for r in g)
+            assert flat == list(range(world)) and all(len(g) == size for g in lay[name]), name
+        for dg in lay["dcp_groups"]:
+            assert len({r % tp for r in dg}) == 1                     # one tp index per attention group
+            assert len({r // tp // d for r in dg}) == 1               # one replica per attention group
+            for tg in lay["tp_groups"]:
+                assert len(set(dg) & set(tg)) <= 1
+        for t, og in enumerate(lay["opt_groups"]):
+            assert all(r % tp == t for r in og)
+        for tg in lay["tp_groups"]:
+            assert tg == list(range(tg[0], tg[0] + tp))               # tensor-parallel ranks are adjacent
