@@ -183,7 +183,14 @@ def plan_batch(spec: PlanSpec, iteration: int, rank: int, seqlens: Sequence[int]
     compiler = InstrCompiler(ctx, ccfg)
     fw_wl, bw_wl, fw_plans, bw_plans = compiler.compile(wl, generate_backward=spec.build_instruction_plans)
     dev = (0, group_rank)
-    program = lower_all(ctx, fw_wl, spec.build_backward, only=dev)[dev]
+    if os.environ.get("DCP_B200_VALIDATE", "0") == "1":
+        # debug: lower every rank's program and check the tables against each other before use
+        from ..planner.validate import validate_programs
+        all_programs = lower_all(ctx, fw_wl, spec.build_backward)
+        validate_programs(all_programs)
+        program = all_programs[dev]
+    else:
+        program = lower_all(ctx, fw_wl, spec.build_backward, only=dev)[dev]
     lay = LocalLayout(fw_wl, dev)
     idx = []
     for _, m in lay.blocks.get(BufferType.LOCAL_Q, []):

@@ -218,3 +218,112 @@ def _merge(D: _Dev, srcs, dst: BufferBlock, producers, final: int) -> None:
         union |= set(v[2])
     _check(all(v[-1] == dst.n_tokens for v in vals), f"{D.dev}: reduction token counts differ")
     D.write(dst, ("part", vals[0][1], frozenset(union), dst.n_tokens))
+
+
+# ------------------------------------------------------------------------------- fused programs
+def validate_programs(programs) -> Dict[str, int]:
+    """Static checks of the fused executor's tables for all ranks at once (``programs`` is a list
+    indexed by rank or a {device: program} dict in rank order):
+
+    * pulls read only rows the owner holds locally and write disjoint staging ranges above the
+      local rows, before the first stage that reads them;
+    * every row range a forward tile or a backward item reads is local or was pulled in an earlier
+      or the same stage; every row it writes lies inside the destination arena;
+    * partial-arena slots are written by exactly one tile set and consumed by exactly one merge;
+      every merged destination row range is local to the merging rank;
+    * gradient pushes cover exactly the pulled row ranges and land in the owner's local rows.
+
+    Returns counters (pulls, tiles, items, merges).  Raises PlanValidationError otherwise."""
+    import numpy as np
+    progs = list(programs.values()) if isinstance(programs, dict) else list(programs)
+    world = len(progs)
+    stats = {"pulls": 0, "tiles": 0, "items": 0, "merges": 0}
+    for r, p in enumerate(progs):
+        _check(p.rank == r and p.world == world, f"rank {r}: program says rank {p.rank} of {p.world}")
+        _check(all(n >= v for n, v in zip(p.need_all, p.max_rows())), f"rank {r}: need_all below own rows")
+
+    def ranges_disjoint(ranges, what):
+        ranges = sorted(ranges)
+        for (a0, a1), (b0, b1) in zip(ranges, ranges[1:]):
+            _check(a1 <= b0, f"{what}: rows [{a0},{a1}) and [{b0},{b1}) overlap")
+
+    part_written = [dict() for _ in range(world)]          # owner -> {slot row: n rows}
+    for r, p in enumerate(progs):
+        for kind, pulls, local_rows, total_rows, owner_local in (
+                ("q", p.q_pulls, p.q_local_rows, p.q_rows, lambda peer: progs[peer].q_local_rows),
+                ("kv", p.kv_pulls, p.kv_local_rows, p.kv_rows, lambda peer: progs[peer].kv_local_rows)):
+            avail = [(0, local_rows, -1)]                   # (row0, row1, stage it becomes readable)
+            staged = []
+            for s, tab in enumerate(pulls):
+                for peer, src, dst, n in np.asarray(tab).reshape(-1, 4).tolist():
+                    stats["pulls"] += 1
+                    _check(0 <= peer < world and peer != r, f"rank {r} {kind} pull from rank {peer}")
+                    _check(0 <= src and src + n <= owner_local(peer), f"rank {r} {kind} pull reads non-local rows of {peer}")
+                    _check(local_rows <= dst and dst + n <= total_rows, f"rank {r} {kind} pull writes outside staging")
+                    staged.append((dst, dst + n))
+                    avail.append((dst, dst + n, s))
+            ranges_disjoint(staged, f"rank {r} {kind} staging")
+
+            def readable(row0, n, stage, avail=avail):
+                return any(a0 <= row0 and row0 + n <= a1 and st <= stage for a0, a1, st in avail)
+
+            if kind == "q":
+                q_readable = readable
+            else:
+                kv_readable = readable
+        for s in range(p.n_stages):
+            ft, bt = p.fwd[s], p.bwd[s] if p.bwd else None
+            if ft is not None:
+                tiles, entries = ft.tiles.numpy(), ft.kv_entries.numpy()
+                for q_row, n_rows, head, kv_off, n_kv, mask_row, out_dev, out_row in tiles.tolist():
+                    stats["tiles"] += 1
+                    _check(0 <= head < p.heads_q, f"rank {r}: tile head {head}")
+                    _check(q_readable(q_row, n_rows, s), f"rank {r} stage {s}: tile reads Q rows [{q_row},+{n_rows}) not present")
+                    for row, n_tok in entries[kv_off:kv_off + n_kv].tolist():
+                        _check(kv_readable(row, n_tok, s), f"rank {r} stage {s}: tile reads KV rows [{row},+{n_tok}) not present")
+                    _check(mask_row >= 0 and mask_row + n_rows <= ft.masks.shape[0], f"rank {r}: mask rows out of range")
+                    if out_dev < world:
+                        _check(out_row + n_rows <= progs[out_dev].part_rows, f"rank {r}: partial outside rank {out_dev}'s arena")
+                        if head == 0:
+                            part_written[out_dev].setdefault((out_row, out_row + n_rows), set()).add((r, s))
+                    else:
+                        own = out_dev - world
+                        _check(0 <= own < world and out_row + n_rows <= progs[own].q_local_rows,
+                               f"rank {r}: final output outside rank {own}'s local rows")
+            if bt is not None:
+                items = bt.items.numpy()
+                for kv_row, n_valid, item_off, n_items, dkv_dev, dkv_row, _, _ in bt.ctas.numpy().tolist():
+                    _check(kv_readable(kv_row, n_valid, s), f"rank {r} stage {s}: backward reads KV rows [{kv_row},+{n_valid})")
+                    _check(dkv_dev == 0 and dkv_row + n_valid <= p.kv_rows, f"rank {r}: dKV rows outside the accumulator")
+                    for q_row, n_rows, _pos, mask_row, dq_dev, dq_row, _full, _ in items[item_off:item_off + n_items].tolist():
+                        stats["items"] += 1
+                        _check(q_readable(q_row, n_rows, s), f"rank {r} stage {s}: backward reads Q rows [{q_row},+{n_rows})")
+                        _check(dq_dev == 0 and dq_row + n_rows <= p.q_rows, f"rank {r}: dQ rows outside the accumulator")
+                        _check(mask_row + n_rows <= bt.masks.shape[0], f"rank {r}: backward mask rows out of range")
+    for r, p in enumerate(progs):
+        consumed = set()
+        seen_slots = set()
+        for dst_row, n, off, n_src in np.asarray(p.merge_ops).reshape(-1, 4).tolist():
+            stats["merges"] += 1
+            _check(n_src >= 2, f"rank {r}: merge of {n_src} partial(s)")
+            _check(dst_row + n <= p.q_local_rows, f"rank {r}: merge destination outside local rows")
+            for slot in np.asarray(p.merge_src)[off:off + n_src].tolist():
+                _check(slot not in seen_slots, f"rank {r}: partial slot {slot} merged twice")
+                seen_slots.add(slot)
+                inside = sorted(iv for iv in part_written[r] if slot <= iv[0] and iv[1] <= slot + n)
+                _check(inside and inside[0][0] == slot and inside[-1][1] == slot + n and
+                       all(a[1] == b[0] for a, b in zip(inside, inside[1:])),
+                       f"rank {r}: partial slot [{slot},+{n}) is not fully written ({inside[:3]})")
+                writers = set().union(*(part_written[r][iv] for iv in inside))
+                _check(len(writers) == 1, f"rank {r}: partial slot {slot} written by {sorted(writers)}")
+                consumed.update(inside)
+        _check(consumed == set(part_written[r]), f"rank {r}: partial rows written but never merged: "
+                                                 f"{sorted(set(part_written[r]) - consumed)[:4]}")
+        for kind, push, pulls, owner_local in (("dq", p.dq_push, p.q_pulls, lambda o: progs[o].q_local_rows),
+                                               ("dkv", p.dkv_push, p.kv_pulls, lambda o: progs[o].kv_local_rows)):
+            pulled = sorted((peer, src, dst, n) for tab in pulls for peer, src, dst, n in np.asarray(tab).reshape(-1, 4).tolist())
+            pushed = sorted((o, dst, src, n) for o, src, dst, n in np.asarray(push).reshape(-1, 4).tolist())
+            _check(pulled == pushed, f"rank {r}: {kind} pushes do not mirror the pulls")
+            for o, src, dst, n in np.asarray(push).reshape(-1, 4).tolist():
+                _check(dst + n <= owner_local(o), f"rank {r}: {kind} push lands outside rank {o}'s local rows")
+    return stats

@@ -194,3 +194,19 @@ def test_plan_cache_reuses_plans_by_batch_signature(tmp_path):
     assert s0 != batch_signature(spec, 1, [100, 200], None, None)
     assert s0 != batch_signature(spec, 0, [100, 201], None, None)
     assert s0 != batch_signature(mk(cache_dir=str(tmp_path), mem_imbalance_epsilon=0.2), 0, [100, 200], None, None)
+
+
+def test_plan_service_validate_mode(monkeypatch):
+    """DCP_B200_VALIDATE=1: every rank's tables are lowered and cross-checked before the rank's own
+    program is handed out; the program is the same as without the check."""
+    from dcp_b200.data import synth
+    from dcp_b200.data.plan_service import PlanSpec, plan_iteration
+    spec = PlanSpec(world=4, dcp_size=4, tokens_per_step=8192, n_heads=8, n_kv_heads=2, block_size=512,
+                    length_dist=synth.LengthDist("lognormal", 2000.0, 0.8, 128, 8192), vocab=1000)
+    plain = plan_iteration(spec, 2, 1)
+    monkeypatch.setenv("DCP_B200_VALIDATE", "1")
+    checked = plan_iteration(spec, 2, 1)
+    assert torch.equal(plain.tokens, checked.tokens)
+    assert plain.program.q_rows == checked.program.q_rows and plain.program.part_rows == checked.program.part_rows
+    for a, b in zip(plain.program.kv_pulls, checked.program.kv_pulls):
+        assert (a == b).all()

@@ -9,6 +9,7 @@ from dcp_b200.core.instructions import BufferType
 from dcp_b200.planner import masks
 from dcp_b200.planner.compiler import CompilerConfig, InstrCompiler
 from dcp_b200.planner.lowering import lower_all
+from dcp_b200.planner.validate import PlanValidationError, validate_programs
 from dcp_b200.planner.workload import generate_workload, pad_seqlens
 from dcp_b200.runtime.emulate_fused import emulate
 from dcp_b200.runtime.layout import LocalLayout, gather_local, scatter_to_global
@@ -31,6 +32,8 @@ def test_emulated_programs_match_dense_attention(world, raw, bs, H, Hkv, mask_na
                            torch.bfloat16)
     fw_wl, _, _, _ = InstrCompiler(ctx, CompilerConfig(n_stages=n_stages)).compile(wl, generate_backward=False)
     progs = lower_all(ctx, fw_wl)
+    counts = validate_programs(progs)                     # static cross-rank consistency of the tables
+    assert counts["tiles"] > 0 and counts["items"] > 0
     devs = ctx.devices()
     T = sum(raw)
     g = torch.Generator().manual_seed(11)
@@ -56,3 +59,48 @@ def test_emulated_programs_match_dense_attention(world, raw, bs, H, Hkv, mask_na
     assert (dq_g - rdq).abs().max() < 1e-8 and (dkv_g - rdkv).abs().max() < 1e-8
     # something actually moved between ranks (otherwise the case would not test the lowering)
     assert sum(int(x.shape[0]) for p in progs.values() for x in p.q_pulls + p.kv_pulls) > 0
+
+
+def test_program_validator_catches_corrupted_tables():
+    import copy
+    world, raw, bs, H, Hkv = 4, [1000, 300, 2100, 640], 256, 4, 2
+    ctx = get_default_execution_context(world, 1)
+    pad = pad_seqlens(raw, bs)
+    m = masks.get_mask_fn("causal")(raw, pad, torch.int32)
+    wl = generate_workload((sum(pad), H, 32), (sum(pad), 2, Hkv, 32), raw, pad, bs, H, ctx.comp_cost_model, m,
+                           torch.bfloat16)
+    fw_wl, _, _, _ = InstrCompiler(ctx, CompilerConfig()).compile(wl, generate_backward=False)
+    good = list(lower_all(ctx, fw_wl).values())
+    validate_programs(good)
+    r = next(i for i, p in enumerate(good) if sum(len(t) for t in p.kv_pulls) > 0 and len(p.merge_ops) > 0)
+
+    def corrupted(fn):
+        progs = copy.deepcopy(good)
+        fn(progs[r])
+        return progs
+
+    def drop_pull(p):
+        s = next(i for i, t in enumerate(p.kv_pulls) if len(t))
+        p.kv_pulls[s] = p.kv_pulls[s][1:]
+
+    def late_pull(p):       # a block pulled one stage after its first reader
+        s = next(i for i, t in enumerate(p.kv_pulls) if len(t))
+        if s + 1 < p.n_stages:
+            import numpy as np
+            p.kv_pulls[s + 1] = np.concatenate([p.kv_pulls[s + 1].reshape(-1, 4), p.kv_pulls[s][:1]])
+        p.kv_pulls[s] = p.kv_pulls[s][1:]
+
+    def bad_merge(p):
+        p.merge_src = p.merge_src.copy()
+        p.merge_src[0] += 8
+
+    def lost_push(p):
+        p.dkv_push = p.dkv_push[1:]
+
+    def out_of_arena(p):
+        s = next(i for i, t in enumerate(p.fwd) if t is not None)
+        p.fwd[s].tiles[0, 0] = p.q_rows + 5
+
+    for fn in (drop_pull, late_pull, bad_merge, lost_push, out_of_arena):
+        with pytest.raises(PlanValidationError):
+            validate_programs(corrupted(fn))
