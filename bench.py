@@ -47,7 +47,8 @@ def reference_arm() -> None:
               "Megatron-LM and TransformerEngine, none of which are on this offline image; "
               "`pip install --no-deps` of the reference source tree succeeds but `import dcp.graph_partition.graph` and "
               "`dcp.runtime.flash_attention.executor` fail with ModuleNotFoundError")
-    print(json.dumps({"impl": "reference", "unavailable": reason}))
+    if int(os.environ.get("RANK", "0")) == 0:      # one line per job, also when launched with several ranks
+        print(json.dumps({"impl": "reference", "unavailable": reason}))
 
 
 class ClockSampler:
