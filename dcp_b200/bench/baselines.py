@@ -19,7 +19,7 @@ torch SDPA per sequence otherwise.
 """
 from __future__ import annotations
 
-from typing import List, Optional, Sequence
+from typing import List, Sequence
 
 import torch
 import torch.distributed as dist

@@ -3,7 +3,6 @@ from __future__ import annotations
 
 import struct
 from dataclasses import dataclass, field
-from typing import Optional
 
 from .cost_model import AttnRooflineCostModel, CommunicationCostModel
 

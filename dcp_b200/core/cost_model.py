@@ -10,7 +10,7 @@ kernels (128-query forward tiles, 128-key backward tiles).
 from __future__ import annotations
 
 import struct
-from typing import List, Sequence, Tuple
+from typing import Tuple
 
 import numpy as np
 import torch

@@ -13,7 +13,7 @@ from __future__ import annotations
 import concurrent.futures as cf
 import multiprocessing as mp
 from dataclasses import dataclass, field
-from typing import Callable, Dict, Iterator, List, Optional, Sequence
+from typing import Callable, Iterator, List, Optional, Sequence
 
 import numpy as np
 import torch

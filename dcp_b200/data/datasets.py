@@ -10,7 +10,7 @@ reference's (dcp/data/hf_dataset.py:249-312).
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Dict, Iterator, List, Optional, Sequence
+from typing import Dict, Iterator, List, Optional
 
 import numpy as np
 import torch

@@ -8,7 +8,7 @@ linear address space instead of a re-implementation of torch's multi-pool alloca
 from __future__ import annotations
 
 import bisect
-from typing import Dict, List, Optional, Tuple
+from typing import Dict, List, Tuple
 
 
 class OutOfArena(MemoryError):

@@ -6,7 +6,7 @@ thin aliases; the kernels are ahead-of-time compiled, so the warm-up is a no-op.
 from __future__ import annotations
 
 import ctypes
-from typing import List, Sequence
+from typing import Sequence
 
 import numpy as np
 import torch

@@ -10,7 +10,7 @@ per-token loops, plus the parameterisations the B200 benchmark configurations na
 """
 from __future__ import annotations
 
-from typing import Callable, Dict, List, Optional, Sequence
+from typing import Callable, Dict, Optional, Sequence
 
 import numpy as np
 import torch

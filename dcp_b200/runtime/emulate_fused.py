@@ -9,7 +9,7 @@ kernels themselves on one or two devices).
 """
 from __future__ import annotations
 
-from typing import Dict, List, Optional, Tuple
+from typing import List, Optional, Tuple
 
 import numpy as np
 import torch

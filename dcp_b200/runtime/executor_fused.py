@@ -17,7 +17,7 @@ from __future__ import annotations
 
 import os
 
-from typing import List, Optional
+from typing import Optional
 
 import numpy as np
 import torch

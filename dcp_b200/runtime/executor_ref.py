@@ -8,7 +8,7 @@ dcp/runtime/flash_attention/executor.py:340-2133; the attention rows are evaluat
 from __future__ import annotations
 
 import math
-from typing import Dict, List, Optional, Sequence, Tuple
+from typing import Optional, Sequence
 
 import torch
 

@@ -9,7 +9,7 @@ instruction with torch ops over ``torch.distributed`` point-to-point (gloo on CP
 """
 from __future__ import annotations
 
-from typing import Dict, List, Optional, Sequence, Tuple
+from typing import Dict, Optional, Sequence
 
 import numpy as np
 import torch

@@ -10,7 +10,7 @@ Cross-GPU synchronisation uses a flag row per rank inside the arena and the boun
 """
 from __future__ import annotations
 
-from typing import Dict, List, Optional, Tuple
+from typing import Dict, List, Tuple
 
 import torch
 
