@@ -210,3 +210,55 @@ def test_plan_service_validate_mode(monkeypatch):
     assert plain.program.q_rows == checked.program.q_rows and plain.program.part_rows == checked.program.part_rows
     for a, b in zip(plain.program.kv_pulls, checked.program.kv_pulls):
         assert (a == b).all()
+
+
+def test_every_public_name_of_the_reference_api_resolves():
+    """The reference's public API surface, module by module: every name a user of the reference
+    imports must resolve under the same path."""
+    import importlib
+    surface = {
+        "dcp_cpp": ["greedy_selection_per_device"],
+        "dcp.core.common": ["ExecutionContext", "ModelSpec", "get_default_execution_context"],
+        "dcp.core.cost_model": ["CommunicationCostModel", "AttnRooflineCostModel"],
+        "dcp.core.block_table": ["BlockType", "DataBlockMeta", "ComputationBlockMeta", "BlockMappings", "BlockManager",
+                                 "WorkloadSpec", "serialize_list_of_workloads", "deserialize_list_of_workloads"],
+        "dcp.core.instructions": ["MemcpyInstr", "CommLaunchInstr", "BarrierInstr", "CommWaitInstr", "AttnInstr",
+                                  "AttnBackwardInstr", "AttnReductionInstr", "SumInstr", "ExecutionPlan", "BufferBlock",
+                                  "BufferType", "CommOp", "CommType", "serialize_list_of_execution_plans",
+                                  "deserialize_list_of_execution_plans"],
+        "dcp.core.serialization": [],
+        "dcp.core.compiler": ["CompilerConfig", "InstrCompiler"],
+        "dcp.core.scheduler": ["schedule", "convert_forward_to_backward"],
+        "dcp.core.executor": ["DCPExecutor"],
+        "dcp.core.pipeline": [],
+        "dcp.core.steiner_tree_packing": [],
+        "dcp.graph_partition.graph": ["HGPSolver", "construct_and_partition_graph_multiconstraint",
+                                      "assign_device_by_heuristic", "assign_input_outputs"],
+        "dcp.data.dataloader": ["TrainingSpec", "generate_workload", "ExecutionPlanner", "DCPDataLoader"],
+        "dcp.data.hf_dataset": ["HuggingFaceDatasetConfig", "HuggingFaceDataset", "DummyMultiModelDataset",
+                                "OrderedBatchSampler"],
+        "dcp.data.kv_redis": [],
+        "dcp.runtime.flash_attention": ["get_executor", "AttentionExecutor", "DCPAttention",
+                                        "prepare_dcp_distributed_attn_for_test", "get_local_q_kv"],
+        "dcp.runtime.flash_attention.utils": ["lambda_mask_fn", "shared_question_mask_fn", "causal_blockwise_mask_fn",
+                                              "get_local_attn_ranges_zigzag", "get_per_step_attn_range",
+                                              "reconstruct_attention_forward_output_for_test",
+                                              "reconstruct_attention_backward_output_for_test"],
+        "dcp.ops.fused_ops": ["flash_attn_update_out_lse", "fused_blockwise_sum", "warmup_triton_ops"],
+        "dcp.memory.host_caching_allocator": ["apply_monkey_patch"],
+        "dcp.utils.logger": ["create_logger", "read_env_bool", "logger"],
+        "dcp.utils.common": ["trepr", "read_env_int"],
+    }
+    missing = []
+    for mod, names in surface.items():
+        m = importlib.import_module(mod)
+        missing += [f"{mod}.{n}" for n in names if not hasattr(m, n)]
+    assert not missing, missing
+    ex = importlib.import_module("dcp.core.executor").DCPExecutor
+    for method in ("register_handler", "check_all_handlers_registered", "init_buffers", "init_forward_input",
+                   "init_backward_input", "deallocate_buffers", "execute"):
+        assert hasattr(ex, method), method
+    ae = importlib.import_module("dcp.runtime.flash_attention").AttentionExecutor
+    for method in ("prepare", "forward", "backward", "switch_to_backward", "capture_cudagraph", "set_local_out_lse",
+                   "deallocate_all_buffers", "log_memory_usage"):
+        assert hasattr(ae, method), method
