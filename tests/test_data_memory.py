@@ -262,3 +262,33 @@ def test_every_public_name_of_the_reference_api_resolves():
     for method in ("prepare", "forward", "backward", "switch_to_backward", "capture_cudagraph", "set_local_out_lse",
                    "deallocate_all_buffers", "log_memory_usage"):
         assert hasattr(ae, method), method
+
+
+def test_planning_is_identical_across_processes():
+    """Every rank plans on its own and all ranks must arrive at the same placement: the plan of a
+    batch may not depend on the process (hash seeds, set iteration order, thread timing)."""
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    code = (
+        "import hashlib, numpy as np\n"
+        "from dcp_b200.data import synth\n"
+        "from dcp_b200.data.plan_service import PlanSpec, plan_iteration\n"
+        "spec = PlanSpec(world=8, dcp_size=8, tokens_per_step=65536, n_heads=8, n_kv_heads=2, block_size=1024,\n"
+        "                length_dist=synth.MIXTURE, vocab=1000)\n"
+        "h = hashlib.sha1()\n"
+        "for rank in (0, 5):\n"
+        "    p = plan_iteration(spec, 4, rank).program\n"
+        "    for a in p.q_pulls + p.kv_pulls + [p.merge_ops, p.merge_src, p.dq_push, p.dkv_push]:\n"
+        "        h.update(np.ascontiguousarray(a).tobytes())\n"
+        "    for t in p.fwd:\n"
+        "        if t is not None:\n"
+        "            h.update(t.tiles.numpy().tobytes()); h.update(t.kv_entries.numpy().tobytes())\n"
+        "print('PLANHASH', h.hexdigest())\n")
+    digests = set()
+    for seed in ("0", "1", "12345"):
+        res = subprocess.run([sys.executable, "-c", code], env=dict(os.environ, PYTHONPATH=root, PYTHONHASHSEED=seed),
+                             stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=600)
+        assert res.returncode == 0, res.stdout[-2000:]
+        digests.add([l for l in res.stdout.splitlines() if l.startswith("PLANHASH")][0])
+    assert len(digests) == 1, digests
