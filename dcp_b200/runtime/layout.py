@@ -36,6 +36,11 @@ class LocalLayout:
                 per_type.setdefault(_TYPE_TO_LOCAL[m.type], {})[idx] = (bid, m)
             for name, by_idx in per_type.items():
                 self.blocks[name] = [by_idx[i] for i in range(len(by_idx))]
+        # head-block width of every buffer, also for buffers this device holds no block of
+        self.head_block: Dict[str, int] = {}
+        for metas in (bm.input_id_to_meta, bm.output_id_to_meta):
+            for m in metas.values():
+                self.head_block.setdefault(_TYPE_TO_LOCAL[m.type], m.head_block_size)
         self.offsets: Dict[str, np.ndarray] = {}
         for name, lst in self.blocks.items():
             self.offsets[name] = np.concatenate([[0], np.cumsum([m.n_tokens for _, m in lst])]).astype(np.int64)
@@ -67,9 +72,10 @@ def gather_local(global_t: torch.Tensor, layout: LocalLayout, name: str, raw_seq
         sl = [slice(t0, t0 + m.n_tokens)] + [slice(None)] * (global_t.dim() - 1)
         sl[head_axis] = slice(m.head_id * hb, (m.head_id + 1) * hb)
         parts.append(global_t[tuple(sl)])
-    if not parts:
+    if not parts:      # a device that owns no block of this kind: empty, but with the buffer's head-block width
         shape = list(global_t.shape)
         shape[0] = 0
+        shape[head_axis] = layout.head_block.get(name, shape[head_axis])
         return global_t.new_zeros(shape)
     return torch.cat(parts, dim=0)
 
