@@ -54,37 +54,24 @@ def bench_f(fn, warmup: int, iters: int, group):
     return sum(vals) / len(vals), max(vals)
 
 
-def main(argv=None):
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--framework", default="dcp", choices=["dcp", "ulysses", "ring", "zigzag", "nccl-plan"])
-    ap.add_argument("--mask", default="causal")
-    ap.add_argument("--tokens", type=int, default=131072)
-    ap.add_argument("--batches", type=int, default=3)
-    ap.add_argument("--n-heads", type=int, default=32)
-    ap.add_argument("--n-kv-heads", type=int, default=8)
-    ap.add_argument("--block-size", type=int, default=2048)
-    ap.add_argument("--length-dist", default="lognormal8k", choices=["lognormal8k", "lognormal16k", "mixture"])
-    ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--iters", type=int, default=10)
-    ap.add_argument("--stages", type=int, default=None)
-    ap.add_argument("--mode", default="fwdbwd", choices=["fwd", "fwdbwd"])
-    ap.add_argument("--seed", type=int, default=0)
-    args = ap.parse_args(argv)
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    group = None
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
-        group = dist.group.WORLD
+def default_args(**over) -> argparse.Namespace:
+    """The microbenchmark's settings as a namespace (BASELINE configuration: 32 / 8 heads, d = 128, bf16,
+    131072-token packed batches, lognormal lengths, causal mask, block size 2048)."""
+    d = dict(framework="dcp", mask="causal", tokens=131072, batches=3, n_heads=32, n_kv_heads=8, block_size=2048,
+             length_dist="lognormal8k", warmup=5, iters=10, stages=None, mode="fwdbwd", seed=0)
+    d.update(over)
+    return argparse.Namespace(**d)
+
+
+def run_batches(args, group, dev, rank: int, world: int, verbose: bool = True) -> dict:
+    """Time ``args.batches`` packed batches with ``args.framework`` on an initialised process group
+    (or one GPU when ``group`` is None) and return the summary (max over ranks per batch)."""
     dists = {"lognormal8k": synth.LOGNORMAL_8K, "lognormal16k": synth.LOGNORMAL_16K, "mixture": synth.MIXTURE}
     spec = PlanSpec(world, world, args.tokens, args.n_heads, args.n_kv_heads, 128, args.block_size, 0, args.mask,
                     dists[args.length_dist], seed=args.seed, n_stages=args.stages,
                     build_instruction_plans=args.framework == "nccl-plan")
     hbm, tf_peak, src = measured_peaks()
-    total_max_ms, total_flops, total_pull = 0.0, 0.0, 0.0
+    total_max_ms, total_flops, total_roof = 0.0, 0.0, 0.0
     ex = None
     for b in range(args.batches):
         plan = plan_iteration(spec, b, rank)
@@ -92,7 +79,7 @@ def main(argv=None):
         H, Hkv = args.n_heads, args.n_kv_heads
         g = torch.Generator(device=dev).manual_seed(1000 + b * 17 + rank)
         if args.framework == "dcp":
-            cap = int(args.tokens * 1.3) + 4 * args.block_size
+            cap = int(args.tokens // world * 1.5) + 4 * args.block_size
             if ex is None:
                 ex = FusedAttentionExecutor(H, Hkv, cap, cap, cap, dev, group)
             ex.prepare(p)
@@ -107,35 +94,17 @@ def main(argv=None):
                 ex.forward()
                 if args.mode == "fwdbwd":
                     ex.backward(ldo)
-        elif args.framework == "ulysses":
-            from .baselines import UlyssesAttention
+        elif args.framework in ("ulysses", "ring", "zigzag", "double-ring", "a2a+p2p"):
+            from .baselines import make_baseline
             assert args.mask == "causal", "the library attention kernel only knows causal masks"
-            ua = UlyssesAttention(group, plan.seqlens, H, Hkv)
-            n = ua.counts[rank]
+            attn, n = make_baseline(args.framework, group, plan.seqlens, H, Hkv, rank, world)
             q = torch.randn(n, H, 128, device=dev, generator=g).bfloat16().requires_grad_(True)
             k = torch.randn(n, Hkv, 128, device=dev, generator=g).bfloat16().requires_grad_(True)
             v = torch.randn(n, Hkv, 128, device=dev, generator=g).bfloat16().requires_grad_(True)
             do = torch.randn(n, H, 128, device=dev, generator=g).bfloat16()
 
             def step():
-                out = ua(q, k, v)
-                if args.mode == "fwdbwd":
-                    out.backward(do)
-                    q.grad = k.grad = v.grad = None
-        elif args.framework in ("ring", "zigzag"):
-            from .baselines import RingAttention
-            assert args.mask == "causal", "the library attention kernel only knows causal masks"
-            assert group is not None, "ring attention needs at least two ranks"
-            # lengths are rounded down to multiples of 2 x ranks (at most 2P - 1 tokens per sequence)
-            ra = RingAttention(group, RingAttention.adjust_seqlens(plan.seqlens, world), zigzag=args.framework == "zigzag")
-            n = ra.cu[-1]
-            q = torch.randn(n, H, 128, device=dev, generator=g).bfloat16().requires_grad_(True)
-            k = torch.randn(n, Hkv, 128, device=dev, generator=g).bfloat16().requires_grad_(True)
-            v = torch.randn(n, Hkv, 128, device=dev, generator=g).bfloat16().requires_grad_(True)
-            do = torch.randn(n, H, 128, device=dev, generator=g).bfloat16()
-
-            def step():
-                out = ra(q, k, v)
+                out = attn(q, k, v)
                 if args.mode == "fwdbwd":
                     out.backward(do)
                     q.grad = k.grad = v.grad = None
@@ -163,10 +132,11 @@ def main(argv=None):
             dist.all_reduce(mx, op=dist.ReduceOp.MAX, group=group)
         total_max_ms += max_ms
         total_flops += float(flops[0])
-        if rank == 0:
-            t_compute = float(mx[0]) / (tf_peak * 1e12) * 1e3
-            t_link = float(mx[1]) * (3.0 if args.mode == "fwdbwd" else 1.0) / (NVLINK_GBS * 1e9) * 1e3
-            roof = max(t_compute, t_link)
+        t_compute = float(mx[0]) / (tf_peak * 1e12) * 1e3
+        t_link = float(mx[1]) * (3.0 if args.mode == "fwdbwd" else 1.0) / (NVLINK_GBS * 1e9) * 1e3
+        roof = max(t_compute, t_link)
+        total_roof += roof
+        if rank == 0 and verbose:
             print(json.dumps({"batch": b, "framework": args.framework, "mask": args.mask, "n_gpus": world,
                               "n_seqs": len(plan.seqlens), "max_seqlen": max(plan.seqlens), "ms_max_over_ranks": round(max_ms, 3),
                               "ms_mean": round(mean_ms, 3), "tflops_per_gpu": round(float(flops[0]) / world / max_ms / 1e9, 1),
@@ -175,14 +145,46 @@ def main(argv=None):
     if ex is not None:
         torch.cuda.synchronize()
         ex.check_status()
+    return {"summary": True, "framework": args.framework, "mask": args.mask, "n_gpus": world,
+            "tokens_per_batch": args.tokens, "batches": args.batches, "mode": args.mode,
+            "avg_ms_per_batch": round(total_max_ms / args.batches, 3), "total_ms": round(total_max_ms, 3),
+            "aggregate_tflops": round(total_flops / total_max_ms / 1e9, 1),
+            f"fraction_of_roofline_({src}_peaks)": round(total_roof / total_max_ms, 3)}
+
+
+FRAMEWORK_NAMES = {"dcp": "DCP", "ulysses": "Ulysses", "ring": "Ring", "zigzag": "ZigzagRing", "nccl-plan": "NCCLPlan",
+                   "double-ring": "DoubleRing", "a2a+p2p": "HierarchicalA2AP2P"}
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--framework", default="dcp", choices=sorted(FRAMEWORK_NAMES))
+    ap.add_argument("--mask", default="causal")
+    ap.add_argument("--tokens", type=int, default=131072)
+    ap.add_argument("--batches", type=int, default=3)
+    ap.add_argument("--n-heads", type=int, default=32)
+    ap.add_argument("--n-kv-heads", type=int, default=8)
+    ap.add_argument("--block-size", type=int, default=2048)
+    ap.add_argument("--length-dist", default="lognormal8k", choices=["lognormal8k", "lognormal16k", "mixture"])
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--stages", type=int, default=None)
+    ap.add_argument("--mode", default="fwdbwd", choices=["fwd", "fwdbwd"])
+    ap.add_argument("--seed", type=int, default=0)
+    args = ap.parse_args(argv)
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    group = None
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+        group = dist.group.WORLD
+    summary = run_batches(args, group, dev, rank, world)
     if rank == 0:
-        name = {"dcp": "DCP", "ulysses": "Ulysses", "ring": "Ring", "zigzag": "ZigzagRing",
-                "nccl-plan": "NCCLPlan"}[args.framework]
-        print(f"{name}: total time {total_max_ms:.3f} ms")
-        print(json.dumps({"summary": True, "framework": args.framework, "mask": args.mask, "n_gpus": world,
-                          "tokens_per_batch": args.tokens, "batches": args.batches, "mode": args.mode,
-                          "avg_ms_per_batch": round(total_max_ms / args.batches, 3),
-                          "aggregate_tflops": round(total_flops / total_max_ms / 1e9, 1)}), flush=True)
+        print(f"{FRAMEWORK_NAMES[args.framework]}: total time {summary['total_ms']:.3f} ms")
+        print(json.dumps(summary), flush=True)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()

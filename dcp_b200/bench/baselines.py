@@ -325,3 +325,16 @@ class RingAttention:
         if self._first.device != q.device:
             self._first, self._second = self._first.to(q.device), self._second.to(q.device)
         return _RingFn.apply(q, k, v, self)
+
+
+def make_baseline(framework: str, group, seqlens: Sequence[int], n_heads: int, n_kv_heads: int, rank: int, world: int):
+    """-> (attention callable (q, k, v) -> out, number of local tokens) for a baseline framework."""
+    if framework == "ulysses":
+        ua = UlyssesAttention(group, seqlens, n_heads, n_kv_heads)
+        return ua, ua.counts[rank]
+    if framework in ("ring", "zigzag"):
+        assert group is not None, "ring attention needs at least two ranks"
+        # lengths are rounded down to multiples of 2 x ranks (at most 2P - 1 tokens per sequence)
+        ra = RingAttention(group, RingAttention.adjust_seqlens(seqlens, world), zigzag=framework == "zigzag")
+        return ra, ra.cu[-1]
+    raise ValueError(f"unknown baseline framework {framework!r}")

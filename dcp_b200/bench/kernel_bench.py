@@ -79,7 +79,7 @@ def bench_attention(kind, args):
         rows.append(A.AttnRow(b0, n, list(range(hq)), [(k0, min(bs, nkv - k0)) for k0 in range(0, nkv, bs)],
                               rng[b0:b0 + n], 0, b0, 0, b0, [(0, k0) for k0 in range(0, nkv, bs)]))
     scale = 128 ** -0.5
-    ft = A.build_fwd_tables(rows, bs, dev)
+    ft = A.build_fwd_tables(rows, bs, dev, tile_m=128 if args.variant in (0, 1) else 256)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
     fwd = lambda: A.attn_fwd(q, kv, ft, [out], [lse], scale, status, args.variant)
     if kind == "attn_fwd":
@@ -182,7 +182,7 @@ def main():
     ap.add_argument("--hkv", type=int, default=8)
     ap.add_argument("--block", type=int, default=2048)
     ap.add_argument("--mask", default="causal", choices=["full", "causal", "lambda"])
-    ap.add_argument("--variant", type=int, default=0)
+    ap.add_argument("--variant", type=int, default=2, help="forward kernel: 2 = two query tiles per CTA (default), 0 / 1 = one tile per CTA with P in TMEM / shared memory")
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--timeline", action="store_true", help="print per-phase cycle counts of one backward CTA")
     ap.add_argument("--skip-dq", action="store_true", help="backward without the dQ drain (upper bound probe)")

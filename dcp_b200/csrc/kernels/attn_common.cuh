@@ -89,6 +89,13 @@ struct KvTileIter {
     }
     return false;
   }
+  // the same two tests for another set of bounds (a sub-tile of the rows `b` covers) on the current tile
+  __device__ __forceinline__ bool needed_by(const TileBounds& tb) const {
+    return (pos0 < tb.u0e && pos0 + n_valid > tb.u0s) || (pos0 < tb.u1e && pos0 + n_valid > tb.u1s);
+  }
+  __device__ __forceinline__ bool full_for(const TileBounds& tb) const {
+    return (n_valid == kTileN) && ((tb.i0s <= pos0 && tb.i0e >= pos0 + n_valid) || (tb.i1s <= pos0 && tb.i1e >= pos0 + n_valid));
+  }
 };
 
 }  // namespace dcpk

@@ -9,6 +9,16 @@
 //  adamw_all_gather      AdamW on the fp32 master shard; the updated bf16 parameters are stored
 //                        straight into every rank's parameter buffer (the all-gather is the
 //                        epilogue of the update).
+//  cast_all_gather       bf16(master shard) stored into every rank's parameter buffer (resume).
+//
+// The flat buffers are cut into buckets (one per decoder layer plus the embeddings / head); a
+// bucket's reduce-scatter is launched on a side stream as soon as the layer's backward has
+// written its gradients, so the reduction overlaps the rest of the backward pass.
+//
+// Failure containment: every kernel that changes optimizer state or parameters takes the status
+// words of the arenas whose barriers guard its inputs; if either is nonzero (a barrier wait ran
+// out, a table was bad) the kernel returns without touching master weights, moments, main
+// gradients or parameters, so a detected failure never reaches the weights.
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -18,10 +28,18 @@ namespace dcpk {
 static constexpr int kMaxRanks = 16;
 struct GradPtrs { const void* p[kMaxRanks]; };
 struct ParamPtrs { void* p[kMaxRanks]; };
+struct StatusPtrs { const int* a; const int* b; };
+
+__device__ __forceinline__ bool failed(const StatusPtrs& st) {
+  return (st.a && *reinterpret_cast<const volatile int*>(st.a) != 0) ||
+         (st.b && *reinterpret_cast<const volatile int*>(st.b) != 0);
+}
 
 __global__ void grad_reduce_scatter_kernel(GradPtrs grads, int world, size_t shard_off, size_t shard_len, float scale,
-                                           float* __restrict__ main_grad, float* __restrict__ sq_norm) {
+                                           float* __restrict__ main_grad, float* __restrict__ sq_norm,
+                                           StatusPtrs st) {
   // shard_off / shard_len in elements, both multiples of 8
+  if (failed(st)) return;
   const size_t n_vec = shard_len / 8;
   float local_sq = 0.f;
   for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n_vec; i += size_t(gridDim.x) * blockDim.x) {
@@ -49,7 +67,8 @@ __global__ void grad_reduce_scatter_kernel(GradPtrs grads, int world, size_t sha
 __global__ void adamw_all_gather_kernel(float* __restrict__ master, float* __restrict__ m, float* __restrict__ v,
                                         const float* __restrict__ grad, ParamPtrs params, int world, size_t shard_off,
                                         size_t shard_len, float lr, float beta1, float beta2, float eps, float wd,
-                                        float bc1, float bc2, const float* __restrict__ clip_coef) {
+                                        float bc1, float bc2, const float* __restrict__ clip_coef, StatusPtrs st) {
+  if (failed(st)) return;
   const float clip = clip_coef ? *clip_coef : 1.f;
   const size_t n_vec = shard_len / 8;
   for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n_vec; i += size_t(gridDim.x) * blockDim.x) {
@@ -105,7 +124,8 @@ __global__ void fused_rs_adamw_ag_kernel(GradPtrs grads, ParamPtrs params, int w
                                          size_t shard_len, float scale, float* __restrict__ master,
                                          float* __restrict__ m, float* __restrict__ v, float lr, float beta1,
                                          float beta2, float eps, float wd, float bc1, float bc2,
-                                         const float* __restrict__ clip_coef) {
+                                         const float* __restrict__ clip_coef, StatusPtrs st) {
+  if (failed(st)) return;
   const float gscale = scale * (clip_coef ? *clip_coef : 1.f);
   const size_t n_vec = shard_len / 8;
   for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n_vec; i += size_t(gridDim.x) * blockDim.x) {
@@ -145,6 +165,23 @@ __global__ void fused_rs_adamw_ag_kernel(GradPtrs grads, ParamPtrs params, int w
   }
 }
 
+// bf16(master) -> every rank's parameter buffer: rebuilds the replicated bf16 parameters from the
+// sharded fp32 master weights (after loading a checkpoint)
+__global__ void cast_all_gather_kernel(const float* __restrict__ master, ParamPtrs params, int world, size_t shard_off,
+                                       size_t shard_len) {
+  const size_t n_vec = shard_len / 8;
+  for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n_vec; i += size_t(gridDim.x) * blockDim.x) {
+    const float4 a = reinterpret_cast<const float4*>(master + i * 8)[0];
+    const float4 b = reinterpret_cast<const float4*>(master + i * 8)[1];
+    uint4 packed;
+    __nv_bfloat162* pk = reinterpret_cast<__nv_bfloat162*>(&packed);
+    pk[0] = __floats2bfloat162_rn(a.x, a.y); pk[1] = __floats2bfloat162_rn(a.z, a.w);
+    pk[2] = __floats2bfloat162_rn(b.x, b.y); pk[3] = __floats2bfloat162_rn(b.z, b.w);
+    for (int r = 0; r < world; ++r)
+      reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(params.p[r]) + shard_off)[i] = packed;
+  }
+}
+
 }  // namespace dcpk
 
 using namespace dcpk;
@@ -163,7 +200,7 @@ extern "C" int dcpk_grad_sqnorm(const void* const* grad_ptrs, int world, long sh
 extern "C" int dcpk_fused_rs_adamw_ag(const void* const* grad_ptrs, void* const* param_ptrs, int world, long shard_off,
                                       long shard_len, float scale, float* master, float* m, float* v, float lr,
                                       float beta1, float beta2, float eps, float wd, int step, const float* clip_coef,
-                                      void* stream) {
+                                      const int* status_a, const int* status_b, void* stream) {
   if (shard_len <= 0) return 0;
   if (world > kMaxRanks || shard_off % 8 || shard_len % 8) return -3;
   GradPtrs g;
@@ -175,24 +212,28 @@ extern "C" int dcpk_fused_rs_adamw_ag(const void* const* grad_ptrs, void* const*
   const float bc1 = 1.f - powf(beta1, float(step)), bc2 = 1.f - powf(beta2, float(step));
   fused_rs_adamw_ag_kernel<<<148 * 4, 256, 0, static_cast<cudaStream_t>(stream)>>>(
       g, p, world, size_t(shard_off), size_t(shard_len), scale, master, m, v, lr, beta1, beta2, eps, wd, bc1, bc2,
-      clip_coef);
+      clip_coef, StatusPtrs{status_a, status_b});
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
 
+// n_ctas: grid size (0 = fill the GPU).  A reduce that overlaps the backward pass is given a small
+// grid so it trickles over NVLink next to the GEMMs instead of taking their SMs.
 extern "C" int dcpk_grad_reduce_scatter(const void* const* grad_ptrs, int world, long shard_off, long shard_len,
-                                        float scale, float* main_grad, float* sq_norm, void* stream) {
+                                        float scale, float* main_grad, float* sq_norm, int n_ctas,
+                                        const int* status_a, const int* status_b, void* stream) {
   if (shard_len <= 0) return 0;
   if (world > kMaxRanks || shard_off % 8 || shard_len % 8) return -3;
   GradPtrs g;
   for (int i = 0; i < kMaxRanks; ++i) g.p[i] = i < world ? grad_ptrs[i] : nullptr;
-  grad_reduce_scatter_kernel<<<148 * 4, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      g, world, size_t(shard_off), size_t(shard_len), scale, main_grad, sq_norm);
+  grad_reduce_scatter_kernel<<<n_ctas > 0 ? n_ctas : 148 * 4, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      g, world, size_t(shard_off), size_t(shard_len), scale, main_grad, sq_norm, StatusPtrs{status_a, status_b});
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
 
 extern "C" int dcpk_adamw_all_gather(float* master, float* m, float* v, const float* grad, void* const* param_ptrs,
                                      int world, long shard_off, long shard_len, float lr, float beta1, float beta2,
-                                     float eps, float wd, int step, const float* clip_coef, void* stream) {
+                                     float eps, float wd, int step, const float* clip_coef, const int* status_a,
+                                     const int* status_b, void* stream) {
   if (shard_len <= 0) return 0;
   if (world > kMaxRanks || shard_off % 8 || shard_len % 8) return -3;
   ParamPtrs p;
@@ -200,6 +241,17 @@ extern "C" int dcpk_adamw_all_gather(float* master, float* m, float* v, const fl
   const float bc1 = 1.f - powf(beta1, float(step)), bc2 = 1.f - powf(beta2, float(step));
   adamw_all_gather_kernel<<<148 * 4, 256, 0, static_cast<cudaStream_t>(stream)>>>(
       master, m, v, grad, p, world, size_t(shard_off), size_t(shard_len), lr, beta1, beta2, eps, wd, bc1, bc2,
-      clip_coef);
+      clip_coef, StatusPtrs{status_a, status_b});
+  return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}
+
+extern "C" int dcpk_cast_all_gather(const float* master, void* const* param_ptrs, int world, long shard_off,
+                                    long shard_len, void* stream) {
+  if (shard_len <= 0) return 0;
+  if (world > kMaxRanks || shard_off % 8 || shard_len % 8) return -3;
+  ParamPtrs p;
+  for (int i = 0; i < kMaxRanks; ++i) p.p[i] = i < world ? param_ptrs[i] : nullptr;
+  cast_all_gather_kernel<<<148 * 4, 256, 0, static_cast<cudaStream_t>(stream)>>>(master, p, world, size_t(shard_off),
+                                                                                size_t(shard_len));
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }

@@ -267,6 +267,19 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
   return r;
 }
+// fp32 pair -> packed bf16 by truncation (one byte-permute on the integer pipe).  The rounding
+// conversion instruction shares the special-function pipe with ex2 (16 per clock per SM), where the
+// softmax loops are bound; callers pre-scale the values by kTruncScale so that truncation is
+// unbiased on average (a value's mantissa lies 128..256 bf16 ulps above its power of two, so the
+// factor adds 0.35..0.7 ulp before the cut), and undo the factor where it does not cancel.
+static constexpr float kTruncScale = 1.0027f;
+static constexpr float kTruncLog2 = 0.0038900f;   // log2(kTruncScale)
+static constexpr float kTruncLn = 0.0026964f;     // ln(kTruncScale)
+__device__ __forceinline__ uint32_t pack_bf16x2_trunc(float lo, float hi) {
+  uint32_t r;
+  asm("prmt.b32 %0, %1, %2, 0x7632;" : "=r"(r) : "r"(__float_as_uint(lo)), "r"(__float_as_uint(hi)));
+  return r;
+}
 __device__ __forceinline__ uint64_t global_timer_ns() {
   uint64_t t;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));

@@ -224,6 +224,8 @@ class PlanService:
         self._pending: Dict[int, "cf.Future"] = {}
         self._next_submit = start
         self.wait_seconds = 0.0
+        self.waits: List[float] = []          # seconds get() blocked, per call
+        self.plan_seconds: List[float] = []   # planning time of every plan handed out
 
     def _submit_up_to(self, last: int) -> None:
         while self._next_submit <= last:
@@ -239,7 +241,10 @@ class PlanService:
         t0 = time.time()
         fut = self._pending.pop(iteration, None)
         plan = fut.result() if fut is not None else plan_iteration(self.spec, iteration, self.rank)
-        self.wait_seconds += time.time() - t0
+        waited = time.time() - t0
+        self.wait_seconds += waited
+        self.waits.append(waited)
+        self.plan_seconds.append(plan.plan_seconds)
         return plan
 
     def close(self) -> None:

@@ -217,6 +217,10 @@ class _DecoderLayerFn(torch.autograd.Function):
         dx, dw1 = model_ops.rmsnorm_bwd_raw(x, w1, rstd1, dh1)
         dx.add_(dx_mid)
         ngrad(w1, dw1)
+        if model.grad_ready_hook is not None and not model.accumulate_grads:
+            # every matrix gradient of this layer is final: its bucket can be reduced over the
+            # data-parallel ranks while the layers below are still in their backward
+            model.grad_ready_hook(model.layer_bucket(l))
         return dx, None, None, None, None, None
 
 
@@ -268,6 +272,8 @@ class LlamaModel:
         # None keeps the autograd + checkpoint path
         self.layer_levels: Optional[List[int]] = None
         self.accumulate_grads = False   # True: weight gradients are added to .grad instead of written
+        # called with a bucket index (see grad_buckets) when that bucket's gradients are final
+        self.grad_ready_hook = None
         # flat layout: parameters every tensor-parallel rank holds in full come first, the sharded
         # matrices after them, so "the replicated part" is one contiguous range of the buffers
         shapes: List[Tuple[str, Tuple[int, ...]]] = self.param_shapes(cfg)
@@ -374,8 +380,32 @@ class LlamaModel:
     def parameters(self):
         return list(self.p.values())
 
+    # ---- gradient buckets: bucket 0 = everything that is not a decoder-layer matrix (embedding,
+    # norm weights, LM head; final only when the whole backward is done), bucket 1 + l = the four
+    # matrices of layer l, which are contiguous in the flat buffers
+    def grad_buckets(self) -> List[Tuple[int, int]]:
+        first = self.offsets["l0.wqkv"][0]
+        out = [(0, first)]
+        for l in range(self.cfg.n_layers):
+            lo = self.offsets[f"l{l}.wqkv"][0]
+            hi = self.offsets[f"l{l + 1}.wqkv"][0] if l + 1 < self.cfg.n_layers else self.n_flat
+            out.append((lo, hi - lo))
+        return out
+
+    @staticmethod
+    def layer_bucket(l: int) -> int:
+        return 1 + l
+
     def zero_grad(self) -> None:
-        self.grads_flat.zero_()
+        """Gradients that autograd accumulates into must start at zero; the hand-written layer
+        backward overwrites every decoder-layer gradient (matrices and norm weights), so only the
+        embedding, the final norm and the LM head are cleared in that mode."""
+        manual = self.layer_levels is not None and self.grads_flat.is_cuda and not self.accumulate_grads
+        if not manual:
+            self.grads_flat.zero_()
+            return
+        for name in ("embed", "norm_f", "lm_head"):
+            self.p[name].grad.zero_()
 
     def set_executor(self, executor) -> None:
         self.executor = executor

@@ -16,7 +16,8 @@ import torch
 
 from . import _lib
 
-TILE_M = 128
+TILE_M = 128          # query rows per softmax warpgroup
+TILE_M_PAIR = 256     # query rows per CTA of the two-tile forward kernel (the default)
 TILE_N = 128
 HEAD_DIM = 128
 
@@ -51,14 +52,16 @@ class FwdTables:
     n_tiles: int
     block_size: int
     flops: float = 0.0
+    tile_m: int = TILE_M_PAIR   # 256: two-tile kernel (attn_fwd_pair.cu); 128: one tile per CTA (attn_fwd.cu)
 
     def to(self, device, non_blocking: bool = True) -> "FwdTables":
         mv = lambda t: t.to(device, non_blocking=non_blocking)
-        return FwdTables(mv(self.tiles), mv(self.kv_entries), mv(self.masks), self.n_tiles, self.block_size, self.flops)
+        return FwdTables(mv(self.tiles), mv(self.kv_entries), mv(self.masks), self.n_tiles, self.block_size, self.flops,
+                         self.tile_m)
 
     def pin(self) -> "FwdTables":
         return FwdTables(self.tiles.pin_memory(), self.kv_entries.pin_memory(), self.masks.pin_memory(), self.n_tiles,
-                         self.block_size, self.flops)
+                         self.block_size, self.flops, self.tile_m)
 
 
 def _pair_count(ranges: np.ndarray) -> float:
@@ -67,7 +70,10 @@ def _pair_count(ranges: np.ndarray) -> float:
     return float(np.maximum(r[:, 1] - r[:, 0], 0).sum() + np.maximum(r[:, 3] - r[:, 2], 0).sum())
 
 
-def build_fwd_tables(rows: Sequence[AttnRow], block_size: int, device) -> FwdTables:
+def build_fwd_tables(rows: Sequence[AttnRow], block_size: int, device, tile_m: int = TILE_M_PAIR) -> FwdTables:
+    """Flatten Q blocks into CTA tiles of ``tile_m`` query rows (256: two 128-row tiles per CTA that
+    share every K/V tile; 128: the one-tile kernel)."""
+    assert tile_m in (TILE_M, TILE_M_PAIR)
     tiles, entries, masks = [], [], []
     mask_row = 0
     pairs = 0.0
@@ -78,12 +84,12 @@ def build_fwd_tables(rows: Sequence[AttnRow], block_size: int, device) -> FwdTab
         assert rng.shape[0] == row.n_tokens
         masks.append(rng)
         pairs += _pair_count(rng) * len(row.heads)
-        n_sub = (row.n_tokens + TILE_M - 1) // TILE_M
+        n_sub = (row.n_tokens + tile_m - 1) // tile_m
         for t in range(n_sub):
-            n_rows = min(TILE_M, row.n_tokens - t * TILE_M)
+            n_rows = min(tile_m, row.n_tokens - t * tile_m)
             for h in row.heads:
-                tiles.append((row.q_row + t * TILE_M, n_rows, int(h), kv_off, len(row.kv),
-                              mask_row + t * TILE_M, row.out_dev, row.out_row + t * TILE_M))
+                tiles.append((row.q_row + t * tile_m, n_rows, int(h), kv_off, len(row.kv),
+                              mask_row + t * tile_m, row.out_dev, row.out_row + t * tile_m))
         mask_row += row.n_tokens
     # longest tiles first: the grid is scheduled in index order, so this is LPT packing
     tiles.sort(key=lambda x: -x[4])
@@ -91,7 +97,7 @@ def build_fwd_tables(rows: Sequence[AttnRow], block_size: int, device) -> FwdTab
     e_np = np.asarray(entries, dtype=np.int32).reshape(-1, 2)
     m_np = np.concatenate(masks, axis=0) if masks else np.zeros((0, 4), np.int32)
     to = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(device, non_blocking=True)
-    return FwdTables(to(t_np), to(e_np), to(m_np), len(tiles), block_size, flops=4.0 * pairs * HEAD_DIM)
+    return FwdTables(to(t_np), to(e_np), to(m_np), len(tiles), block_size, flops=4.0 * pairs * HEAD_DIM, tile_m=tile_m)
 
 
 def _ptr_array(tensors) -> ctypes.Array:
@@ -104,7 +110,8 @@ def _ptr_array(tensors) -> ctypes.Array:
 def attn_fwd(q_arena: torch.Tensor, kv_arena: torch.Tensor, tables: FwdTables, out_dsts, lse_dsts,
              scale: float, status: torch.Tensor, variant: int = 0, lse_stride: Optional[int] = None,
              lse_stride_b: Optional[int] = None, n_dst_a: Optional[int] = None):
-    """Run the forward kernel.
+    """Run the forward kernel the tables were built for (``tables.tile_m``); ``variant`` only applies to
+    the one-tile kernel (0: P in TMEM, 1: P through shared memory).
 
     q_arena: bf16 [rows, hq, 128]; kv_arena: bf16 [rows, 2, hkv, 128]; out_dsts / lse_dsts: lists of
     destination arenas (tensors or raw device addresses; index 0 = this rank), every out arena
@@ -117,6 +124,18 @@ def attn_fwd(q_arena: torch.Tensor, kv_arena: torch.Tensor, tables: FwdTables, o
     hq, hkv = q_arena.shape[1], kv_arena.shape[2]
     if lse_stride is None:
         lse_stride = lse_dsts[0].shape[1]
+    if tables.tile_m == TILE_M_PAIR:
+        rc = lib.dcpk_attn_fwd_pair(
+            _lib.ptr(q_arena), ctypes.c_long(q_arena.shape[0]), _lib.ptr(kv_arena), ctypes.c_long(kv_arena.shape[0]),
+            ctypes.c_int(hq), ctypes.c_int(hkv), _lib.ptr(tables.tiles), ctypes.c_int(tables.n_tiles),
+            _lib.ptr(tables.kv_entries), ctypes.c_int(tables.kv_entries.shape[0]), _lib.ptr(tables.masks),
+            ctypes.c_int(tables.masks.shape[0]), _ptr_array(out_dsts), _ptr_array(lse_dsts),
+            ctypes.c_int(len(out_dsts)), ctypes.c_int(lse_stride),
+            ctypes.c_int(lse_stride if lse_stride_b is None else lse_stride_b),
+            ctypes.c_int(len(out_dsts) if n_dst_a is None else n_dst_a), ctypes.c_int(tables.block_size),
+            ctypes.c_float(scale), _lib.ptr(status), _lib.stream_handle())
+        _lib.check(rc, "dcpk_attn_fwd_pair")
+        return
     rc = lib.dcpk_attn_fwd(
         _lib.ptr(q_arena), ctypes.c_long(q_arena.shape[0]), _lib.ptr(kv_arena), ctypes.c_long(kv_arena.shape[0]),
         ctypes.c_int(hq), ctypes.c_int(hkv), _lib.ptr(tables.tiles), ctypes.c_int(tables.n_tiles),

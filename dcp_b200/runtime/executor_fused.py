@@ -56,6 +56,9 @@ class FusedAttentionExecutor:
         # reusing last call's bytes
         self.synchronous = os.environ.get("DCP_B200_SYNCHRONOUS", "0") == "1"
         self.poison = os.environ.get("DCP_B200_POISON", "0") == "1"
+        # time_calls: one CUDA-event pair around every forward() / backward() call (read with call_times())
+        self.time_calls = False
+        self._call_events = []
 
     def _allocate(self, rows) -> None:
         """(Re)create the symmetric arenas for (q rows, kv rows, partial rows).  Collective: every
@@ -198,6 +201,7 @@ class FusedAttentionExecutor:
         Returns views (out [rows, hq, d] bf16, lse [hq, rows] fp32) of this rank's own tokens."""
         p, a = self.program, self.arena
         main = torch.cuda.current_stream(self.device)
+        tok = self._call_begin("fwd")
         self._mark("fwd:start")
         if self.poison:
             self._poison_staging(False)
@@ -230,6 +234,7 @@ class FusedAttentionExecutor:
             self.kernel_launches += 1
         self._mark("fwd:merge")
         torch.cuda.nvtx.range_pop()
+        self._call_end(tok)
         self._staging_valid = True
         return self.out_local(), self.lse_local()
 
@@ -246,6 +251,7 @@ class FusedAttentionExecutor:
         p, a = self.program, self.arena
         main = torch.cuda.current_stream(self.device)
         n = p.q_local_rows
+        tok = self._call_begin("bwd")
         self._mark("bwd:start")
         if self.poison and not self._staging_valid:
             self._poison_staging(True)
@@ -284,10 +290,35 @@ class FusedAttentionExecutor:
             a.barrier()
             self._mark("bwd:wait gradients of peers")
         torch.cuda.nvtx.range_pop()
+        self._call_end(tok)
         return self.dq[:n], self.dkv[:p.kv_local_rows]
 
     def check_status(self) -> None:
         self.arena.check_status()
+
+    def _call_begin(self, kind: str):
+        if not self.time_calls:
+            return None
+        e0 = torch.cuda.Event(enable_timing=True)
+        e0.record(torch.cuda.current_stream(self.device))
+        return (kind, e0)
+
+    def _call_end(self, tok) -> None:
+        if tok is not None:
+            e1 = torch.cuda.Event(enable_timing=True)
+            e1.record(torch.cuda.current_stream(self.device))
+            self._call_events.append((tok[0], tok[1], e1))
+
+    def call_times(self) -> dict:
+        """{"fwd_ms", "bwd_ms", "n_fwd", "n_bwd"}: device time of the attention calls since the last
+        call_times() (barrier waits included), from event pairs on the launching stream."""
+        torch.cuda.synchronize(self.device)
+        out = {"fwd_ms": 0.0, "bwd_ms": 0.0, "n_fwd": 0, "n_bwd": 0}
+        for kind, e0, e1 in self._call_events:
+            out[kind + "_ms"] += e0.elapsed_time(e1)
+            out["n_" + kind] += 1
+        self._call_events = []
+        return out
 
 
 def a_status(ex: FusedAttentionExecutor) -> torch.Tensor:

@@ -55,6 +55,7 @@ class EngineConfig:
     cost_model: Optional[dict] = None
     plan_cache_dir: Optional[str] = None     # reuse plans by batch signature (saved next to checkpoints on resume)
     tp_size: int = 1                # tensor-parallel ranks per model replica (adjacent ranks)
+    overlap_grad_reduce: bool = True   # reduce each layer's gradient bucket during the backward pass
 
 
 def parallel_layout(world: int, tp: int = 1, dcp_size: int = 0) -> dict:
@@ -113,14 +114,19 @@ class TrainEngine:
         self.bufs = FlatBuffers(n_flat, device, self.opt_group if n_cp > 1 else None)
         self.model = LlamaModel(m, device, self.bufs.params, self.bufs.grads, seed=cfg.seed, recompute=cfg.recompute,
                                 lm_head_chunk=cfg.lm_head_chunk, tp_group=self.tp_group, tp_rank=self.tp_rank, tp_size=tp)
-        self.optimizer = ShardedAdamW(self.bufs, cfg.lr, weight_decay=cfg.weight_decay, clip_grad=cfg.clip_grad,
-                                      group=self.opt_group if n_cp > 1 else None, tp_group=self.tp_group,
-                                      n_replicated=self.model.n_replicated)
         group_tokens = cfg.tokens_per_step // (n_cp // dcp)
         cap = int(group_tokens * 1.3) + 4 * cfg.block_size
         self.executor = FusedAttentionExecutor(m.n_heads, m.n_kv_heads, cap, cap, 2 * cap, device,
                                                self.dcp_group if dcp > 1 else None)
         self.model.set_executor(self.executor)
+        # one gradient bucket per decoder layer (+ one for embeddings / norms / head); with several
+        # ranks each bucket is reduced on a side stream as soon as its layer's backward is done
+        self.optimizer = ShardedAdamW(self.bufs, cfg.lr, weight_decay=cfg.weight_decay, clip_grad=cfg.clip_grad,
+                                      group=self.opt_group if n_cp > 1 else None, tp_group=self.tp_group,
+                                      n_replicated=self.model.n_replicated, buckets=self.model.grad_buckets(),
+                                      extra_status=self.executor.arena.status)
+        if self.optimizer.overlap and cfg.overlap_grad_reduce:
+            self.model.grad_ready_hook = self.optimizer.reduce_bucket
         self.activation_levels = self._plan_activations(group_tokens // dcp)
         self.spec = PlanSpec(n_cp, dcp, cfg.tokens_per_step, m.n_heads, m.n_kv_heads, m.head_dim, cfg.block_size,
                              cfg.head_block_size, cfg.mask, cfg.length_dist or synth.LOGNORMAL_8K, m.vocab, cfg.seed,
@@ -131,6 +137,7 @@ class TrainEngine:
                              cache_dir=cfg.plan_cache_dir)
         self.plans = PlanService(self.spec, self.cp_index, cfg.planner_workers, cfg.lookahead)
         self.iteration = 0
+        self.last_global_tokens = 0
         self.h2d_bytes = 0
         self.d2h_bytes = 0
 
@@ -184,6 +191,7 @@ class TrainEngine:
         """Public API: plan (or fetch) the iteration, copy its inputs in, step, read the loss back."""
         if plan is None:
             plan = self.plans.get(self.iteration)
+        self.last_global_tokens = plan.n_global_tokens
         toks, labels, pos = self.stage_inputs(plan)
         loss = self.run_step(toks, labels, pos, plan.n_global_tokens)
         if self.n_cp_ranks > 1:
@@ -191,9 +199,25 @@ class TrainEngine:
             dist.all_reduce(loss, group=self.opt_group)   # one rank per token (tensor-parallel peers hold copies)
         value = float(loss.item())         # device -> host read of the step's result
         self.d2h_bytes = loss.numel() * loss.element_size()
-        self.executor.check_status()
+        self.check_status()
         self.iteration += 1
         return value
+
+    def check_status(self) -> None:
+        """Raise if a device-side wait of this step ran out (attention arenas or optimizer arena).
+        The update kernels read the same status words and leave the weights alone when one is set."""
+        self.executor.check_status()
+        self.optimizer.check_status()
+
+    def reconfigure(self, tokens_per_step: int, length_dist=None, mask: Optional[str] = None) -> None:
+        """Switch the synthetic workload (token budget, length distribution, mask) without rebuilding
+        the model: a new plan service starts at the current iteration."""
+        import dataclasses
+        self.plans.close()
+        self.spec = dataclasses.replace(self.spec, tokens_per_step=tokens_per_step,
+                                        length_dist=length_dist or self.spec.length_dist, mask=mask or self.spec.mask)
+        self.plans = PlanService(self.spec, self.cp_index, self.cfg.planner_workers, self.cfg.lookahead,
+                                 start=self.iteration)
 
     def close(self) -> None:
         self.plans.close()
@@ -222,20 +246,11 @@ class TrainEngine:
         self.iteration = int(state["iteration"])
         torch.set_rng_state(state["rng"].cpu())
         torch.cuda.set_rng_state(state["cuda_rng"].cpu(), self.device)
-        # every rank rebuilds the bf16 parameters from the fp32 master shards
-        o = self.optimizer
-        self.bufs.arena.barrier()
-        self.bufs.params[o.shard_off:o.shard_off + o.shard_len].copy_(o.master)
-        if self.n_cp_ranks > 1:
-            import torch.distributed as dist
-            shards = [torch.empty_like(self.bufs.params[:o.shard_len]) for _ in range(self.n_cp_ranks)]
-            dist.all_gather(shards, self.bufs.params[o.shard_off:o.shard_off + o.shard_len].contiguous(),
-                            group=self.opt_group)
-            per = o.shard_len
-            for r, s in enumerate(shards):
-                n = min(per, self.bufs.n_flat - r * per)
-                if n > 0:
-                    self.bufs.params[r * per:r * per + n].copy_(s[:n])
+        # every rank's bf16 parameters are rebuilt from the sharded fp32 master weights: each rank
+        # stores its slices (same slicing formula as the optimizer) into every peer's buffer
+        self.optimizer.rebuild_params()
+        torch.cuda.synchronize(self.device)
+        self.check_status()
         self.plans.close()
         self.plans = PlanService(self.spec, self.cp_index, self.cfg.planner_workers, self.cfg.lookahead, start=self.iteration)
 

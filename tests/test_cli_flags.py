@@ -57,10 +57,10 @@ def test_bench_and_train_build_their_engine_configs():
     bench = importlib.util.module_from_spec(spec)
     spec.loader.exec_module(bench)
     a = bench.parse_args(["--gpus", "8", "--dcp-size", "4", "--block-size", "1024", "--tp-size", "2", "--stages", "3",
-                          "--steps", "5"])
+                          "--steps", "5", "--lookahead", "5"])
     cfg, scaling = bench.build_engine_config(a, 8)
     assert (cfg.tokens_per_step, cfg.dcp_size, cfg.block_size, cfg.tp_size, cfg.n_stages, cfg.mask, cfg.lookahead) == \
-        (8 * 32768, 4, 1024, 2, 3, "causal", 6)
+        (8 * 32768, 4, 1024, 2, 3, "causal", 5)
     assert scaling == "weak" and cfg.length_dist.kind == "mixture" and cfg.model.n_layers == 32
     cfg, scaling = bench.build_engine_config(bench.parse_args(["--config", "masks", "--model", "tiny"]), 2)
     assert (cfg.tokens_per_step, cfg.mask, scaling, cfg.tp_size, cfg.dcp_size) == (131072, "mixed", "strong", 1, 0)

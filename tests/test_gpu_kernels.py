@@ -43,7 +43,7 @@ CASES = [
 
 
 @pytest.mark.parametrize("case", CASES)
-@pytest.mark.parametrize("variant", [0, 1])
+@pytest.mark.parametrize("variant", [0, 1, 2])   # one tile per CTA with P in TMEM / in smem; two tiles per CTA
 def test_attention_forward(dev, case, variant):
     nq, kv_blocks, bs, hq, hkv, kind, off = case
     torch.manual_seed(0)
@@ -55,7 +55,7 @@ def test_attention_forward(dev, case, variant):
     status = torch.zeros(1, dtype=torch.int32, device=dev)
     rng = _ranges(kind, nq, off)
     row = A.AttnRow(0, nq, list(range(hq)), [(i * bs, n) for i, n in enumerate(kv_blocks)], rng)
-    tabs = A.build_fwd_tables([row], bs, dev)
+    tabs = A.build_fwd_tables([row], bs, dev, tile_m=256 if variant == 2 else 128)
     A.attn_fwd(q, kv, tabs, [out], [lse], 128 ** -0.5, status, variant)
     torch.cuda.synchronize()
     assert status.item() == 0
