@@ -79,7 +79,7 @@ def bench_attention(kind, args):
         rows.append(A.AttnRow(b0, n, list(range(hq)), [(k0, min(bs, nkv - k0)) for k0 in range(0, nkv, bs)],
                               rng[b0:b0 + n], 0, b0, 0, b0, [(0, k0) for k0 in range(0, nkv, bs)]))
     scale = 128 ** -0.5
-    ft = A.build_fwd_tables(rows, bs, dev, tile_m=128 if args.variant in (0, 1) else 256)
+    ft = A.build_fwd_tables(rows, bs, dev, tile_m=256 if args.variant == 2 else 128)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
     fwd = lambda: A.attn_fwd(q, kv, ft, [out], [lse], scale, status, args.variant)
     if kind == "attn_fwd":

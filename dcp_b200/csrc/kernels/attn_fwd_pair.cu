@@ -39,50 +39,39 @@ struct __align__(1024) PairSmem {
   uint64_t q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], p_ready[2], o_done[2];
   uint32_t tmem_base;
   int abort_word;
-  int red[8][8];
 };
 
-__device__ __forceinline__ void reduce_rows(int (*red)[8], int warp, int lane, bool valid, int s0, int e0, int s1,
-                                            int e1) {
-  bool has0 = valid && e0 > s0, has1 = valid && e1 > s1;
-  int v[8];
-  v[0] = has0 ? s0 : INT_MAX;  v[1] = has0 ? e0 : INT_MIN;
-  v[2] = has1 ? s1 : INT_MAX;  v[3] = has1 ? e1 : INT_MIN;
-  v[4] = valid ? s0 : INT_MIN; v[5] = valid ? e0 : INT_MAX;
-  v[6] = valid ? s1 : INT_MIN; v[7] = valid ? e1 : INT_MAX;
-  v[0] = __reduce_min_sync(0xffffffffu, v[0]);
-  v[1] = __reduce_max_sync(0xffffffffu, v[1]);
-  v[2] = __reduce_min_sync(0xffffffffu, v[2]);
-  v[3] = __reduce_max_sync(0xffffffffu, v[3]);
-  v[4] = __reduce_max_sync(0xffffffffu, v[4]);
-  v[5] = __reduce_min_sync(0xffffffffu, v[5]);
-  v[6] = __reduce_max_sync(0xffffffffu, v[6]);
-  v[7] = __reduce_min_sync(0xffffffffu, v[7]);
-  if (lane == 0) {
-#pragma unroll
-    for (int i = 0; i < 8; ++i) red[warp][i] = v[i];
-  }
-}
+// One 128-key tile of the CTA's KV walk, prepared by the host (build_fwd_tables with tile_m = 256).
+struct KvSub {
+  int row;       // first arena row of the 128 keys
+  int pos0;      // position of the first key in the Q block's concatenated KV
+  int n_valid;   // valid keys (1..128)
+  int flags;     // bit 0 / 1: query tile A / B sees at least one key; bit 2 / 3: A / B sees every pair
+};
 
-__device__ __forceinline__ TileBounds combine_rows(const int (*red)[8], int w0, int w1) {
-  TileBounds b;
-  b.u0s = INT_MAX; b.u0e = INT_MIN; b.u1s = INT_MAX; b.u1e = INT_MIN;
-  b.i0s = INT_MIN; b.i0e = INT_MAX; b.i1s = INT_MIN; b.i1e = INT_MAX;
-  for (int w = w0; w < w1; ++w) {
-    b.u0s = min(b.u0s, red[w][0]); b.u0e = max(b.u0e, red[w][1]);
-    b.u1s = min(b.u1s, red[w][2]); b.u1e = max(b.u1e, red[w][3]);
-    b.i0s = max(b.i0s, red[w][4]); b.i0e = min(b.i0e, red[w][5]);
-    b.i1s = max(b.i1s, red[w][6]); b.i1e = min(b.i1e, red[w][7]);
+// walks the list with the next entry already in registers, so a step never waits on global memory
+struct SubIter {
+  const int4* p;
+  int n, i;
+  int4 cur, ahead;
+  __device__ __forceinline__ void init(const int4* base, int count) {
+    p = base; n = count; i = -1;
+    ahead = count > 0 ? base[0] : make_int4(0, 0, 0, 0);
   }
-  return b;
-}
+  __device__ __forceinline__ bool next() {
+    if (++i >= n) return false;
+    cur = ahead;
+    if (i + 1 < n) ahead = p[i + 1];
+    return true;
+  }
+};
 
 __global__ void __launch_bounds__(kPairThreads, 1)
 attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_kv,
-                     const AttnTile* __restrict__ tiles, const KvEntry* __restrict__ kv_entries,
+                     const AttnTile* __restrict__ tiles, const int4* __restrict__ kv_subs,
                      const int4* __restrict__ masks, PeerPtrs ptrs, int hq, int hkv, int lse_stride_a,
                      int lse_stride_b, int n_dst_a, int n_dst, int q_rows, int block_size, int n_mask_rows,
-                     int n_kv_entries, float scale, int* __restrict__ status) {
+                     int n_kv_subs, float scale, int* __restrict__ status) {
   extern __shared__ uint8_t smem_raw[];
   PairSmem& sm = *reinterpret_cast<PairSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -96,7 +85,7 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                      tile.n_rows > 2 * kTileM || tile.out_row + tile.n_rows > dst_rows || tile.head < 0 ||
                      tile.head >= hq || tile.q_row < 0 || tile.q_row + tile.n_rows > q_rows || tile.n_kv < 0 ||
                      tile.mask_row < 0 || tile.mask_row + tile.n_rows > n_mask_rows || tile.kv_off < 0 ||
-                     tile.kv_off + tile.n_kv > n_kv_entries;
+                     tile.kv_off + tile.n_kv > n_kv_subs;
     if (bad) {
       if (threadIdx.x == 0) atomicExch(status, kStatusBadArgs);
       return;
@@ -128,17 +117,14 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       int4 m = masks[tile.mask_row + X * kTileM + r];
       s0 = m.x; e0 = max(m.y, m.x); s1 = m.z; e1 = max(m.w, m.z);
     }
-    reduce_rows(sm.red, warp, lane, valid, s0, e0, s1, e1);
   }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  // the CTA walks the KV tiles either query tile can see; each tile then tests its own bounds
-  const TileBounds pair_bounds = combine_rows(sm.red, 0, 8);
   const uint32_t tmem = sm.tmem_base;
   volatile int* abort_word = &sm.abort_word;
-  KvTileIter it;
-  it.init(kv_entries + tile.kv_off, tile.n_kv, block_size, pair_bounds);
+  SubIter it;
+  it.init(kv_subs + tile.kv_off, tile.n_kv);
 
   // register rebalancing between warpgroups (setmaxnreg inside each role's branch): the four
   // non-softmax warps give registers up, the softmax warps take them
@@ -161,14 +147,14 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         ok = mbar_wait(&sm.k_empty[st], (u & 1) ^ 1, abort_word);
         if (!ok) break;
         mbar_expect_tx(&sm.k_full[st], kTileBytesP);
-        tma_load_3d(sm.k[st], &tm_kv, &sm.k_full[st], 0, kv_head, it.row);
-        tma_load_3d(sm.k[st] + kHalfBytesP, &tm_kv, &sm.k_full[st], 64, kv_head, it.row);
+        tma_load_3d(sm.k[st], &tm_kv, &sm.k_full[st], 0, kv_head, it.cur.x);
+        tma_load_3d(sm.k[st] + kHalfBytesP, &tm_kv, &sm.k_full[st], 64, kv_head, it.cur.x);
         k_pending[st] = u & 1;
         ok = mbar_wait(&sm.v_empty[st], (u & 1) ^ 1, abort_word);
         if (!ok) break;
         mbar_expect_tx(&sm.v_full[st], kTileBytesP);
-        tma_load_3d(sm.v[st], &tm_kv, &sm.v_full[st], 0, hkv + kv_head, it.row);
-        tma_load_3d(sm.v[st] + kHalfBytesP, &tm_kv, &sm.v_full[st], 64, hkv + kv_head, it.row);
+        tma_load_3d(sm.v[st], &tm_kv, &sm.v_full[st], 0, hkv + kv_head, it.cur.x);
+        tma_load_3d(sm.v[st] + kHalfBytesP, &tm_kv, &sm.v_full[st], 64, hkv + kv_head, it.cur.x);
         v_pending[st] = u & 1;
         ++j;
       }
@@ -186,7 +172,6 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     // ------------------------------------------------------------ UMMA issuer
     constexpr uint32_t idesc_qk = make_idesc_bf16(128, 128, 0, 0);
     constexpr uint32_t idesc_pv = make_idesc_bf16(128, 128, 0, 1);
-    const TileBounds bx[2] = {combine_rows(sm.red, 0, 4), combine_rows(sm.red, 4, 8)};
     bool ok = mbar_wait(&sm.q_full, 0, abort_word);
     int j = 0;
     int cnt[2] = {0, 0};                 // KV tiles issued so far per query tile
@@ -232,7 +217,7 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       bool need_cur[2];
 #pragma unroll
       for (int x = 0; x < 2; ++x) {
-        need_cur[x] = it.needed_by(bx[x]);
+        need_cur[x] = (it.cur.w >> x) & 1;
         // S_X may only be overwritten after P_X of the previous tile was consumed: its PV goes first
         if (need_prev[x]) { ok = issue_pv(x, cnt[x] - 1, j - 1); if (!ok) break; }
         if (need_cur[x]) { issue_qk(x, st); ++cnt[x]; }
@@ -262,12 +247,11 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     const float sl2 = scale * 1.4426950408889634f;
     const float rescale_gap = 8.0f / sl2;   // 8 in the base-2 exponent, expressed in raw score units
     const int len0 = e0 - s0, len1 = e1 - s1;
-    const TileBounds mine = combine_rows(sm.red, 4 * X, 4 * X + 4);
     float m_run = -INFINITY, l_run = 0.f;
     int j = 0;   // KV tiles this query tile took part in
     bool ok = true;
     while (ok && it.next()) {
-      if (!it.needed_by(mine)) continue;
+      if (!((it.cur.w >> X) & 1)) continue;
       ok = mbar_wait(&sm.s_full[X], j & 1, abort_word);
       if (!ok) break;
       tc_fence_after();
@@ -280,16 +264,16 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       float mxp[8];
 #pragma unroll
       for (int i = 0; i < 8; ++i) mxp[i] = -INFINITY;
-      if (it.full_for(mine)) {
+      if ((it.cur.w >> (2 + X)) & 1) {
 #pragma unroll
         for (int c = 0; c < 64; ++c)
           mxp[c & 7] = fmax3(mxp[c & 7], __uint_as_float(sreg[2 * c]), __uint_as_float(sreg[2 * c + 1]));
       } else {
-        const int rel0 = it.pos0 - s0, rel1 = it.pos0 - s1;
+        const int rel0 = it.cur.y - s0, rel1 = it.cur.y - s1, n_valid = it.cur.z;
 #pragma unroll
         for (int c = 0; c < 128; ++c) {
           bool allow = (unsigned(rel0 + c) < unsigned(len0)) || (unsigned(rel1 + c) < unsigned(len1));
-          allow = allow && (c < it.n_valid);
+          allow = allow && (c < n_valid);
           float sv = allow ? __uint_as_float(sreg[c]) : -INFINITY;
           sreg[c] = __float_as_uint(sv);
           mxp[c & 7] = fmaxf(mxp[c & 7], sv);
@@ -406,8 +390,9 @@ static int g_pair_attr_set = 0;
 
 using namespace dcpk;
 
-// Same contract as dcpk_attn_fwd, for tile tables built with 256-row tiles (AttnTile.n_rows <= 256).
-// n_mask_rows / n_kv_entries are the lengths of the mask and KV-entry tables (bounds checks).
+// Same contract as dcpk_attn_fwd, for tile tables built with 256-row tiles (AttnTile.n_rows <= 256):
+// `kv_entries` is the KvSub list (AttnTile.kv_off / n_kv index it), n_mask_rows / n_kv_entries are the
+// lengths of the mask table and of that list (bounds checks).
 extern "C" int dcpk_attn_fwd_pair(const void* q_arena, long q_rows, const void* kv_arena, long kv_rows, int hq,
                                   int hkv, const void* tiles, int n_tiles, const void* kv_entries, int n_kv_entries,
                                   const void* masks, int n_mask_rows, void* const* out_ptrs, float* const* lse_ptrs,
@@ -430,7 +415,7 @@ extern "C" int dcpk_attn_fwd_pair(const void* q_arena, long q_rows, const void* 
     g_pair_attr_set = 1;
   }
   attn_fwd_pair_kernel<<<n_tiles, kPairThreads, smem, static_cast<cudaStream_t>(stream)>>>(
-      tm_q, tm_kv, static_cast<const AttnTile*>(tiles), static_cast<const KvEntry*>(kv_entries),
+      tm_q, tm_kv, static_cast<const AttnTile*>(tiles), static_cast<const int4*>(kv_entries),
       static_cast<const int4*>(masks), pp, hq, hkv, lse_stride_a, lse_stride_b, n_dst_a, n_dst, int(q_rows),
       block_size, n_mask_rows, n_kv_entries, scale, status);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;

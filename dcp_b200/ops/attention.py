@@ -71,33 +71,86 @@ def _pair_count(ranges: np.ndarray) -> float:
 
 
 def build_fwd_tables(rows: Sequence[AttnRow], block_size: int, device, tile_m: int = TILE_M_PAIR) -> FwdTables:
-    """Flatten Q blocks into CTA tiles of ``tile_m`` query rows (256: two 128-row tiles per CTA that
-    share every K/V tile; 128: the one-tile kernel)."""
+    """Flatten Q blocks into CTA tiles of ``tile_m`` query rows.
+
+    tile_m = 128: one tile per CTA (attn_fwd.cu, attn_fwd_split.cu); ``kv_entries`` lists the KV blocks
+    (arena row, tokens) and the kernel derives the 128-key tiles it needs from the mask bounds.
+
+    tile_m = 256: two 128-row tiles per CTA that share every K/V tile (attn_fwd_pair.cu);
+    ``kv_entries`` then is the ready-made walk of the CTA: one int32 x 4 entry per 128-key tile that
+    at least one of the two query tiles can see = (arena row, position of its first key, valid keys,
+    flags) with flags bit 0 / 1 = query tile A / B sees a key of it, bit 2 / 3 = A / B sees every
+    (query, key) pair of it (no per-element masking needed).  ``AttnTile.kv_off / n_kv`` index it.
+    """
     assert tile_m in (TILE_M, TILE_M_PAIR)
     tiles, entries, masks = [], [], []
     mask_row = 0
     pairs = 0.0
+    n_entries = 0
     for row in rows:
-        kv_off = len(entries)
-        entries.extend((int(r), int(n)) for r, n in row.kv)
         rng = np.ascontiguousarray(row.ranges, dtype=np.int32).reshape(-1, 4)
         assert rng.shape[0] == row.n_tokens
         masks.append(rng)
         pairs += _pair_count(rng) * len(row.heads)
         n_sub = (row.n_tokens + tile_m - 1) // tile_m
+        if tile_m == TILE_M:
+            kv_off = n_entries
+            entries.append(np.asarray([(int(r), int(n)) for r, n in row.kv], dtype=np.int32).reshape(-1, 2))
+            n_entries += len(row.kv)
+            per_tile = [(kv_off, len(row.kv))] * n_sub
+        else:
+            per_tile = []
+            for sub in _kv_walks(row, rng, block_size):
+                per_tile.append((n_entries, sub.shape[0]))
+                entries.append(sub)
+                n_entries += sub.shape[0]
         for t in range(n_sub):
             n_rows = min(tile_m, row.n_tokens - t * tile_m)
+            off, cnt = per_tile[t]
             for h in row.heads:
-                tiles.append((row.q_row + t * tile_m, n_rows, int(h), kv_off, len(row.kv),
+                tiles.append((row.q_row + t * tile_m, n_rows, int(h), off, cnt,
                               mask_row + t * tile_m, row.out_dev, row.out_row + t * tile_m))
         mask_row += row.n_tokens
     # longest tiles first: the grid is scheduled in index order, so this is LPT packing
     tiles.sort(key=lambda x: -x[4])
+    width = 2 if tile_m == TILE_M else 4
     t_np = np.asarray(tiles, dtype=np.int32).reshape(-1, 8)
-    e_np = np.asarray(entries, dtype=np.int32).reshape(-1, 2)
+    e_np = np.concatenate(entries, axis=0) if entries else np.zeros((0, width), np.int32)
     m_np = np.concatenate(masks, axis=0) if masks else np.zeros((0, 4), np.int32)
     to = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(device, non_blocking=True)
-    return FwdTables(to(t_np), to(e_np), to(m_np), len(tiles), block_size, flops=4.0 * pairs * HEAD_DIM, tile_m=tile_m)
+    return FwdTables(to(t_np), to(e_np.astype(np.int32)), to(m_np), len(tiles), block_size, flops=4.0 * pairs * HEAD_DIM,
+                     tile_m=tile_m)
+
+
+def _kv_walks(row: AttnRow, rng: np.ndarray, block_size: int) -> List[np.ndarray]:
+    """Per 256-row CTA tile of a Q block: int32 [n, 4] list of the 128-key tiles it visits (see
+    build_fwd_tables).  Visibility comes from the union / intersection of the two key ranges over each
+    128-row query tile, the same test the one-tile kernels run on the device."""
+    n_qt, (u0s, u0e, u1s, u1e, i0s, i0e, i1s, i1e) = _tile_bounds(rng, TILE_M)
+    k_row, k_pos, k_nv = [], [], []
+    for e, (kv_row, n_tok) in enumerate(row.kv):
+        n_sub = (int(n_tok) + TILE_N - 1) // TILE_N
+        t = np.arange(n_sub)
+        k_row.append(int(kv_row) + t * TILE_N)
+        k_pos.append(e * block_size + t * TILE_N)
+        k_nv.append(np.minimum(TILE_N, int(n_tok) - t * TILE_N))
+    if not k_row:
+        return [np.zeros((0, 4), np.int32) for _ in range((n_qt + 1) // 2)]
+    k_row, k_pos, k_nv = np.concatenate(k_row), np.concatenate(k_pos), np.concatenate(k_nv)
+    lo, hi = k_pos[:, None], (k_pos + k_nv)[:, None]                                   # [n_k, 1]
+    need = ((lo < u0e[None]) & (hi > u0s[None])) | ((lo < u1e[None]) & (hi > u1s[None]))           # [n_k, n_qt]
+    full = (k_nv[:, None] == TILE_N) & (((i0s[None] <= lo) & (i0e[None] >= hi)) | ((i1s[None] <= lo) & (i1e[None] >= hi)))
+    out = []
+    for c in range((n_qt + 1) // 2):
+        a, b = 2 * c, 2 * c + 1
+        need_a, full_a = need[:, a], full[:, a]
+        need_b = need[:, b] if b < n_qt else np.zeros_like(need_a)
+        full_b = full[:, b] if b < n_qt else np.zeros_like(full_a)
+        sel = np.nonzero(need_a | need_b)[0]
+        flags = (need_a[sel].astype(np.int64) | (need_b[sel].astype(np.int64) << 1) |
+                 ((full_a[sel] & need_a[sel]).astype(np.int64) << 2) | ((full_b[sel] & need_b[sel]).astype(np.int64) << 3))
+        out.append(np.stack([k_row[sel], k_pos[sel], k_nv[sel], flags], axis=1).astype(np.int32))
+    return out
 
 
 def _ptr_array(tensors) -> ctypes.Array:

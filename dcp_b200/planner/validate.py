@@ -279,7 +279,10 @@ def validate_programs(programs) -> Dict[str, int]:
                     stats["tiles"] += 1
                     _check(0 <= head < p.heads_q, f"rank {r}: tile head {head}")
                     _check(q_readable(q_row, n_rows, s), f"rank {r} stage {s}: tile reads Q rows [{q_row},+{n_rows}) not present")
-                    for row, n_tok in entries[kv_off:kv_off + n_kv].tolist():
+                    _check(0 <= kv_off and kv_off + n_kv <= entries.shape[0], f"rank {r}: tile's KV list is out of range")
+                    for ent in entries[kv_off:kv_off + n_kv].tolist():
+                        # (row, tokens) per KV block for 128-row tiles, (row, position, keys, flags) per 128-key tile otherwise
+                        row, n_tok = (ent[0], ent[1]) if ft.tile_m == 128 else (ent[0], ent[2])
                         _check(kv_readable(row, n_tok, s), f"rank {r} stage {s}: tile reads KV rows [{row},+{n_tok}) not present")
                     _check(mask_row >= 0 and mask_row + n_rows <= ft.masks.shape[0], f"rank {r}: mask rows out of range")
                     if out_dev < world:

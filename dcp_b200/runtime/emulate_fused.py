@@ -75,26 +75,42 @@ def emulate(programs: List[FusedProgram], q_local: List[torch.Tensor], kv_local:
             for q_row, n_rows, head, kv_off, n_kv, mask_row, out_dev, out_row in tiles.tolist():
                 if n_rows <= 0:
                     continue
-                rng = masks[mask_row:mask_row + n_rows].to(torch.int64)
-                ks, vs, pos = [], [], []
-                for e in range(n_kv):
-                    row, n_tok = entries[kv_off + e].tolist()
-                    ks.append(A[r].kv[row:row + n_tok, 0, head // g])
-                    vs.append(A[r].kv[row:row + n_tok, 1, head // g])
-                    pos.append(torch.arange(e * bs, e * bs + n_tok))
-                k, v, pos = torch.cat(ks), torch.cat(vs), torch.cat(pos)
-                sc = (A[r].q[q_row:q_row + n_rows, head] @ k.T) * scale
-                sc = sc.masked_fill(~_allowed(rng, pos), NEG_INF)
-                lse = torch.logsumexp(sc, dim=-1)
-                prob = torch.exp(sc - torch.where(torch.isinf(lse), torch.zeros_like(lse), lse)[:, None])
-                prob = torch.where(torch.isinf(lse)[:, None], torch.zeros_like(prob), prob)
-                o = prob @ v
-                if out_dev < world:                           # a partial, in the owner's partial arena
-                    A[out_dev].part_out[out_row:out_row + n_rows, head] = o
-                    A[out_dev].part_lse[head, out_row:out_row + n_rows] = lse
-                else:                                         # the only contribution: owner's final buffer
-                    A[out_dev - world].out[out_row:out_row + n_rows, head] = o
-                    A[out_dev - world].lse[head, out_row:out_row + n_rows] = lse
+                # 128-row tiles carry (arena row, tokens) per KV block; 256-row tiles carry the ready-made
+                # walk (arena row, position, valid keys, flags) and each 128-row half only takes the
+                # entries whose flag bit says it can see them
+                halves = [(0, n_rows, None)] if t.tile_m == 128 else [(x * 128, min(128, n_rows - x * 128), x)
+                                                                       for x in range(2) if n_rows > x * 128]
+                for r0, nr, x in halves:
+                    rng = masks[mask_row + r0:mask_row + r0 + nr].to(torch.int64)
+                    ks, vs, pos = [], [], []
+                    for e in range(n_kv):
+                        ent = entries[kv_off + e].tolist()
+                        if x is None:
+                            row, n_tok, p0 = ent[0], ent[1], e * bs
+                        else:
+                            row, p0, n_tok, flags = ent
+                            if not (flags >> x) & 1:
+                                continue
+                        ks.append(A[r].kv[row:row + n_tok, 0, head // g])
+                        vs.append(A[r].kv[row:row + n_tok, 1, head // g])
+                        pos.append(torch.arange(p0, p0 + n_tok))
+                    if ks:
+                        k, v, pos = torch.cat(ks), torch.cat(vs), torch.cat(pos)
+                        sc = (A[r].q[q_row + r0:q_row + r0 + nr, head] @ k.T) * scale
+                        sc = sc.masked_fill(~_allowed(rng, pos), NEG_INF)
+                        lse = torch.logsumexp(sc, dim=-1)
+                        prob = torch.exp(sc - torch.where(torch.isinf(lse), torch.zeros_like(lse), lse)[:, None])
+                        prob = torch.where(torch.isinf(lse)[:, None], torch.zeros_like(prob), prob)
+                        o = prob @ v
+                    else:
+                        o = torch.zeros(nr, d, dtype=dtype)
+                        lse = torch.full((nr,), NEG_INF, dtype=dtype)
+                    if out_dev < world:                           # a partial, in the owner's partial arena
+                        A[out_dev].part_out[out_row + r0:out_row + r0 + nr, head] = o
+                        A[out_dev].part_lse[head, out_row + r0:out_row + r0 + nr] = lse
+                    else:                                         # the only contribution: owner's final buffer
+                        A[out_dev - world].out[out_row + r0:out_row + r0 + nr, head] = o
+                        A[out_dev - world].lse[head, out_row + r0:out_row + r0 + nr] = lse
     for r, p in enumerate(programs):                          # owner-side merge of the partials
         for dst_row, n, off, n_src in p.merge_ops.tolist():
             slots = p.merge_src[off:off + n_src].tolist()
