@@ -17,6 +17,8 @@
 // (local accumulator) or one 128-byte bulk reduce per query row (peer accumulator).  dK/dV stay
 // in TMEM for the CTA's lifetime and are added once with red.global.add.v4.f32.
 // TMEM columns: S^T [0,64) dP^T [64,128) dQ^T [128,192) [192,256) dK [256,384) dV [384,512).
+// Two more warps per CTA fetch the next plan stage's remote operands (Q, dO, KV rows and the lse /
+// delta statistics of the queries) from peer GPUs while the items are computed (copy_jobs.cuh).
 //
 // Reference behaviour covered: the varlen backward the executor calls at
 // dcp/runtime/flash_attention/executor.py:1058-1115, plus the blockwise partial sums
@@ -25,12 +27,13 @@
 #include <math.h>
 
 #include "attn_common.cuh"
+#include "copy_jobs.cuh"
 #include "ptx.cuh"
 #include "tmap.cuh"
 
 namespace dcpk {
 
-static constexpr int kBwdThreads = 320;  // 8 gradient warps + TMA producer + UMMA issuer
+static constexpr int kBwdThreads = 384;  // 8 gradient warps + TMA producer + UMMA issuer + 2 operand-fetch warps
 static constexpr int kQTile = 64;
 static constexpr int kStages = 3;  // depth of the Q / dO / statistics ring
 static constexpr int kKvHalf = 128 * 64 * 2;  // [128 x 64] bf16 half tile, 16 KB
@@ -122,7 +125,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                 const __grid_constant__ CUtensorMap tm_kv, const __grid_constant__ CUtensorMap tm_dq,
                 const BwdCta* __restrict__ ctas, const BwdItemDesc* __restrict__ items, const int4* __restrict__ masks,
                 const float* __restrict__ lse, const float* __restrict__ delta, BwdPtrs ptrs, int hq, int hkv,
-                int stat_stride, int n_dst, int q_rows, int kv_rows, float scale, int* __restrict__ status) {
+                int stat_stride, int n_dst, int q_rows, int kv_rows, int n_mask_rows, int n_items_total, float scale,
+                const CopyJob* __restrict__ jobs, int n_jobs, const __grid_constant__ CopyCtx copy_ctx,
+                int* __restrict__ status) {
   extern __shared__ uint8_t smem_raw[];
   BwdSmem& sm = *reinterpret_cast<BwdSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -134,10 +139,12 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   const int n_items = cta.n_items * group;  // visits
   {
     // table sanity before anything is allocated: a key tile whose gradient rows would fall outside
-    // the accumulator is reported and skipped (items are checked one by one by the producer warp)
+    // the accumulator, or whose item list runs past the item table, is reported and skipped (items
+    // are checked one by one by the producer warp, mask rows included)
     const bool bad = cta.dkv_dev < 0 || cta.dkv_dev >= n_dst || cta.dkv_row < 0 || cta.n_valid < 0 ||
                      cta.n_valid > 128 || cta.dkv_row + cta.n_valid > kv_rows || cta.kv_row < 0 ||
-                     cta.kv_row + cta.n_valid > kv_rows || cta.n_items < 0 || cta.item_off < 0;
+                     cta.kv_row + cta.n_valid > kv_rows || cta.n_items < 0 || cta.item_off < 0 ||
+                     cta.item_off + cta.n_items > n_items_total;
     if (bad) {
       if (threadIdx.x == 0) atomicExch(status, kStatusBadArgs);
       return;
@@ -188,7 +195,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     for (int i = 0; i < n_items && ok; ++i, st = (st + 1 == kStages ? 0 : st + 1), u += (st == 0)) {
       const BwdItem itx = load_item(my_items, i, group, kv_head);
       if (itx.n_rows < 0 || itx.n_rows > kQTile || itx.q_row < 0 || itx.q_row + itx.n_rows > q_rows ||
-          itx.q_row + itx.n_rows > stat_stride || itx.dq_dev >= n_dst ||
+          itx.q_row + itx.n_rows > stat_stride || itx.dq_dev >= n_dst || itx.mask_row < 0 ||
+          (!itx.full && itx.mask_row + itx.n_rows > n_mask_rows) ||
           (itx.dq_dev >= 0 && (itx.dq_row < 0 || itx.dq_row + itx.n_rows > q_rows))) {
         sm.abort_word = kStatusBadArgs;  // every waiter unwinds; the code is reported as the status
         ok = false;
@@ -307,6 +315,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     }
     if (ok && n_items > 0) ok = issue_acc(n_items - 1);
     if (ok && n_items > 0) mbar_wait(&sm.dq_full, (n_items - 1) & 1, abort_word);
+  } else if (warp >= 10) {
+    // ------------------------------------------------------------ operand fetch for the next stage
+    run_copy_jobs(jobs, n_jobs, copy_ctx, blockIdx.y * gridDim.x + blockIdx.x, gridDim.x * gridDim.y,
+                  threadIdx.x - 320, 64);
   } else {
     // ------------------------------------------------------------ softmax-gradient threads
     // 8 warps: warp w works on TMEM lanes 32*(w&3).. (key rows) and on query columns 32*(w>>2)..+31
@@ -526,6 +538,8 @@ static long long* g_bwd_timeline_host = nullptr;  // non-null selects the instru
 
 }  // namespace dcpk
 
+void dcpk_fill_copy_ctx(dcpk::CopyCtx* ctx, void* const* src_ptrs, void* const* dst_ptrs, int stat_stride);
+
 using namespace dcpk;
 
 extern "C" int dcpk_attn_delta(const void* o, const void* d_o, float* delta, int n_rows, int hq, int stat_stride,
@@ -547,13 +561,15 @@ extern "C" int dcpk_attn_bwd_set_timeline(void* buf) {
   return cudaMemcpyToSymbol(g_bwd_timeline, &p, sizeof(p)) == cudaSuccess ? 0 : -5;
 }
 
-// Launches the backward kernel: one CTA per (entry of `ctas`, KV head).
+// Launches the backward kernel: one CTA per (entry of `ctas`, KV head).  n_items_total / n_mask_rows are the
+// lengths of the item and mask tables; entries that point past them are reported (status 3), not read.
 extern "C" int dcpk_attn_bwd(const void* q_arena, const void* do_arena, long q_rows, const void* kv_arena,
                              long kv_rows, int hq, int hkv, const void* ctas, int n_ctas, const void* items,
-                             const void* masks, const float* lse, const float* delta, int stat_stride,
-                             float* const* dq_ptrs, float* const* dkv_ptrs, int n_dst, float scale, int* status,
-                             void* stream) {
-  if (n_ctas <= 0) return 0;
+                             int n_items_total, const void* masks, int n_mask_rows, const float* lse, const float* delta,
+                             int stat_stride, float* const* dq_ptrs, float* const* dkv_ptrs, int n_dst, float scale,
+                             const void* jobs, int n_jobs, void* const* job_src_ptrs, void* const* job_dst_ptrs,
+                             int job_stat_stride, int* status, void* stream) {
+  if (n_ctas <= 0) return n_jobs > 0 ? -6 : 0;   // copy jobs need a kernel to ride on
   if (n_dst > kMaxPeers || hq % hkv != 0) return -3;
   CUtensorMap tm_q, tm_do, tm_kv, tm_dq;
   if (encode_f32_tile_map(&tm_dq, dq_ptrs[0], uint64_t(q_rows), uint32_t(hq), kHeadDim, 16, 32)) return -1;
@@ -565,6 +581,8 @@ extern "C" int dcpk_attn_bwd(const void* q_arena, const void* do_arena, long q_r
     pp.dq[i] = i < n_dst ? dq_ptrs[i] : nullptr;
     pp.dkv[i] = i < n_dst ? dkv_ptrs[i] : nullptr;
   }
+  CopyCtx ctx;
+  dcpk_fill_copy_ctx(&ctx, n_jobs > 0 ? job_src_ptrs : nullptr, n_jobs > 0 ? job_dst_ptrs : nullptr, job_stat_stride);
   const int smem = int(sizeof(BwdSmem)) + 1024;
   const int v = g_bwd_timeline_host ? 1 : 0;
   auto kernel = v ? attn_bwd_kernel<true> : attn_bwd_kernel<false>;
@@ -574,7 +592,7 @@ extern "C" int dcpk_attn_bwd(const void* q_arena, const void* do_arena, long q_r
   }
   kernel<<<dim3(hkv, n_ctas), kBwdThreads, smem, static_cast<cudaStream_t>(stream)>>>(
       tm_q, tm_do, tm_kv, tm_dq, static_cast<const BwdCta*>(ctas), static_cast<const BwdItemDesc*>(items),
-      static_cast<const int4*>(masks), lse, delta, pp, hq, hkv, stat_stride, n_dst, int(q_rows), int(kv_rows), scale,
-      status);
+      static_cast<const int4*>(masks), lse, delta, pp, hq, hkv, stat_stride, n_dst, int(q_rows), int(kv_rows),
+      n_mask_rows, n_items_total, scale, static_cast<const CopyJob*>(jobs), n_jobs, ctx, status);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }

@@ -93,8 +93,8 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_kv,
                 const AttnTile* __restrict__ tiles, const KvEntry* __restrict__ kv_entries,
                 const int4* __restrict__ masks, PeerPtrs ptrs, int hq, int hkv, int lse_stride_a,
-                int lse_stride_b, int n_dst_a, int n_dst, int q_rows, int block_size, float scale,
-                int* __restrict__ status) {
+                int lse_stride_b, int n_dst_a, int n_dst, int q_rows, int block_size, int n_mask_rows,
+                int n_kv_entries, float scale, int* __restrict__ status) {
   extern __shared__ uint8_t smem_raw[];
   FwdSmem& sm = *reinterpret_cast<FwdSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -102,11 +102,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   const int kv_head = tile.head / (hq / hkv);
   {
     // table sanity before anything is allocated: a tile that would store outside its destination
-    // arena (or read a head / row that does not exist) is reported and skipped, never executed
+    // arena, or read a head / row / mask row / KV-list entry that does not exist, is reported and
+    // skipped, never executed
     const int dst_rows = tile.out_dev < n_dst_a ? lse_stride_a : lse_stride_b;
     const bool bad = tile.out_dev < 0 || tile.out_dev >= n_dst || tile.out_row < 0 || tile.n_rows < 0 ||
                      tile.n_rows > kTileM || tile.out_row + tile.n_rows > dst_rows || tile.head < 0 ||
-                     tile.head >= hq || tile.q_row < 0 || tile.q_row + tile.n_rows > q_rows || tile.n_kv < 0;
+                     tile.head >= hq || tile.q_row < 0 || tile.q_row + tile.n_rows > q_rows || tile.n_kv < 0 ||
+                     tile.mask_row < 0 || tile.mask_row + tile.n_rows > n_mask_rows || tile.kv_off < 0 ||
+                     tile.kv_off + tile.n_kv > n_kv_entries;
     if (bad) {
       if (threadIdx.x == 0) atomicExch(status, kStatusBadArgs);
       return;
@@ -442,8 +445,8 @@ extern "C" int dcpk_attn_fwd_set_timeline(void* buf) {
 // Launches the forward kernel over `n_tiles` tiles.  `variant` 0 keeps P in TMEM (TS
 // UMMA), 1 stages P through shared memory (SS UMMA).  Returns 0 or a negative error.
 extern "C" int dcpk_attn_fwd(const void* q_arena, long q_rows, const void* kv_arena, long kv_rows, int hq,
-                             int hkv, const void* tiles, int n_tiles, const void* kv_entries,
-                             const void* masks, void* const* out_ptrs, float* const* lse_ptrs, int n_dst,
+                             int hkv, const void* tiles, int n_tiles, const void* kv_entries, int n_kv_entries,
+                             const void* masks, int n_mask_rows, void* const* out_ptrs, float* const* lse_ptrs, int n_dst,
                              int lse_stride_a, int lse_stride_b, int n_dst_a, int block_size, float scale,
                              int* status, int variant, void* stream) {
   if (n_tiles <= 0) return 0;
@@ -459,7 +462,7 @@ extern "C" int dcpk_attn_fwd(const void* q_arena, long q_rows, const void* kv_ar
   const int smem = int(sizeof(FwdSmem)) + 1024;
   const int v = (variant ? 1 : 0) + (g_fwd_timeline_host ? 2 : 0);
   using KernelFn = void (*)(const CUtensorMap, const CUtensorMap, const AttnTile*, const KvEntry*, const int4*, PeerPtrs,
-                            int, int, int, int, int, int, int, int, float, int*);
+                            int, int, int, int, int, int, int, int, int, int, float, int*);
   static const KernelFn kernels[4] = {attn_fwd_kernel<false, false>, attn_fwd_kernel<true, false>,
                                       attn_fwd_kernel<false, true>, attn_fwd_kernel<true, true>};
   if (!g_fwd_attr_set[v]) {
@@ -469,6 +472,6 @@ extern "C" int dcpk_attn_fwd(const void* q_arena, long q_rows, const void* kv_ar
   kernels[v]<<<n_tiles, kFwdThreads, smem, static_cast<cudaStream_t>(stream)>>>(
       tm_q, tm_kv, static_cast<const AttnTile*>(tiles), static_cast<const KvEntry*>(kv_entries),
       static_cast<const int4*>(masks), pp, hq, hkv, lse_stride_a, lse_stride_b, n_dst_a, n_dst, int(q_rows), block_size,
-      scale, status);
+      n_mask_rows, n_kv_entries, scale, status);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }

@@ -3,7 +3,10 @@
 // One CTA = up to 256 queries (two 128-row tiles A and B of one Q block) of one head.  Warps:
 //   0-3  softmax of tile A, 4-7 softmax of tile B (one thread per query row),
 //   8    TMA producer (Q of both tiles once, 2-deep rings of K and V tiles),
-//   9    UMMA issuer, 10-11 only donate registers (setmaxnreg).
+//   9    UMMA issuer,
+//   10-11 fetch the next plan stage's remote operands (copy jobs: peer loads over NVLink into this
+//        GPU's staging rows, see copy_jobs.cuh) while the tiles are computed; they also donate
+//        registers (setmaxnreg).
 // K and V tiles are loaded once and used by both query tiles, and the two softmax warpgroups
 // alternate on the tensor core: per KV tile j the issuer emits
 //   PV(A, j-1), QK(A, j), PV(B, j-1), QK(B, j)
@@ -23,6 +26,7 @@
 #include <math.h>
 
 #include "attn_common.cuh"
+#include "copy_jobs.cuh"
 #include "ptx.cuh"
 #include "tmap.cuh"
 
@@ -71,7 +75,8 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                      const AttnTile* __restrict__ tiles, const int4* __restrict__ kv_subs,
                      const int4* __restrict__ masks, PeerPtrs ptrs, int hq, int hkv, int lse_stride_a,
                      int lse_stride_b, int n_dst_a, int n_dst, int q_rows, int block_size, int n_mask_rows,
-                     int n_kv_subs, float scale, int* __restrict__ status) {
+                     int n_kv_subs, float scale, const CopyJob* __restrict__ jobs, int n_jobs,
+                     const __grid_constant__ CopyCtx copy_ctx, int* __restrict__ status) {
   extern __shared__ uint8_t smem_raw[];
   PairSmem& sm = *reinterpret_cast<PairSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -238,7 +243,10 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
 #pragma unroll
     for (int x = 0; x < 2; ++x)
       if (ok && cnt[x] > 0) ok = mbar_wait(&sm.o_done[x], (cnt[x] - 1) & 1, abort_word);
-   }  // warps 10-11 only donate registers
+   } else {
+    // ------------------------------------------------------------ operand fetch for the next stage
+    run_copy_jobs(jobs, n_jobs, copy_ctx, blockIdx.x, gridDim.x, threadIdx.x - 320, 64);
+   }
   } else {
     // ------------------------------------------------------------ softmax + epilogue of tile X
     asm volatile("setmaxnreg.inc.sync.aligned.u32 208;");
@@ -388,6 +396,8 @@ static int g_pair_attr_set = 0;
 
 }  // namespace dcpk
 
+void dcpk_fill_copy_ctx(dcpk::CopyCtx* ctx, void* const* src_ptrs, void* const* dst_ptrs, int stat_stride);
+
 using namespace dcpk;
 
 // Same contract as dcpk_attn_fwd, for tile tables built with 256-row tiles (AttnTile.n_rows <= 256):
@@ -397,8 +407,9 @@ extern "C" int dcpk_attn_fwd_pair(const void* q_arena, long q_rows, const void* 
                                   int hkv, const void* tiles, int n_tiles, const void* kv_entries, int n_kv_entries,
                                   const void* masks, int n_mask_rows, void* const* out_ptrs, float* const* lse_ptrs,
                                   int n_dst, int lse_stride_a, int lse_stride_b, int n_dst_a, int block_size,
-                                  float scale, int* status, void* stream) {
-  if (n_tiles <= 0) return 0;
+                                  float scale, const void* jobs, int n_jobs, void* const* job_src_ptrs,
+                                  void* const* job_dst_ptrs, int job_stat_stride, int* status, void* stream) {
+  if (n_tiles <= 0) return n_jobs > 0 ? -6 : 0;   // copy jobs need a kernel to ride on
   if (n_dst > kMaxPeers || hq % hkv != 0) return -3;
   CUtensorMap tm_q, tm_kv;
   if (encode_arena_map(&tm_q, q_arena, uint64_t(q_rows), uint32_t(hq), kHeadDim, 128)) return -1;
@@ -408,6 +419,8 @@ extern "C" int dcpk_attn_fwd_pair(const void* q_arena, long q_rows, const void* 
     pp.out[i] = i < n_dst ? out_ptrs[i] : nullptr;
     pp.lse[i] = i < n_dst ? lse_ptrs[i] : nullptr;
   }
+  CopyCtx ctx;
+  dcpk_fill_copy_ctx(&ctx, n_jobs > 0 ? job_src_ptrs : nullptr, n_jobs > 0 ? job_dst_ptrs : nullptr, job_stat_stride);
   const int smem = int(sizeof(PairSmem)) + 1024;
   if (!g_pair_attr_set) {
     if (cudaFuncSetAttribute(attn_fwd_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
@@ -417,6 +430,6 @@ extern "C" int dcpk_attn_fwd_pair(const void* q_arena, long q_rows, const void* 
   attn_fwd_pair_kernel<<<n_tiles, kPairThreads, smem, static_cast<cudaStream_t>(stream)>>>(
       tm_q, tm_kv, static_cast<const AttnTile*>(tiles), static_cast<const int4*>(kv_entries),
       static_cast<const int4*>(masks), pp, hq, hkv, lse_stride_a, lse_stride_b, n_dst_a, n_dst, int(q_rows),
-      block_size, n_mask_rows, n_kv_entries, scale, status);
+      block_size, n_mask_rows, n_kv_entries, scale, static_cast<const CopyJob*>(jobs), n_jobs, ctx, status);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }

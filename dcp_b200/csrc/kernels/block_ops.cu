@@ -1,6 +1,8 @@
 // Data-movement and reduction kernels around the attention kernels.  All of them can read
 // or write peer GPU memory through NVLink mappings (plain ld/st/red, never TMA multicast):
 //
+//  copy_jobs        stand-alone launch of a stage's copy-job list (see copy_jobs.cuh; normally the
+//                   attention kernel of the previous stage carries the list).
 //  gather_rows      pull token rows of Q/KV/dO (and per-head fp32 statistics) from peers'
 //                   arenas into this GPU's staging rows; replaces pack -> all_to_all -> unpack
 //                   (dcp/ops/fused_ops.py:290-335 + executor.py:1915-2074 in the reference).
@@ -12,6 +14,7 @@
 //  signal_barrier   all-to-all flag barrier with a deadline: a peer that never arrives makes
 //                   the kernel record an error code and return instead of spinning forever.
 #include "attn_common.cuh"
+#include "copy_jobs.cuh"
 #include "ptx.cuh"
 
 namespace dcpk {
@@ -55,6 +58,10 @@ __global__ void gather_stats_kernel(const RowCopy* __restrict__ entries, PtrTabl
     const int h = i / e.n_rows, r = i % e.n_rows;
     dst[size_t(h) * dst_stride + e.dst_row + r] = src[size_t(h) * src_stride + e.src_row + r];
   }
+}
+
+__global__ void copy_jobs_kernel(const CopyJob* __restrict__ jobs, int n_jobs, CopyCtx ctx) {
+  run_copy_jobs(jobs, n_jobs, ctx, blockIdx.x, gridDim.x, threadIdx.x, blockDim.x);
 }
 
 struct MergeOp {
@@ -163,6 +170,25 @@ static PtrTable make_ptrs(void* const* ptrs, int n) {
   PtrTable t;
   for (int i = 0; i < kMaxPeers; ++i) t.p[i] = i < n ? ptrs[i] : nullptr;
   return t;
+}
+
+// src_ptrs: kCopyKinds x kMaxPeers region bases (row-major, unused entries null), dst_ptrs: kCopyKinds bases
+void dcpk_fill_copy_ctx(CopyCtx* ctx, void* const* src_ptrs, void* const* dst_ptrs, int stat_stride) {
+  ctx->stat_stride = stat_stride;
+  for (int k = 0; k < kCopyKinds; ++k) {
+    for (int r = 0; r < kMaxPeers; ++r) ctx->src[k][r] = static_cast<const uint8_t*>(src_ptrs ? src_ptrs[k * kMaxPeers + r] : nullptr);
+    ctx->dst[k] = static_cast<uint8_t*>(dst_ptrs ? dst_ptrs[k] : nullptr);
+  }
+}
+
+extern "C" int dcpk_copy_jobs(const void* jobs, int n_jobs, void* const* src_ptrs, void* const* dst_ptrs, int stat_stride,
+                              void* stream) {
+  if (n_jobs <= 0) return 0;
+  CopyCtx ctx;
+  dcpk_fill_copy_ctx(&ctx, src_ptrs, dst_ptrs, stat_stride);
+  const int grid = n_jobs < 592 ? n_jobs : 592;
+  copy_jobs_kernel<<<grid, 128, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const CopyJob*>(jobs), n_jobs, ctx);
+  return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
 
 extern "C" int dcpk_gather_rows(const void* entries, int n_entries, void* const* src_ptrs, int n_src, void* dst,

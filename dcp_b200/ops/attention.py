@@ -160,11 +160,47 @@ def _ptr_array(tensors) -> ctypes.Array:
     return arr
 
 
+class CopyContext:
+    """Region bases of the copy jobs an attention kernel may carry (csrc/kernels/copy_jobs.cuh): for
+    every region kind (q, kv, dout, lse, delta) the device address of the region on every rank of the
+    group, and the local base.  ``stat_stride`` = rows per head of the statistics regions."""
+    KINDS = ("q", "kv", "dout", "lse", "delta")
+    MAX_PEERS = 16
+
+    def __init__(self, peer_ptrs_of, rank: int, stat_stride: int):
+        self.src = (ctypes.c_void_p * (len(self.KINDS) * self.MAX_PEERS))()
+        self.dst = (ctypes.c_void_p * len(self.KINDS))()
+        for k, name in enumerate(self.KINDS):
+            ptrs = peer_ptrs_of(name)
+            for r, ptr in enumerate(ptrs):
+                self.src[k * self.MAX_PEERS + r] = ptr
+            self.dst[k] = ptrs[rank]
+        self.stat_stride = int(stat_stride)
+
+
+def _job_args(jobs, ctx):
+    """ctypes arguments (jobs, n_jobs, src bases, dst bases, stat stride) of a kernel's copy-job list."""
+    if jobs is None or ctx is None or jobs.shape[0] == 0:
+        return ctypes.c_void_p(0), ctypes.c_int(0), ctypes.c_void_p(0), ctypes.c_void_p(0), ctypes.c_int(0)
+    return _lib.ptr(jobs), ctypes.c_int(jobs.shape[0]), ctx.src, ctx.dst, ctypes.c_int(ctx.stat_stride)
+
+
+def copy_jobs(jobs: torch.Tensor, ctx: CopyContext) -> None:
+    """Stand-alone launch of a copy-job list (int32 [n, 4]); used when no attention kernel can carry it."""
+    if jobs is None or jobs.shape[0] == 0:
+        return
+    lib = _lib.load()
+    _lib.check(lib.dcpk_copy_jobs(*_job_args(jobs, ctx), _lib.stream_handle()), "dcpk_copy_jobs")
+
+
 def attn_fwd(q_arena: torch.Tensor, kv_arena: torch.Tensor, tables: FwdTables, out_dsts, lse_dsts,
              scale: float, status: torch.Tensor, variant: int = 0, lse_stride: Optional[int] = None,
-             lse_stride_b: Optional[int] = None, n_dst_a: Optional[int] = None):
+             lse_stride_b: Optional[int] = None, n_dst_a: Optional[int] = None, jobs: Optional[torch.Tensor] = None,
+             job_ctx: Optional[CopyContext] = None):
     """Run the forward kernel the tables were built for (``tables.tile_m``); ``variant`` only applies to
-    the one-tile kernel (0: P in TMEM, 1: P through shared memory).
+    the one-tile kernel (0: P in TMEM, 1: P through shared memory).  ``jobs`` (int32 [n, 4] on the
+    device, see copy_jobs.cuh) is a list of peer -> local copies the two-tile kernel performs with
+    two spare warps per CTA while it computes; ``job_ctx`` names the regions they refer to.
 
     q_arena: bf16 [rows, hq, 128]; kv_arena: bf16 [rows, 2, hkv, 128]; out_dsts / lse_dsts: lists of
     destination arenas (tensors or raw device addresses; index 0 = this rank), every out arena
@@ -186,13 +222,15 @@ def attn_fwd(q_arena: torch.Tensor, kv_arena: torch.Tensor, tables: FwdTables, o
             ctypes.c_int(len(out_dsts)), ctypes.c_int(lse_stride),
             ctypes.c_int(lse_stride if lse_stride_b is None else lse_stride_b),
             ctypes.c_int(len(out_dsts) if n_dst_a is None else n_dst_a), ctypes.c_int(tables.block_size),
-            ctypes.c_float(scale), _lib.ptr(status), _lib.stream_handle())
+            ctypes.c_float(scale), *_job_args(jobs, job_ctx), _lib.ptr(status), _lib.stream_handle())
         _lib.check(rc, "dcpk_attn_fwd_pair")
         return
+    assert jobs is None or jobs.shape[0] == 0, "only the two-tile forward kernel carries copy jobs"
     rc = lib.dcpk_attn_fwd(
         _lib.ptr(q_arena), ctypes.c_long(q_arena.shape[0]), _lib.ptr(kv_arena), ctypes.c_long(kv_arena.shape[0]),
         ctypes.c_int(hq), ctypes.c_int(hkv), _lib.ptr(tables.tiles), ctypes.c_int(tables.n_tiles),
-        _lib.ptr(tables.kv_entries), _lib.ptr(tables.masks), _ptr_array(out_dsts), _ptr_array(lse_dsts),
+        _lib.ptr(tables.kv_entries), ctypes.c_int(tables.kv_entries.shape[0]), _lib.ptr(tables.masks),
+        ctypes.c_int(tables.masks.shape[0]), _ptr_array(out_dsts), _ptr_array(lse_dsts),
         ctypes.c_int(len(out_dsts)), ctypes.c_int(lse_stride),
         ctypes.c_int(lse_stride if lse_stride_b is None else lse_stride_b),
         ctypes.c_int(len(out_dsts) if n_dst_a is None else n_dst_a), ctypes.c_int(tables.block_size),
@@ -322,18 +360,20 @@ def attn_delta(out_arena: torch.Tensor, dout_arena: torch.Tensor, delta: torch.T
 
 
 def attn_bwd(q_arena, do_arena, kv_arena, lse, delta, tables: BwdTables, dq_dsts, dkv_dsts, scale: float,
-             status: torch.Tensor):
+             status: torch.Tensor, jobs: Optional[torch.Tensor] = None, job_ctx: Optional[CopyContext] = None):
     """Run the backward kernel; dq_dsts/dkv_dsts are fp32 accumulators (zeroed by the caller),
-    [rows, hq, 128] and [rows, 2, hkv, 128]; lse/delta are fp32 [hq, rows]."""
+    [rows, hq, 128] and [rows, 2, hkv, 128]; lse/delta are fp32 [hq, rows].  ``jobs`` / ``job_ctx``: copy
+    jobs two spare warps per CTA perform meanwhile (the next stage's operands, see attn_fwd)."""
     lib = _lib.load()
     hq, hkv = q_arena.shape[1], kv_arena.shape[2]
     assert q_arena.shape == do_arena.shape and lse.shape == delta.shape
     rc = lib.dcpk_attn_bwd(
         _lib.ptr(q_arena), _lib.ptr(do_arena), ctypes.c_long(q_arena.shape[0]), _lib.ptr(kv_arena),
         ctypes.c_long(kv_arena.shape[0]), ctypes.c_int(hq), ctypes.c_int(hkv), _lib.ptr(tables.ctas),
-        ctypes.c_int(tables.n_ctas), _lib.ptr(tables.items), _lib.ptr(tables.masks), _lib.ptr(lse), _lib.ptr(delta),
+        ctypes.c_int(tables.n_ctas), _lib.ptr(tables.items), ctypes.c_int(tables.items.shape[0]), _lib.ptr(tables.masks),
+        ctypes.c_int(tables.masks.shape[0]), _lib.ptr(lse), _lib.ptr(delta),
         ctypes.c_int(lse.shape[1]), _ptr_array(dq_dsts), _ptr_array(dkv_dsts), ctypes.c_int(len(dq_dsts)),
-        ctypes.c_float(scale), _lib.ptr(status), _lib.stream_handle())
+        ctypes.c_float(scale), *_job_args(jobs, job_ctx), _lib.ptr(status), _lib.stream_handle())
     _lib.check(rc, "dcpk_attn_bwd")
 
 

@@ -48,6 +48,10 @@ class FusedProgram:
     merge_src: np.ndarray = None        # int32
     dq_push: np.ndarray = None          # int32 [n,4] (owner, src_row, dst_row, n)
     dkv_push: np.ndarray = None
+    # the pulls as copy jobs (csrc/kernels/copy_jobs.cuh), per stage: Q + KV rows, and what the backward
+    # needs on top (dO rows, lse / delta statistics of the pulled query rows)
+    jobs_qkv: List[np.ndarray] = field(default_factory=list)    # int32 [n,4] (src_off, dst_off, n, where)
+    jobs_grad: List[np.ndarray] = field(default_factory=list)
     fwd_flops: float = 0.0
     bwd_flops: float = 0.0
     pull_bytes: float = 0.0
@@ -59,6 +63,30 @@ class FusedProgram:
 
 def _i4(rows) -> np.ndarray:
     return np.asarray(rows, dtype=np.int32).reshape(-1, 4)
+
+
+JOB_CHUNK_UNITS = 4096     # 64 KB of 16-byte units per copy job: the unit of work one CTA's fetch warps take
+KIND_Q, KIND_KV, KIND_DOUT, KIND_LSE, KIND_DELTA = range(5)
+
+
+def row_copy_jobs(pulls: np.ndarray, kind: int, row_units: int) -> np.ndarray:
+    """Row pulls (peer, src_row, dst_row, n_rows) of a [rows, ...] region with ``row_units`` 16-byte
+    units per row -> copy jobs of at most JOB_CHUNK_UNITS units."""
+    out = []
+    for peer, src_row, dst_row, n in np.asarray(pulls).reshape(-1, 4).tolist():
+        total, s0, d0 = n * row_units, src_row * row_units, dst_row * row_units
+        for off in range(0, total, JOB_CHUNK_UNITS):
+            out.append((s0 + off, d0 + off, min(JOB_CHUNK_UNITS, total - off), peer | (kind << 8)))
+    return _i4(out)
+
+
+def stat_copy_jobs(pulls: np.ndarray, kind: int, heads: int) -> np.ndarray:
+    """Pulls of query rows -> per-head copy jobs of a [heads, rows] fp32 statistics region."""
+    out = []
+    for peer, src_row, dst_row, n in np.asarray(pulls).reshape(-1, 4).tolist():
+        for h in range(heads):
+            out.append((src_row, dst_row, n, peer | (kind << 8) | (1 << 16) | (h << 24)))
+    return _i4(out)
 
 
 def lower_all(context: ExecutionContext, workload: WorkloadSpec, build_backward: bool = True,
@@ -148,6 +176,10 @@ def lower_all(context: ExecutionContext, workload: WorkloadSpec, build_backward:
         for s in range(n_stages):
             prog.q_pulls.append(_i4(q_pulls[d][s]))
             prog.kv_pulls.append(_i4(kv_pulls[d][s]))
+            qp, kp = prog.q_pulls[-1], prog.kv_pulls[-1]
+            prog.jobs_qkv.append(np.concatenate([row_copy_jobs(qp, KIND_Q, hq * 16), row_copy_jobs(kp, KIND_KV, hkv * 32)]))
+            prog.jobs_grad.append(np.concatenate([row_copy_jobs(qp, KIND_DOUT, hq * 16), stat_copy_jobs(qp, KIND_LSE, hq),
+                                                  stat_copy_jobs(qp, KIND_DELTA, hq)]) if build_backward else _i4([]))
             attn_rows: List[AttnRow] = []
             for q_id in sorted(rows_ps[d][s]):
                 units = sorted((work_meta[w] for w in rows_ps[d][s][q_id]), key=lambda u: in_meta[u.kv_id].block_id)

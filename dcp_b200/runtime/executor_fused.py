@@ -2,13 +2,16 @@
 
 Per attention call (all layers of an iteration share one executor and one program):
 
-forward   barrier -> [side stream] pull stage s+1 operands from peers' arenas
-                  -> [main stream] tcgen05 attention of stage s; every tile stores its partial
-                     (out, lse) into the owner's partial arena / final buffer over NVLink
+forward   barrier -> tcgen05 attention of stage s, whose spare warps fetch the remote operands of
+                     stage s+1 from peers' arenas while its tiles are computed (stage 0 works on
+                     local operands only); every tile stores its partial (out, lse) into the
+                     owner's partial arena / final buffer over NVLink
           barrier -> merge kernel on the owner
-backward  delta = rowsum(dO * O); barrier -> pulls (Q, dO, lse, delta, KV) overlapped with the
-          backward kernel per stage, dQ/dK/dV accumulated with fp32 red into arena mirrors
-          -> push-add of staged gradients into the owners' accumulators -> barrier
+backward  delta = rowsum(dO * O); barrier -> backward kernel per stage, fetching the next stage's
+          Q, dO, lse, delta, KV the same way, dQ/dK/dV accumulated with fp32 red into arena
+          mirrors -> push-add of staged gradients into the owners' accumulators -> barrier
+One stream, no events: a stage's operands are in place when its kernel starts because the
+previous stage's kernel brought them.
 
 No NCCL call is made on these paths.  Takes the role of AttentionExecutor
 (dcp/runtime/flash_attention/executor.py:340-2133) for single-node NVSwitch machines.
@@ -42,7 +45,6 @@ class FusedAttentionExecutor:
         self.arena = None
         self.n_reallocations = 0
         self._allocate((max_q_rows, max_kv_rows, max_part_rows))
-        self.side = torch.cuda.Stream(device=device)
         self.program: Optional[FusedProgram] = None
         self.arena_epoch = 0          # bumped whenever q/kv local regions are rewritten
         self._staging_valid = False   # remote Q/KV rows in staging match the current local data on peers
@@ -85,6 +87,7 @@ class FusedAttentionExecutor:
         self.world, self.rank = self.arena.world, self.arena.rank
         for name in regions:
             setattr(self, name, self.arena.view(name))
+        self.copy_ctx = attn_ops.CopyContext(self.arena.peer_ptrs, self.rank, rq)
 
     # ---- program upload
     def prepare(self, program: FusedProgram) -> None:
@@ -96,8 +99,11 @@ class FusedAttentionExecutor:
         dev = self.device
         up = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(dev, non_blocking=True)
         self.program = program
-        self.q_pulls = [up(x) for x in program.q_pulls]
-        self.kv_pulls = [up(x) for x in program.kv_pulls]
+        # copy jobs per stage: Q + KV rows (forward, and backward when the staging rows were
+        # overwritten since), dO + statistics (backward)
+        self.jobs_qkv = [up(x) for x in program.jobs_qkv]
+        self.jobs_grad = [up(x) for x in program.jobs_grad]
+        self.jobs_all = [up(np.concatenate([a, b])) for a, b in zip(program.jobs_qkv, program.jobs_grad)]
         self.fwd_tabs = [t.to(dev) if t is not None else None for t in program.fwd]
         self.bwd_tabs = [t.to(dev) if t is not None else None for t in program.bwd]
         self.merge_ops, self.merge_src = up(program.merge_ops), up(program.merge_src)
@@ -121,17 +127,18 @@ class FusedAttentionExecutor:
         self.arena_epoch += 1
         self._staging_valid = False
 
-    def _pull_inputs(self, s: int, with_grads: bool, skip_qkv: bool = False) -> None:
-        a = self.arena
-        if not skip_qkv:
-            block_ops.gather_rows(self.q_pulls[s], a.peer_ptrs("q"), self.q, self.hq * HEAD_DIM * 2)
-            block_ops.gather_rows(self.kv_pulls[s], a.peer_ptrs("kv"), self.kv, 2 * self.hkv * HEAD_DIM * 2)
-            self.kernel_launches += 2 * (self.q_pulls[s].shape[0] > 0)
-        if with_grads:
-            block_ops.gather_rows(self.q_pulls[s], a.peer_ptrs("dout"), self.dout, self.hq * HEAD_DIM * 2)
-            block_ops.gather_stats(self.q_pulls[s], a.peer_ptrs("lse"), self.lse, self.hq, self.cap[0])
-            block_ops.gather_stats(self.q_pulls[s], a.peer_ptrs("delta"), self.delta, self.hq, self.cap[0])
-            self.kernel_launches += 3 * (self.q_pulls[s].shape[0] > 0)
+    def _jobs_of(self, lists, s: int):
+        """Copy jobs of stage ``s`` (None when there are none or the group has a single rank)."""
+        if self.world <= 1 or s >= len(lists) or lists[s].shape[0] == 0:
+            return None
+        return lists[s]
+
+    def _fetch_standalone(self, jobs) -> None:
+        """Operands that no attention kernel can bring along (stage 0 of a single-stage plan, or a
+        stage that follows one without work on this rank) are fetched by a launch of their own."""
+        if jobs is not None:
+            attn_ops.copy_jobs(jobs, self.copy_ctx)
+            self.kernel_launches += 1
 
     # ---- optional phase timing (DCP_B200_PROFILE=1): CUDA events on the main stream around the
     # barriers and the kernels of every call; read with profile_summary() after a synchronize
@@ -207,25 +214,18 @@ class FusedAttentionExecutor:
             self._poison_staging(False)
         a.barrier()                                   # every rank's inputs are in place
         self._mark("fwd:wait inputs of peers")
-        ready = []
-        if self.world > 1:
-            self.side.wait_stream(main)
-            with torch.cuda.stream(self.side):
-                for s in range(p.n_stages):
-                    self._pull_inputs(s, with_grads=False)
-                    ev = torch.cuda.Event()
-                    ev.record(self.side)
-                    ready.append(ev)
         out_dsts = a.peer_ptrs("part_out") + a.peer_ptrs("out")
         lse_dsts = a.peer_ptrs("part_lse") + a.peer_ptrs("lse")
+        self._fetch_standalone(self._jobs_of(self.jobs_qkv, 0))
         for s in range(p.n_stages):
-            if ready:
-                main.wait_event(ready[s])
+            nxt = self._jobs_of(self.jobs_qkv, s + 1)
             t = self.fwd_tabs[s]
-            if t is None:
-                continue
-            self._launch_fwd(t, out_dsts, lse_dsts)
-        self._mark("fwd:pulls + kernels")
+            if t is None or t.tile_m != attn_ops.TILE_M_PAIR:
+                self._fetch_standalone(nxt)
+                nxt = None
+            if t is not None:
+                self._launch_fwd(t, out_dsts, lse_dsts, nxt)
+        self._mark("fwd:kernels (with operand fetch)")
         if self.world > 1:
             a.barrier()                               # all partials have landed at their owners
         self._mark("fwd:wait partials of peers")
@@ -238,10 +238,12 @@ class FusedAttentionExecutor:
         self._staging_valid = True
         return self.out_local(), self.lse_local()
 
-    def _launch_fwd(self, t, out_dsts, lse_dsts) -> None:
-        # destinations 0..world-1 are partial arenas (row stride cap[2]), the rest final buffers (cap[0])
+    def _launch_fwd(self, t, out_dsts, lse_dsts, jobs=None) -> None:
+        # destinations 0..world-1 are partial arenas (row stride cap[2]), the rest final buffers (cap[0]);
+        # `jobs`: the next stage's operand fetch, carried by this kernel
         attn_ops.attn_fwd(self.q, self.kv, t, out_dsts, lse_dsts, self.scale, a_status(self), self.variant,
-                          lse_stride=self.cap[2], lse_stride_b=self.cap[0], n_dst_a=self.world)
+                          lse_stride=self.cap[2], lse_stride_b=self.cap[0], n_dst_a=self.world, jobs=jobs,
+                          job_ctx=self.copy_ctx)
         self.kernel_launches += 1
 
     # ---- backward
@@ -263,25 +265,18 @@ class FusedAttentionExecutor:
         self._mark("bwd:dout copy, delta, zero accumulators")
         a.barrier()
         self._mark("bwd:wait inputs of peers")
-        ready = []
-        if self.world > 1:
-            self.side.wait_stream(main)
-            with torch.cuda.stream(self.side):
-                for s in range(p.n_stages):
-                    self._pull_inputs(s, with_grads=True, skip_qkv=self._staging_valid)
-                    ev = torch.cuda.Event()
-                    ev.record(self.side)
-                    ready.append(ev)
+        lists = self.jobs_grad if self._staging_valid else self.jobs_all
+        self._fetch_standalone(self._jobs_of(lists, 0))
         for s in range(p.n_stages):
-            if ready:
-                main.wait_event(ready[s])
+            nxt = self._jobs_of(lists, s + 1)
             t = self.bwd_tabs[s]
             if t is None:
+                self._fetch_standalone(nxt)
                 continue
             attn_ops.attn_bwd(self.q, self.dout, self.kv, self.lse, self.delta, t, [self.dq], [self.dkv], self.scale,
-                              a_status(self))
+                              a_status(self), jobs=nxt, job_ctx=self.copy_ctx)
             self.kernel_launches += 1
-        self._mark("bwd:pulls + kernels")
+        self._mark("bwd:kernels (with operand fetch)")
         if self.world > 1:
             block_ops.push_add_rows(self.dq_push, self.dq, a.peer_ptrs("dq"), self.hq * HEAD_DIM)
             block_ops.push_add_rows(self.dkv_push, self.dkv, a.peer_ptrs("dkv"), 2 * self.hkv * HEAD_DIM)

@@ -59,7 +59,7 @@ def run_case(rank, world, group, raw, bs, H, Hkv, mask_name, hbs, n_stages=None,
         ex.check_status()
     trace = ex.profile_chrome_trace()
     names = {e["name"] for e in trace}
-    assert {"fwd:pulls + kernels", "bwd:pulls + kernels"} <= names and all(e["dur"] >= 0 for e in trace), names
+    assert {"fwd:kernels (with operand fetch)", "bwd:kernels (with operand fetch)"} <= names and all(e["dur"] >= 0 for e in trace), names
     assert ex.profile_summary() == {}      # consumed
     out_g, lse_g = torch.zeros(T, H, d), torch.zeros(H, T)
     dq_g, dkv_g = torch.zeros(T, H, d), torch.zeros(T, 2, Hkv, d)
@@ -96,7 +96,13 @@ def main():
     cases = [([1000, 300, 2100, 640], 256, 8, 2, "causal", 8, None),
              ([1000, 300, 2100, 640], 256, 8, 2, "lambda", 4, 2),
              ([3000, 700], 512, 4, 4, "shared_question", 4, 3),
-             ([2048, 1024, 512], 512, 8, 2, "causal_blockwise", 8, None)]
+             ([2048, 1024, 512], 512, 8, 2, "causal_blockwise", 8, None),
+             # one stage only: every remote operand is fetched by a launch of its own before the kernels
+             ([1500, 900, 2600], 256, 8, 2, "causal", 8, 1)]
+    if world >= 4:
+        # a longer mixed batch so that every rank of a larger group holds work of several stages
+        cases.append(([5000, 1200, 9000, 700, 3100, 2048, 6100, 4700], 512, 8, 2, "causal", 4, None))
+        cases.append(([16384, 2000, 8192, 6000], 1024, 8, 4, "lambda", 8, 3))
     for c in cases:
         run_case(rank, world, group, *c)
     if rank == 0:

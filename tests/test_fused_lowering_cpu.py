@@ -157,3 +157,42 @@ def test_random_configurations(seed):
         ro, _rl, rdq, rdkv = dense_reference(q, kv, raw, pad, m, d ** -0.5, dout)
         err = max((out_g - ro).abs().max().item(), (dq_g - rdq).abs().max().item(), (dkv_g - rdkv).abs().max().item())
         assert err < 1e-8, (desc, err)
+
+
+def test_copy_jobs_move_exactly_the_pulled_rows():
+    """The copy-job form of the pulls (what the attention kernels' fetch warps execute) moves the same
+    bytes as the row pulls it was derived from: emulate the job semantics of copy_jobs.cuh on NumPy
+    regions for row data (16-byte units, chunked) and for per-head statistics (4-byte units)."""
+    import numpy as np
+    from dcp_b200.planner import lowering as L
+    rng = np.random.default_rng(0)
+    world, hq, rows = 3, 4, 700
+    row_units = hq * 16                                   # [rows, hq, 128] bf16 -> 16-byte units per row
+    src = [rng.integers(0, 1 << 30, size=(rows * row_units, 4), dtype=np.int64).astype(np.uint32) for _ in range(world)]
+    stats = [rng.standard_normal((hq, rows)).astype(np.float32) for _ in range(world)]
+    pulls = np.asarray([(1, 10, 300, 257), (2, 0, 560, 33), (1, 400, 600, 1)], dtype=np.int32)
+    L_saved = L.JOB_CHUNK_UNITS
+    L.JOB_CHUNK_UNITS = 1000                              # force several chunks per pull, with a ragged tail
+    try:
+        jobs = L.row_copy_jobs(pulls, L.KIND_Q, row_units)
+    finally:
+        L.JOB_CHUNK_UNITS = L_saved
+    assert jobs.shape[0] > pulls.shape[0] and (jobs[:, 2] <= 1000).all()
+    dst = np.zeros_like(src[0])
+    for s_off, d_off, n, where in jobs.tolist():
+        assert (where >> 8) & 0xff == L.KIND_Q and not where & (1 << 16)
+        dst[d_off:d_off + n] = src[where & 0xff][s_off:s_off + n]
+    ref = np.zeros_like(src[0])
+    for peer, s_row, d_row, n in pulls.tolist():
+        ref[d_row * row_units:(d_row + n) * row_units] = src[peer][s_row * row_units:(s_row + n) * row_units]
+    assert (dst == ref).all()
+    sjobs = L.stat_copy_jobs(pulls, L.KIND_LSE, hq)
+    assert sjobs.shape[0] == pulls.shape[0] * hq
+    dst_s, ref_s = np.zeros((hq, rows), np.float32), np.zeros((hq, rows), np.float32)
+    for s_off, d_off, n, where in sjobs.tolist():
+        assert where & (1 << 16) and (where >> 8) & 0xff == L.KIND_LSE
+        h = (where >> 24) & 0xff
+        dst_s[h, d_off:d_off + n] = stats[where & 0xff][h, s_off:s_off + n]
+    for peer, s_row, d_row, n in pulls.tolist():
+        ref_s[:, d_row:d_row + n] = stats[peer][:, s_row:s_row + n]
+    assert (dst_s == ref_s).all()

@@ -23,14 +23,17 @@ def test_fused_executor_single_gpu():
     assert res.returncode == 0 and "FUSED_OK" in res.stdout, res.stdout[-3000:]
 
 
-def test_fused_executor_two_gpus():
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_fused_executor_multi_gpu(world):
+    """The fused executor on 2 / 4 / 8 GPUs against dense attention: peer operand fetch inside the
+    kernels, partial (out, lse) stores into owners' arenas, merge, gradient push, flag barriers."""
     _need_gpu()
-    if torch.cuda.device_count() < 2:
-        pytest.skip("needs two GPUs")
-    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
-           "127.0.0.1", "--master-port", "29541", os.path.join(ROOT, "tests", "fused_worker.py")]
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr",
+           "127.0.0.1", "--master-port", str(29541 + world), os.path.join(ROOT, "tests", "fused_worker.py")]
     # also exercises the executor's debugging modes: a status check after every phase, and staging
-    # regions filled with a sentinel before every call (an un-pulled block would wreck the result)
+    # regions filled with a sentinel before every call (an un-fetched block would wreck the result)
     res = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=900,
                          env=dict(os.environ, PYTHONPATH=ROOT, DCP_B200_SYNCHRONOUS="1", DCP_B200_POISON="1"))
     assert res.returncode == 0 and "FUSED_OK" in res.stdout, res.stdout[-3000:]
