@@ -17,8 +17,10 @@
 // (local accumulator) or one 128-byte bulk reduce per query row (peer accumulator).  dK/dV stay
 // in TMEM for the CTA's lifetime and are added once with red.global.add.v4.f32.
 // TMEM columns: S^T [0,64) dP^T [64,128) dQ^T [128,192) [192,256) dK [256,384) dV [384,512).
-// Two more warps per CTA fetch the next plan stage's remote operands (Q, dO, KV rows and the lse /
-// delta statistics of the queries) from peer GPUs while the items are computed (copy_jobs.cuh).
+// The first `n_copy_rows` rows of the grid are fetch CTAs: they compute nothing and bring the next plan
+// stage's remote operands (Q, dO, KV rows and the lse / delta statistics of the queries) from peer
+// GPUs into this GPU's staging rows (copy_jobs.cuh) while the other CTAs of the same launch work
+// through the items; they are scheduled first and retire after about a millisecond.
 //
 // Reference behaviour covered: the varlen backward the executor calls at
 // dcp/runtime/flash_attention/executor.py:1058-1115, plus the blockwise partial sums
@@ -33,7 +35,7 @@
 
 namespace dcpk {
 
-static constexpr int kBwdThreads = 384;  // 8 gradient warps + TMA producer + UMMA issuer + 2 operand-fetch warps
+static constexpr int kBwdThreads = 320;  // 8 gradient warps + TMA producer + UMMA issuer
 static constexpr int kQTile = 64;
 static constexpr int kStages = 3;  // depth of the Q / dO / statistics ring
 static constexpr int kKvHalf = 128 * 64 * 2;  // [128 x 64] bf16 half tile, 16 KB
@@ -127,12 +129,18 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                 const float* __restrict__ lse, const float* __restrict__ delta, BwdPtrs ptrs, int hq, int hkv,
                 int stat_stride, int n_dst, int q_rows, int kv_rows, int n_mask_rows, int n_items_total, float scale,
                 const CopyJob* __restrict__ jobs, int n_jobs, const __grid_constant__ CopyCtx copy_ctx,
-                int* __restrict__ status) {
+                int n_copy_rows, int* __restrict__ status) {
+  if (int(blockIdx.y) < n_copy_rows) {
+    // ------------------------------------------------------------ operand fetch for the next stage
+    run_copy_jobs(jobs, n_jobs, copy_ctx, blockIdx.y * gridDim.x + blockIdx.x, n_copy_rows * gridDim.x, threadIdx.x,
+                  kBwdThreads);
+    return;
+  }
   extern __shared__ uint8_t smem_raw[];
   BwdSmem& sm = *reinterpret_cast<BwdSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // grid = (kv heads, key tiles): neighbouring CTAs share the item list and the mask rows
-  const BwdCta cta = ctas[blockIdx.y];
+  const BwdCta cta = ctas[blockIdx.y - n_copy_rows];
   const int kv_head = blockIdx.x;
   const int group = hq / hkv;
   const BwdItemDesc* my_items = items + cta.item_off;
@@ -176,7 +184,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   volatile int* abort_word = &sm.abort_word;
   constexpr uint32_t cS = 0, cdP = 64, cdQ = 128 /* two 64-column buffers */, cdK = 256, cdV = 384;
 
-  long long* tl = (kTL && blockIdx.x == 0 && blockIdx.y == 0 && (warp == 0 || warp == 9)) ? g_bwd_timeline : nullptr;
+  long long* tl = (kTL && blockIdx.x == 0 && int(blockIdx.y) == n_copy_rows && (warp == 0 || warp == 9)) ? g_bwd_timeline : nullptr;
   long long tl_t = kTL ? clock64() : 0;
   if (warp == 8) {
     // ------------------------------------------------------------ TMA producer
@@ -315,10 +323,6 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     }
     if (ok && n_items > 0) ok = issue_acc(n_items - 1);
     if (ok && n_items > 0) mbar_wait(&sm.dq_full, (n_items - 1) & 1, abort_word);
-  } else if (warp >= 10) {
-    // ------------------------------------------------------------ operand fetch for the next stage
-    run_copy_jobs(jobs, n_jobs, copy_ctx, blockIdx.y * gridDim.x + blockIdx.x, gridDim.x * gridDim.y,
-                  threadIdx.x - 320, 64);
   } else {
     // ------------------------------------------------------------ softmax-gradient threads
     // 8 warps: warp w works on TMEM lanes 32*(w&3).. (key rows) and on query columns 32*(w>>2)..+31
@@ -590,9 +594,11 @@ extern "C" int dcpk_attn_bwd(const void* q_arena, const void* do_arena, long q_r
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return -4;
     g_bwd_attr_set[v] = 1;
   }
-  kernel<<<dim3(hkv, n_ctas), kBwdThreads, smem, static_cast<cudaStream_t>(stream)>>>(
+  // about 16 fetch CTAs when there is something to fetch
+  const int n_copy_rows = n_jobs > 0 ? (16 + hkv - 1) / hkv : 0;
+  kernel<<<dim3(hkv, n_ctas + n_copy_rows), kBwdThreads, smem, static_cast<cudaStream_t>(stream)>>>(
       tm_q, tm_do, tm_kv, tm_dq, static_cast<const BwdCta*>(ctas), static_cast<const BwdItemDesc*>(items),
       static_cast<const int4*>(masks), lse, delta, pp, hq, hkv, stat_stride, n_dst, int(q_rows), int(kv_rows),
-      n_mask_rows, n_items_total, scale, static_cast<const CopyJob*>(jobs), n_jobs, ctx, status);
+      n_mask_rows, n_items_total, scale, static_cast<const CopyJob*>(jobs), n_jobs, ctx, n_copy_rows, status);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }

@@ -292,3 +292,27 @@ def test_planning_is_identical_across_processes():
         assert res.returncode == 0, res.stdout[-2000:]
         digests.add([l for l in res.stdout.splitlines() if l.startswith("PLANHASH")][0])
     assert len(digests) == 1, digests
+
+
+def test_optimizer_shard_layout_covers_every_bucket_for_any_world_size():
+    """The slicing formula shared by optimizer state, reduce-scatter, all-gather and resume: for
+    world sizes that do not divide the buckets (3, 5, 6, 7) the ranks' slices tile every bucket
+    exactly, are 8-element aligned, and the state offsets are the running sum of the lengths."""
+    from dcp_b200.parallel.dist_optimizer import shard_layout
+    buckets = [(0, 4096), (4096, 8 * 1001), (4096 + 8 * 1001, 8), (4096 + 8 * 1002, 8 * 3333)]
+    for world in (1, 2, 3, 5, 6, 7, 8):
+        per_rank = [shard_layout(buckets, world, r) for r in range(world)]
+        for b, (off, length) in enumerate(buckets):
+            pos = off
+            for r in range(world):
+                s = per_rank[r][b]
+                assert s.bucket == b and s.length % 8 == 0 and s.flat_off % 8 == 0
+                if s.length:
+                    assert s.flat_off == pos
+                    pos += s.length
+            assert pos == off + length
+        for shards in per_rank:
+            acc = 0
+            for s in shards:
+                assert s.state_off == acc
+                acc += s.length

@@ -39,6 +39,20 @@ def test_fused_executor_multi_gpu(world):
     assert res.returncode == 0 and "FUSED_OK" in res.stdout, res.stdout[-3000:]
 
 
+def test_overlapped_sharded_optimizer_two_gpus():
+    """Bucketed reduce-scatter on a side stream + sharded AdamW + all-gather against fp32
+    torch.optim.AdamW on the rank-summed gradients, parameter rebuild from the master shards, and
+    the status guard that keeps a detected failure away from the weights."""
+    _need_gpu()
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
+           "127.0.0.1", "--master-port", "29561", os.path.join(ROOT, "tests", "opt_worker.py")]
+    res = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=600,
+                         env=dict(os.environ, PYTHONPATH=ROOT))
+    assert res.returncode == 0 and "OPT_OK" in res.stdout, res.stdout[-3000:]
+
+
 def test_tensor_parallel_step_two_gpus():
     """Tensor parallelism (heads and FFN split over two ranks): loss and gradients match the fp32
     model assembled from the shards; replicated parameters stay identical through a step."""
