@@ -25,7 +25,7 @@ from ..core.common import get_default_execution_context
 from ..core.instructions import BufferType
 from ..planner import masks as mask_lib
 from ..planner.compiler import CompilerConfig, InstrCompiler
-from ..planner.lowering import FusedProgram, lower_all
+from ..planner.lowering import FusedProgram, lower_all, lower_plans
 from ..planner.workload import generate_workload, pad_seqlens
 from ..runtime.layout import LocalLayout, seq_token_offsets
 from . import synth
@@ -49,6 +49,7 @@ class PlanSpec:
     n_stages: Optional[int] = None
     build_backward: bool = True
     build_instruction_plans: bool = False   # also emit ExecutionPlans (plan-interpreting executors)
+    lower_from_plans: bool = False          # derive the fused tables from the ExecutionPlan instruction streams
     # planner knobs (None = the defaults of CompilerConfig / the cost models)
     mem_imbalance_epsilon: Optional[float] = None
     comp_imbalance_epsilon: Optional[float] = None
@@ -183,14 +184,15 @@ def plan_batch(spec: PlanSpec, iteration: int, rank: int, seqlens: Sequence[int]
     compiler = InstrCompiler(ctx, ccfg)
     fw_wl, bw_wl, fw_plans, bw_plans = compiler.compile(wl, generate_backward=spec.build_instruction_plans)
     dev = (0, group_rank)
+    lower = (lambda c, w, bb, only=None: lower_plans(c, w, fw_plans, bb, only)) if spec.lower_from_plans else lower_all
     if os.environ.get("DCP_B200_VALIDATE", "0") == "1":
         # debug: lower every rank's program and check the tables against each other before use
         from ..planner.validate import validate_programs
-        all_programs = lower_all(ctx, fw_wl, spec.build_backward)
+        all_programs = lower(ctx, fw_wl, spec.build_backward)
         validate_programs(all_programs)
         program = all_programs[dev]
     else:
-        program = lower_all(ctx, fw_wl, spec.build_backward, only=dev)[dev]
+        program = lower(ctx, fw_wl, spec.build_backward, only=dev)[dev]
     lay = LocalLayout(fw_wl, dev)
     idx = []
     for _, m in lay.blocks.get(BufferType.LOCAL_Q, []):

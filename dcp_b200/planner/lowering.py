@@ -56,6 +56,7 @@ class FusedProgram:
     bwd_flops: float = 0.0
     pull_bytes: float = 0.0
     need_all: Tuple[int, int, int] = (0, 0, 0)   # max over all ranks of (q_rows, kv_rows, part_rows)
+    relayed_blocks: int = 0   # blocks an instruction plan relays through a non-owner (fetched from the owner here)
 
     def max_rows(self) -> Tuple[int, int, int]:
         return self.q_rows, self.kv_rows, self.part_rows
@@ -91,7 +92,47 @@ def stat_copy_jobs(pulls: np.ndarray, kind: int, heads: int) -> np.ndarray:
 
 def lower_all(context: ExecutionContext, workload: WorkloadSpec, build_backward: bool = True,
               only: Optional[Device] = None) -> Dict[Device, FusedProgram]:
-    """Programs of all devices, or just of ``only`` (row and slot numbering is global either way)."""
+    """Programs of all devices, or just of ``only`` (row and slot numbering is global either way),
+    from the placed and staged workload (``work_to_device_map`` / ``work_to_stage_map``)."""
+    return _lower(context, workload, workload.work_to_device_map, workload.work_to_stage_map, None, None,
+                  build_backward, only)
+
+
+def lower_plans(context: ExecutionContext, workload: WorkloadSpec, fw_plans, build_backward: bool = True,
+                only: Optional[Device] = None) -> Dict[Device, FusedProgram]:
+    """Programs derived from the forward ``ExecutionPlan`` instruction streams of all devices.
+
+    The plans are run symbolically (``planner.validate.validate_plans``, which also checks them): every
+    attention row of every AttnInstr gives the device and stage of its work units, the order of its KV
+    blocks and its key ranges; every RECV gives the stage's source of a remote block.  Those replace
+    the workload's own maps and masks as the input of the lowering, so a plan deserialised from bytes
+    (plus the workload's block metadata) is all the fused executor needs.  What the fused path does
+    not take over from the plan is its temporary slot numbering: the interpreter reuses slots in time
+    (pairwise reductions free them), the fused path keeps every partial until its single merge, so
+    staging rows and partial slots are numbered by the lowering.  A block the plan relays through a
+    non-owner is fetched from its owner instead (all peers of an NVSwitch node are equally far, and
+    only the owners' local rows are guaranteed complete at the barrier that opens a call).
+
+    Role of AttentionExecutor.execute interpreting a plan (dcp/runtime/flash_attention/executor.py:486-515,
+    dcp/core/executor.py:128-141)."""
+    from .validate import validate_plans
+    trace: dict = {}
+    validate_plans(context, workload, fw_plans, True, trace)
+    pair_to_work = {(u.q_id, u.kv_id): w for w, u in workload.block_mapping.work_id_to_meta.items()}
+    w2d, w2s, row_ranges = {}, {}, {}
+    for dev, stage, q_id, kv_ids, rng4 in trace["rows"]:
+        for kv_id in kv_ids:
+            w = pair_to_work[(q_id, kv_id)]
+            w2d[w], w2s[w] = tuple(dev), stage
+        row_ranges[(tuple(dev), stage, q_id)] = (list(kv_ids), rng4)
+    return _lower(context, workload, w2d, w2s, row_ranges, trace["recv"], build_backward, only)
+
+
+def _lower(context: ExecutionContext, workload: WorkloadSpec, work_to_device, work_to_stage, row_ranges, sources,
+           build_backward: bool, only: Optional[Device]) -> Dict[Device, FusedProgram]:
+    """Shared lowering.  ``row_ranges`` {(device, stage, q id): ([kv ids in order], ranges [n, 4])} and
+    ``sources`` {(device, block id): device the plan receives it from} come from instruction plans
+    (None: derive rows and masks from the workload, fetch from owners)."""
     wl = workload
     devices = context.devices()
     world = len(devices)
@@ -101,7 +142,7 @@ def lower_all(context: ExecutionContext, workload: WorkloadSpec, build_backward:
     any_q = next(m for m in in_meta.values() if m.type == BlockType.Q)
     any_kv = next(m for m in in_meta.values() if m.type == BlockType.KV)
     block_size, hq, hkv = any_q.block_size, any_q.head_block_size, any_kv.head_block_size
-    n_stages = (max(wl.work_to_stage_map.values()) + 1) if wl.work_to_stage_map else 1
+    n_stages = (max(work_to_stage.values()) + 1) if work_to_stage else 1
     layouts = {d: LocalLayout(wl, d) for d in devices}
     owner_in = {i: tuple(d) for i, d in wl.input_to_device_map.items()}
     owner_out = {o: tuple(d) for o, d in wl.output_to_device_map.items()}
@@ -118,8 +159,9 @@ def lower_all(context: ExecutionContext, workload: WorkloadSpec, build_backward:
     q_pulls = {d: [[] for _ in range(n_stages)] for d in devices}
     kv_pulls = {d: [[] for _ in range(n_stages)] for d in devices}
     units_ps: Dict[Device, List[List[int]]] = {d: [[] for _ in range(n_stages)] for d in devices}
-    for w in sorted(wl.work_to_stage_map):
-        units_ps[tuple(wl.work_to_device_map[w])][wl.work_to_stage_map[w]].append(w)
+    for w in sorted(work_to_stage):
+        units_ps[tuple(work_to_device[w])][work_to_stage[w]].append(w)
+    relayed = 0
     pull_bytes = {d: 0.0 for d in devices}
     for d in devices:
         for s in range(n_stages):
@@ -133,6 +175,9 @@ def lower_all(context: ExecutionContext, workload: WorkloadSpec, build_backward:
                     if own == d:
                         rows[d][bid] = local_row(d, buf, bid)
                     else:
+                        if sources is not None:
+                            assert (d, bid) in sources, f"plan of {d} uses remote block {bid} without receiving it"
+                            relayed += tuple(sources[(d, bid)]) != own
                         n = in_meta[bid].n_tokens
                         rows[d][bid] = nxt[d]
                         pulls[d][s].append((rank_of[own], local_row(own, buf, bid), nxt[d], n))
@@ -172,6 +217,7 @@ def lower_all(context: ExecutionContext, workload: WorkloadSpec, build_backward:
                             layouts[d].n_tokens(BufferType.LOCAL_Q), layouts[d].n_tokens(BufferType.LOCAL_KV),
                             q_next[d], kv_next[d], part_next[d])
         prog.pull_bytes = pull_bytes[d]
+        prog.relayed_blocks = relayed
         prog.need_all = (max(q_next.values()), max(kv_next.values()), max(part_next.values()))
         for s in range(n_stages):
             prog.q_pulls.append(_i4(q_pulls[d][s]))
@@ -184,8 +230,15 @@ def lower_all(context: ExecutionContext, workload: WorkloadSpec, build_backward:
             for q_id in sorted(rows_ps[d][s]):
                 units = sorted((work_meta[w] for w in rows_ps[d][s][q_id]), key=lambda u: in_meta[u.kv_id].block_id)
                 qm = in_meta[q_id]
-                rng = _concat_row_mask(units, qm.n_tokens, block_size)           # [range, bound, n_q]
-                ranges = np.ascontiguousarray(rng.transpose(2, 0, 1).reshape(qm.n_tokens, 4))
+                if row_ranges is not None:
+                    kv_order, ranges = row_ranges[(d, s, q_id)]
+                    by_kv = {u.kv_id: u for u in units}
+                    assert sorted(kv_order) == sorted(by_kv), f"plan row of q block {q_id} lists other KV blocks"
+                    units = [by_kv[k] for k in kv_order]                         # the plan's table order
+                    ranges = np.ascontiguousarray(ranges, dtype=np.int32).reshape(qm.n_tokens, 4)
+                else:
+                    rng = _concat_row_mask(units, qm.n_tokens, block_size)       # [range, bound, n_q]
+                    ranges = np.ascontiguousarray(rng.transpose(2, 0, 1).reshape(qm.n_tokens, 4))
                 out_id = units[0].out_id
                 own = owner_out[out_id]
                 if (out_id, d, s) in part_slot:

@@ -13,6 +13,8 @@ from __future__ import annotations
 from collections import defaultdict, deque
 from typing import Dict, List, Tuple
 
+import numpy as np
+
 from ..core.blocks import BlockType, Device, WorkloadSpec
 from ..core.common import ExecutionContext
 from ..core.instructions import (AttnBackwardInstr, AttnInstr, AttnReductionInstr, BarrierInstr, BufferBlock,
@@ -62,8 +64,15 @@ def _is_input_buffer(name: str, wl: WorkloadSpec) -> bool:
 
 
 def validate_plans(context: ExecutionContext, workload: WorkloadSpec, plans: Dict[Device, ExecutionPlan],
-                   is_forward: bool = True) -> dict:
+                   is_forward: bool = True, trace: dict = None) -> dict:
+    """Symbolic run of all devices' plans (see the module docstring).  When ``trace`` is a dict it is
+    filled with what the instruction streams say was done: ``trace["rows"]`` = one entry per attention
+    row (device, stage, q block id, [kv block ids in table order], int32 [n_tokens, 4] key ranges) and
+    ``trace["recv"]`` = {(device, input block id): device it was received from}."""
     wl = workload
+    if trace is not None:
+        trace.setdefault("rows", [])
+        trace.setdefault("recv", {})
     in_meta, out_meta = wl.block_mapping.input_id_to_meta, wl.block_mapping.output_id_to_meta
     pair_to_work = {}
     for w, u in wl.block_mapping.work_id_to_meta.items():
@@ -106,6 +115,8 @@ def validate_plans(context: ExecutionContext, workload: WorkloadSpec, plans: Dic
                 _check(_family(sblk.buffer_type) == _family(blk.buffer_type),
                        f"{D.dev}: {ins.key} from {peer}: {sblk.buffer_type} received into {blk.buffer_type}")
                 D.write(blk, val)
+                if trace is not None and val[0] == "in":
+                    trace["recv"][(D.dev, val[1])] = peer
                 stats["comm_blocks"] += 1
         elif isinstance(ins, BarrierInstr):
             pass
@@ -140,6 +151,15 @@ def validate_plans(context: ExecutionContext, workload: WorkloadSpec, plans: Dic
                     seg = m[..., col:col + ins.seqlens_q[i]]
                     _check(int(seg.min()) >= 0 and int(seg.max()) <= ins.seqlens_kv[i], f"{D.dev}: mask range outside row")
                 u = wl.block_mapping.work_id_to_meta[next(iter(works))]
+                if trace is not None:
+                    n_tok = q[2]
+                    cols = [np.asarray(m[..., col:col + n_tok]) for m in items]
+                    if cols[0].ndim == 1:      # compact single-range form: items = (starts, ends)
+                        rng4 = np.stack([cols[0], cols[1], np.zeros_like(cols[0]), np.zeros_like(cols[0])], axis=1)
+                    else:                      # items = ranges, each [bound, query]
+                        rng4 = np.stack([cols[0][0], cols[0][1], cols[1][0], cols[1][1]], axis=1)
+                    kv_ids = [D.read(kb, "attn kv")[1] for kb in ins.kv_block_table[i]]
+                    trace["rows"].append((D.dev, ins.stage_id, q[1], kv_ids, rng4.astype(np.int32)))
                 if not bw:
                     ob, lb = ins.out_block_table[i][0], ins.lse_block_table[i][0]
                     D.write(ob, ("part", u.out_id, frozenset(works), ob.n_tokens))

@@ -101,12 +101,20 @@ class FusedPlanExecutor:
                  fw_exec_plan: Optional[ExecutionPlan] = None, fw_workload: Optional[WorkloadSpec] = None,
                  bw_exec_plan: Optional[ExecutionPlan] = None, bw_workload: Optional[WorkloadSpec] = None,
                  process_group=None, synchronous: bool = False, device: Optional[torch.device] = None,
-                 softmax_scale: Optional[float] = None, **_unused):
-        from ..planner.lowering import lower_all
+                 softmax_scale: Optional[float] = None, all_fw_exec_plans=None, **_unused):
+        """``all_fw_exec_plans`` ({device: forward ExecutionPlan} of every device of the group, e.g.
+        deserialised from bytes): when given, the kernel tables are derived from those instruction
+        streams (``planner.lowering.lower_plans``); a rank needs its peers' plans because its tiles
+        store partial results straight into the owners' arenas.  Without it the tables come from
+        the placed and staged workload, which every rank holds."""
+        from ..planner.lowering import lower_all, lower_plans
         from .executor_fused import FusedAttentionExecutor
         assert head_dim == 128, "the sm_100a attention kernels are built for head_dim 128"
         dev = (fw_exec_plan.node_id, fw_exec_plan.local_device_id)
-        self.program = lower_all(exec_context, fw_workload, build_backward=True, only=dev)[dev]
+        if all_fw_exec_plans is not None:
+            self.program = lower_plans(exec_context, fw_workload, all_fw_exec_plans, build_backward=True, only=dev)[dev]
+        else:
+            self.program = lower_all(exec_context, fw_workload, build_backward=True, only=dev)[dev]
         device = device or torch.device("cuda", torch.cuda.current_device())
         rq, rkv, rp = self.program.need_all
         self.impl = FusedAttentionExecutor(self.program.heads_q, self.program.heads_kv, rq, rkv, max(rp, 128), device,
@@ -163,11 +171,11 @@ class FusedPlanExecutor:
 def get_executor(n_heads_per_block: int, head_dim: int, exec_context: ExecutionContext, fw_exec_plan=None,
                  fw_workload=None, bw_exec_plan=None, bw_workload=None, executor_impl: str = "python",
                  process_group=None, synchronous: bool = False, iteration_idx=None, tp_rank=None,
-                 use_cudagraph: bool = False, comm=None, device=None) -> AttentionExecutor:
+                 use_cudagraph: bool = False, comm=None, device=None, all_fw_exec_plans=None) -> AttentionExecutor:
     if executor_impl == "fused":
         # the B200-native path behind the same interface (CUDA only, head_dim 128)
         return FusedPlanExecutor(n_heads_per_block, head_dim, exec_context, fw_exec_plan, fw_workload, bw_exec_plan,
-                                 bw_workload, process_group, synchronous, device)
+                                 bw_workload, process_group, synchronous, device, all_fw_exec_plans=all_fw_exec_plans)
     if executor_impl not in ("python", "reference"):
         raise ValueError("executor_impl is 'python' (plan interpreter) or 'fused' (sm_100a kernels)")
     return AttentionExecutor(n_heads_per_block, head_dim, exec_context, fw_exec_plan, fw_workload, bw_exec_plan,
@@ -213,8 +221,15 @@ def prepare_dcp_distributed_attn_for_test(raw_seqlens: Sequence[int], n_heads: i
     q = torch.randn(T, n_heads, head_dim, generator=g).to(dtype)
     kv = torch.randn(T, 2, n_query_groups, head_dim, generator=g).to(dtype)
     dout = torch.randn(T, n_heads, head_dim, generator=g).to(dtype)
+    all_plans = None
+    if executor_impl == "fused-from-plan-bytes":
+        # the fused executor fed with nothing but serialised plans: every device's forward plan goes
+        # through its byte encoding and the kernel tables are derived from the instruction streams
+        executor_impl = "fused"
+        all_plans = {d: ExecutionPlan.deserialize(p.serialize())[0] for d, p in fw.items()}
     ex = get_executor(head_block_size, head_dim, exec_context, fw[dev], fw_wl, bw[dev], bw_wl,
-                      executor_impl=executor_impl, process_group=process_group, comm=comm, device=device)
+                      executor_impl=executor_impl, process_group=process_group, comm=comm, device=device,
+                      all_fw_exec_plans=all_plans)
     lay = LocalLayout(fw_wl, dev)
     mv = (lambda t: t.to(device)) if device is not None else (lambda t: t)
     lq, lkv = get_local_q_kv(q, kv, fw_wl, dev, raw_seqlens)

@@ -25,7 +25,8 @@ from .layout import LocalLayout, gather_local, scatter_to_global, seq_token_offs
 
 def dense_reference(q: torch.Tensor, kv: torch.Tensor, raw_seqlens: Sequence[int], padded_seqlens: Sequence[int],
                     attn_mask: Optional[torch.Tensor], scale: float, dout: Optional[torch.Tensor] = None):
-    """Per-sequence dense masked attention in fp64 -> (out [T,H,d], lse [H,T], dq, dkv)."""
+    """Per-sequence dense masked attention in fp64 -> (out [T,H,d], lse [H,T], dq, dkv), computed on
+    the device the inputs live on."""
     T, H, d = q.shape
     hkv = kv.shape[2]
     g = H // hkv
@@ -39,11 +40,11 @@ def dense_reference(q: torch.Tensor, kv: torch.Tensor, raw_seqlens: Sequence[int
         qs = qd[cu[s]:cu[s] + n]
         ks = kvd[cu[s]:cu[s] + n, 0].repeat_interleave(g, dim=1)
         vs = kvd[cu[s]:cu[s] + n, 1].repeat_interleave(g, dim=1)
-        pos = torch.arange(n)[None, :]
+        pos = torch.arange(n, device=q.device)[None, :]
         if rng is None:
-            allow = pos <= torch.arange(n)[:, None]
+            allow = pos <= torch.arange(n, device=q.device)[:, None]
         else:
-            r = torch.from_numpy(rng[pcu[s]:pcu[s] + n])
+            r = torch.from_numpy(rng[pcu[s]:pcu[s] + n]).to(q.device)
             allow = ((pos >= r[:, 0, 0:1]) & (pos < r[:, 0, 1:2])) | ((pos >= r[:, 1, 0:1]) & (pos < r[:, 1, 1:2]))
         sc = torch.einsum("qhd,khd->hqk", qs, ks) * scale
         sc = sc.masked_fill(~allow[None], float("-inf"))

@@ -106,6 +106,32 @@ def test_program_validator_catches_corrupted_tables():
             validate_programs(corrupted(fn))
 
 
+def _assert_same_programs(a, b, desc):
+    import dataclasses
+    import numpy as np
+    assert a.keys() == b.keys(), desc
+
+    def same(x, y, path):
+        if dataclasses.is_dataclass(x):
+            for f in dataclasses.fields(x):
+                if f.name == "relayed_blocks":      # informational: how often the plan relays through a non-owner
+                    continue
+                same(getattr(x, f.name), getattr(y, f.name), f"{path}.{f.name}")
+        elif isinstance(x, (list, tuple)):
+            assert len(x) == len(y), (desc, path)
+            for i, (u, v) in enumerate(zip(x, y)):
+                same(u, v, f"{path}[{i}]")
+        elif isinstance(x, torch.Tensor):
+            assert x.shape == y.shape and bool((x == y).all()), (desc, path)
+        elif isinstance(x, np.ndarray):
+            assert x.shape == y.shape and bool((x == y).all()), (desc, path)
+        else:
+            assert x == y, (desc, path, x, y)
+
+    for dev in a:
+        same(a[dev], b[dev], str(dev))
+
+
 @pytest.mark.parametrize("seed", [1, 2])
 def test_random_configurations(seed):
     """Seeded fuzz over world sizes (odd ones included), block sizes, head-block splits, masks, stage
@@ -136,6 +162,12 @@ def test_random_configurations(seed):
         validate_plans(ctx, bw_wl, bw, False)
         progs = lower_all(ctx, fw_wl)
         validate_programs(progs)
+        # the fused programs derived from the instruction streams (here: plans that went through their
+        # byte serialisation) are identical to the ones derived from the placed workload
+        from dcp_b200.core.instructions import ExecutionPlan
+        from dcp_b200.planner.lowering import lower_plans
+        fw_bytes = {dev: ExecutionPlan.deserialize(plan.serialize())[0] for dev, plan in fw.items()}
+        _assert_same_programs(lower_plans(ctx, fw_wl, fw_bytes), progs, desc)
         if sum(raw) > 2000:
             continue
         devs, T = ctx.devices(), sum(raw)

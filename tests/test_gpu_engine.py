@@ -134,9 +134,11 @@ def test_checkpoint_resume_continues_identically(tmp_path):
     a.close(); b.close()
 
 
-def test_reference_api_with_fused_backend():
-    """The reference's call sequence (get_executor(...), DCPAttention.apply) with executor_impl="fused":
-    same local layouts as the plan interpreter, results equal to dense attention."""
+@pytest.mark.parametrize("impl", ["fused", "fused-from-plan-bytes"])
+def test_reference_api_with_fused_backend(impl):
+    """The reference's call sequence (get_executor(...), DCPAttention.apply) with the fused executor,
+    its tables lowered from the placed workload or from plans deserialised from bytes: same local
+    layouts as the plan interpreter, results equal to dense attention."""
     _need_gpu()
     from dcp_b200.core.common import get_default_execution_context
     from dcp_b200.runtime.interface import DCPAttention, prepare_dcp_distributed_attn_for_test
@@ -145,7 +147,7 @@ def test_reference_api_with_fused_backend():
     ctx = get_default_execution_context(1, 1)
     raw = [700, 300, 1100]
     ex, lq, lkv, ldo, q, kv, dout, _, pad = prepare_dcp_distributed_attn_for_test(
-        raw, 8, 2, 128, 256, 8, ctx, 0, "lambda", torch.bfloat16, device=dev, executor_impl="fused")
+        raw, 8, 2, 128, 256, 8, ctx, 0, "lambda", torch.bfloat16, device=dev, executor_impl=impl)
     lq.requires_grad_(True); lkv.requires_grad_(True)
     out = DCPAttention.apply(ex, False, False, lq, lkv)
     out.backward(ldo)
