@@ -122,15 +122,19 @@ class DCPDataLoader:
                  num_workers: int = 0, num_preprocess_workers: int = 2, pin_memory: bool = False,
                  drop_last: bool = False, timeout: float = 0, *, prefetch_factor: int = 2,
                  persistent_workers: bool = False, input_key: str = "text", mask_fn: Optional[Callable] = None,
-                 mask_fn_extra_keys=None, is_dryrun: bool = False, world: Optional[int] = None):
+                 mask_fn_extra_keys=None, is_dryrun: bool = False, world: Optional[int] = None,
+                 build_instruction_plans: bool = True):
         assert batch_sampler is not None, "pass an OrderedBatchSampler (token-budget batches)"
         self.training_spec, self.dataset, self.batch_sampler = training_spec, dataset, batch_sampler
         self.dcp_rank, self.pin_memory, self.is_dryrun = dcp_rank, pin_memory, is_dryrun
+        # pipeline stages read the same plans as their first stage (attention placement does not depend
+        # on the layer range a stage holds); kept so a caller can tell the stages' loaders apart
+        self.pp_rank, self.tp_rank = pp_rank, tp_rank
         ms = training_spec.model_spec
         self.plan_spec = PlanSpec(world or training_spec.dcp_size, training_spec.dcp_size, 0, ms.n_heads,
                                   ms.n_query_groups, ms.head_dim, training_spec.block_size,
                                   training_spec.head_block_size if training_spec.head_block_size != 1 else 0,
-                                  training_spec.mask_type, build_instruction_plans=True)
+                                  training_spec.mask_type, build_instruction_plans=build_instruction_plans)
         self.prefetch = max(1, prefetch_factor)
         self._pool = None
         if num_preprocess_workers > 0:

@@ -110,6 +110,24 @@ def plan_iteration(spec: PlanSpec, iteration: int, rank: int) -> RankPlan:
     return plan_batch(spec, iteration, rank, seqlens, batch, info, group_members=members)
 
 
+def plan_iteration_all(spec: PlanSpec, iteration: int) -> Dict[int, RankPlan]:
+    """Same batch as ``plan_iteration`` draws for ``iteration``, planned once for every rank."""
+    seed = spec.seed * 1000003 + iteration
+    n_groups = spec.world // spec.dcp_size
+    members = None
+    if n_groups > 1:
+        seqlens, members = [], []
+        for g in range(n_groups):
+            part = synth.sample_seqlens(spec.tokens_per_step // n_groups, spec.length_dist, seed * 64 + g + 1)
+            members.append(list(range(len(seqlens), len(seqlens) + len(part))))
+            seqlens += part
+    else:
+        seqlens = synth.sample_seqlens(spec.tokens_per_step, spec.length_dist, seed)
+    batch = synth.make_token_batch(seqlens, spec.vocab, seed)
+    info = synth.assign_mask_kinds(seqlens, seed) if spec.mask == "mixed" else None
+    return plan_batch_all(spec, iteration, seqlens, batch, info, group_members=members)
+
+
 def batch_signature(spec: PlanSpec, rank: int, seqlens: Sequence[int], mask_fn_info, group_members) -> str:
     """Stable key of everything a rank's plan depends on (the iteration number is not part of it:
     the same batch planned at another step gives the same plan)."""
@@ -146,10 +164,29 @@ def plan_batch(spec: PlanSpec, iteration: int, rank: int, seqlens: Sequence[int]
     """Plan one packed batch (``batch`` holds per-token arrays over the concatenated sequences) and
     return rank ``rank``'s share: its fused program, its tokens in local buffer order and, when
     requested, its instruction plans."""
+    group_id = rank // spec.dcp_size
+    return _plan_group(spec, iteration, group_id, seqlens, batch, mask_fn_info, mask_fn, group_members, only_rank=rank)[rank]
+
+
+def plan_batch_all(spec: PlanSpec, iteration: int, seqlens: Sequence[int], batch: Dict[str, np.ndarray],
+                   mask_fn_info: Optional[List[dict]] = None, mask_fn=None,
+                   group_members: Optional[List[List[int]]] = None) -> Dict[int, RankPlan]:
+    """Plan one packed batch once for every rank: each context-parallel group's sub-batch is placed,
+    staged and lowered a single time and every rank's share is cut from that result.  This is the
+    planner-process side of shared planning (the reference plans a batch once and publishes per-rank
+    plans, dcp/data/dataloader.py:519-740)."""
+    out: Dict[int, RankPlan] = {}
+    for g in range(spec.world // spec.dcp_size):
+        out.update(_plan_group(spec, iteration, g, seqlens, batch, mask_fn_info, mask_fn, group_members))
+    return out
+
+
+def _plan_group(spec: PlanSpec, iteration: int, group_id: int, seqlens: Sequence[int], batch: Dict[str, np.ndarray],
+                mask_fn_info, mask_fn, group_members, only_rank: Optional[int] = None) -> Dict[int, RankPlan]:
+    """Plans of the ranks of one context-parallel group (all of them, or just ``only_rank``)."""
     t0 = time.time()
     seqlens = [int(x) for x in seqlens]
     n_groups = spec.world // spec.dcp_size
-    group_id, group_rank = divmod(rank, spec.dcp_size)
     if group_members is not None:
         members = group_members[group_id]
     else:
@@ -183,30 +220,38 @@ def plan_batch(spec: PlanSpec, iteration: int, rank: int, seqlens: Sequence[int]
             setattr(ccfg, name, getattr(spec, name))
     compiler = InstrCompiler(ctx, ccfg)
     fw_wl, bw_wl, fw_plans, bw_plans = compiler.compile(wl, generate_backward=spec.build_instruction_plans)
-    dev = (0, group_rank)
     lower = (lambda c, w, bb, only=None: lower_plans(c, w, fw_plans, bb, only)) if spec.lower_from_plans else lower_all
-    if os.environ.get("DCP_B200_VALIDATE", "0") == "1":
-        # debug: lower every rank's program and check the tables against each other before use
-        from ..planner.validate import validate_programs
-        all_programs = lower(ctx, fw_wl, spec.build_backward)
-        validate_programs(all_programs)
-        program = all_programs[dev]
+    only_dev = None if only_rank is None else (0, only_rank % spec.dcp_size)
+    if only_dev is None or os.environ.get("DCP_B200_VALIDATE", "0") == "1":
+        programs = lower(ctx, fw_wl, spec.build_backward)
+        if os.environ.get("DCP_B200_VALIDATE", "0") == "1":
+            # debug: check every rank's tables against each other before use
+            from ..planner.validate import validate_programs
+            validate_programs(programs)
     else:
-        program = lower(ctx, fw_wl, spec.build_backward, only=dev)[dev]
-    lay = LocalLayout(fw_wl, dev)
-    idx = []
-    for _, m in lay.blocks.get(BufferType.LOCAL_Q, []):
-        if m.head_id != 0:
+        programs = lower(ctx, fw_wl, spec.build_backward, only=only_dev)
+    out: Dict[int, RankPlan] = {}
+    plan_s = time.time() - t0
+    for group_rank in range(spec.dcp_size):
+        dev = (0, group_rank)
+        if only_dev is not None and dev != only_dev:
             continue
-        t0_tok = int(cu_all[members[m.seq_id]]) + m.block_id * bs
-        idx.append(np.arange(t0_tok, t0_tok + m.n_tokens))
-    idx = np.concatenate(idx) if idx else np.zeros(0, dtype=np.int64)
-    to_t = lambda a: torch.from_numpy(np.ascontiguousarray(np.asarray(a)[idx]))
-    return RankPlan(iteration, program, to_t(batch["tokens"]), to_t(batch["labels"]), to_t(batch["positions"]),
-                    int(sum(seqlens)), int(sum(raw)), list(seqlens), time.time() - t0,
-                    fw_plans.get(dev) if spec.build_instruction_plans else None,
-                    bw_plans.get(dev) if (spec.build_instruction_plans and bw_plans) else None,
-                    fw_wl if spec.build_instruction_plans else None, bw_wl if spec.build_instruction_plans else None)
+        lay = LocalLayout(fw_wl, dev)
+        idx = []
+        for _, m in lay.blocks.get(BufferType.LOCAL_Q, []):
+            if m.head_id != 0:
+                continue
+            t0_tok = int(cu_all[members[m.seq_id]]) + m.block_id * bs
+            idx.append(np.arange(t0_tok, t0_tok + m.n_tokens))
+        idx = np.concatenate(idx) if idx else np.zeros(0, dtype=np.int64)
+        to_t = lambda a: torch.from_numpy(np.ascontiguousarray(np.asarray(a)[idx]))
+        keep = spec.build_instruction_plans
+        out[group_id * spec.dcp_size + group_rank] = RankPlan(
+            iteration, programs[dev], to_t(batch["tokens"]), to_t(batch["labels"]), to_t(batch["positions"]),
+            int(sum(seqlens)), int(sum(raw)), list(seqlens), plan_s,
+            fw_plans.get(dev) if keep else None, bw_plans.get(dev) if (keep and bw_plans) else None,
+            fw_wl if keep else None, bw_wl if keep else None)
+    return out
 
 
 def _worker_init():
@@ -243,6 +288,95 @@ class PlanService:
         t0 = time.time()
         fut = self._pending.pop(iteration, None)
         plan = fut.result() if fut is not None else plan_iteration(self.spec, iteration, self.rank)
+        waited = time.time() - t0
+        self.wait_seconds += waited
+        self.waits.append(waited)
+        self.plan_seconds.append(plan.plan_seconds)
+        return plan
+
+    def close(self) -> None:
+        if self._pool is not None:
+            self._pool.shutdown(wait=False, cancel_futures=True)
+            self._pool = None
+
+
+def _pickle_plans(spec: PlanSpec, iteration: int) -> Dict[int, bytes]:
+    """Worker-process job of shared planning: plan once, hand back one pickled plan per rank."""
+    import pickle
+    return {r: pickle.dumps(p, protocol=pickle.HIGHEST_PROTOCOL) for r, p in plan_iteration_all(spec, iteration).items()}
+
+
+class SharedPlanService:
+    """One planning per batch for all ranks that need it.
+
+    The planner rank (one per node; the engine picks local rank 0) runs the look-ahead pool; a worker
+    plans a batch once for every rank and the planner rank publishes each rank's pickled share in a
+    key-value store (``data.kv_store.KVStore``: TCPStore across processes, a dict in one process)
+    under ``<name>/<iteration>/<rank>``.  Every other rank just ``get``s its key (bounded wait).  The
+    ``readers`` consumers of one rank's plan (the tensor-parallel ranks of one context-parallel rank
+    read the same plan) count their reads; the last one deletes the entry.  Same interface as
+    ``PlanService``.  Role of the planner poller + per-rank KV entries + reader acknowledgement of
+    dcp/data/dataloader.py:99-161, 519-740, 976-1137, without Redis.
+    """
+
+    def __init__(self, spec: PlanSpec, rank: int, store, is_planner: bool, n_workers: int = 4, lookahead: int = 3,
+                 start: int = 0, readers: int = 1, name: str = "dcp_plans", timeout_s: float = 600.0):
+        self.spec, self.rank, self.store, self.is_planner = spec, rank, store, is_planner
+        self.lookahead, self.readers, self.name, self.timeout_s = max(1, lookahead), max(1, readers), name, timeout_s
+        self._pool = None
+        if is_planner:
+            self._pool = cf.ProcessPoolExecutor(max_workers=max(1, n_workers), mp_context=mp.get_context("spawn"),
+                                                initializer=_worker_init)
+        self._pending: Dict[int, "cf.Future"] = {}
+        self._next_submit = start
+        self.wait_seconds = 0.0
+        self.waits: List[float] = []
+        self.plan_seconds: List[float] = []
+        self.n_published = 0
+
+    def _key(self, iteration: int, rank: int) -> str:
+        return f"{self.name}/{iteration}/{rank}"
+
+    def _publish(self, iteration: int, plans: Dict[int, bytes]) -> bytes:
+        mine = None
+        for r, blob in plans.items():
+            if r == self.rank and self.readers == 1:
+                mine = blob             # the planner's own share needs no round trip
+                continue
+            self.store.set(self._key(iteration, r), blob)
+            if r == self.rank:
+                mine = blob
+        self.n_published += 1
+        return mine
+
+    def _publish_finished(self, upto_excl: int) -> None:
+        """Publish iterations whose planning finished while the GPU was busy, so peers never wait for
+        the planner rank to come around."""
+        for i in sorted(k for k, f in self._pending.items() if k != upto_excl and f.done()):
+            self._done[i] = self._publish(i, self._pending.pop(i).result())
+
+    def get(self, iteration: int) -> RankPlan:
+        import pickle
+        t0 = time.time()
+        if self.is_planner:
+            if not hasattr(self, "_done"):
+                self._done: Dict[int, bytes] = {}
+            while self._next_submit <= iteration + self.lookahead:
+                self._pending[self._next_submit] = self._pool.submit(_pickle_plans, self.spec, self._next_submit)
+                self._next_submit += 1
+            self._publish_finished(-1)
+            if iteration in self._pending:
+                self._done[iteration] = self._publish(iteration, self._pending.pop(iteration).result())
+            blob = self._done.pop(iteration)
+        else:
+            blob = self.store.get(self._key(iteration, self.rank), self.timeout_s)
+        if not (self.is_planner and self.readers == 1):
+            # reader acknowledgement: the last of the `readers` consumers removes the entry
+            key = self._key(iteration, self.rank)
+            if self.store.add(key + "/reads", 1) >= self.readers:
+                self.store.delete(key)
+                self.store.delete(key + "/reads")
+        plan = pickle.loads(blob)
         waited = time.time() - t0
         self.wait_seconds += waited
         self.waits.append(waited)

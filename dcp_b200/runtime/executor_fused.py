@@ -61,6 +61,10 @@ class FusedAttentionExecutor:
         # time_calls: one CUDA-event pair around every forward() / backward() call (read with call_times())
         self.time_calls = False
         self._call_events = []
+        # host_pin: optional callable (CPU tensor -> pinned CPU tensor) used for every table upload, so
+        # the copies are truly asynchronous; the engine passes its pinned host arena's `pin`
+        self.host_pin = None
+        self._host_keep = []
 
     def _allocate(self, rows) -> None:
         """(Re)create the symmetric arenas for (q rows, kv rows, partial rows).  Collective: every
@@ -97,17 +101,33 @@ class FusedAttentionExecutor:
             # grow with headroom; all ranks see the same need_all, so all of them get here together
             self._allocate(tuple(max(int(n * 1.25), c) for n, c in zip(need, self.cap)))
         dev = self.device
-        up = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(dev, non_blocking=True)
+        keep = []          # pinned staging copies stay alive until the next prepare (the copies are asynchronous)
+
+        def up(a):
+            t = a if isinstance(a, torch.Tensor) else torch.from_numpy(np.ascontiguousarray(a))
+            if self.host_pin is not None and t.numel():
+                t = self.host_pin(t)
+                keep.append(t)
+            return t.to(dev, non_blocking=True)
+
+        def up_tabs(tabs):
+            if tabs is None:
+                return None
+            import dataclasses
+            return dataclasses.replace(tabs, **{f.name: up(getattr(tabs, f.name)) for f in dataclasses.fields(tabs)
+                                                if isinstance(getattr(tabs, f.name), torch.Tensor)})
+
         self.program = program
         # copy jobs per stage: Q + KV rows (forward, and backward when the staging rows were
         # overwritten since), dO + statistics (backward)
         self.jobs_qkv = [up(x) for x in program.jobs_qkv]
         self.jobs_grad = [up(x) for x in program.jobs_grad]
         self.jobs_all = [up(np.concatenate([a, b])) for a, b in zip(program.jobs_qkv, program.jobs_grad)]
-        self.fwd_tabs = [t.to(dev) if t is not None else None for t in program.fwd]
-        self.bwd_tabs = [t.to(dev) if t is not None else None for t in program.bwd]
+        self.fwd_tabs = [up_tabs(t) for t in program.fwd]
+        self.bwd_tabs = [up_tabs(t) for t in program.bwd]
         self.merge_ops, self.merge_src = up(program.merge_ops), up(program.merge_src)
         self.dq_push, self.dkv_push = up(program.dq_push), up(program.dkv_push)
+        self._host_keep = keep
         self._staging_valid = False
 
     # ---- views the model writes into / reads from

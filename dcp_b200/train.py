@@ -56,6 +56,10 @@ class EngineConfig:
     plan_cache_dir: Optional[str] = None     # reuse plans by batch signature (saved next to checkpoints on resume)
     tp_size: int = 1                # tensor-parallel ranks per model replica (adjacent ranks)
     overlap_grad_reduce: bool = True   # reduce each layer's gradient bucket during the backward pass
+    # plan every batch once (on global rank 0, in its worker pool) and hand each rank its share through a
+    # TCP key-value store instead of planning on every rank; None = on whenever there are several ranks
+    shared_planning: Optional[bool] = None
+    host_arena_mb: int = 256           # pinned host arena the per-step inputs and kernel tables are staged in
 
 
 def parallel_layout(world: int, tp: int = 1, dcp_size: int = 0) -> dict:
@@ -135,11 +139,38 @@ class TrainEngine:
                              inter_node_comp_imbalance_factor=cfg.inter_node_comp_imbalance_factor,
                              use_block_size_heuristic=cfg.use_block_size_heuristic, cost_model=cfg.cost_model,
                              cache_dir=cfg.plan_cache_dir)
-        self.plans = PlanService(self.spec, self.cp_index, cfg.planner_workers, cfg.lookahead)
+        from .memory.host_caching_allocator import HostCachingAllocator
+        self.host_arena = HostCachingAllocator(cfg.host_arena_mb << 20)
+        self.executor.host_pin = self.host_arena.pin
+        self._staged_host = []
+        self._kv, self._kv_server, self._plan_generation = None, None, 0
+        shared = cfg.shared_planning if cfg.shared_planning is not None else self.world > 1
+        if shared and self.world > 1:
+            from .data.kv_store import KVServer, KVStore
+            host = os.environ.get("DCP_KV_HOST", os.environ.get("MASTER_ADDR", "127.0.0.1"))
+            port = int(os.environ.get("DCP_KV_PORT", int(os.environ.get("MASTER_PORT", "29500")) + 29))
+            if self.rank == 0:
+                self._kv_server = KVServer(host, port)
+            dist.barrier(group=world_group)
+            self._kv = KVStore(host, port, timeout_s=600.0)
+        self.plans = self._make_plan_service(0)
+        self.samples_consumed = 0       # dataset samples trained on (checkpointed for the batch sampler)
         self.iteration = 0
         self.last_global_tokens = 0
         self.h2d_bytes = 0
         self.d2h_bytes = 0
+
+    def _make_plan_service(self, start: int):
+        """Look-ahead planner starting at iteration ``start``: shared (rank 0 plans once per batch,
+        everybody reads its share from the key-value store) or per rank."""
+        cfg = self.cfg
+        if self._kv is None:
+            return PlanService(self.spec, self.cp_index, cfg.planner_workers, cfg.lookahead, start=start)
+        from .data.plan_service import SharedPlanService
+        self._plan_generation += 1
+        return SharedPlanService(self.spec, self.cp_index, self._kv, self.rank == 0, 2 * cfg.planner_workers,
+                                 cfg.lookahead, start=start, readers=self.tp_size,
+                                 name=f"dcp_plans_g{self._plan_generation}")
 
     def _plan_activations(self, tokens_per_rank: int):
         """Choose how much each layer keeps for its backward (see LlamaModel.plan_activation_levels)."""
@@ -166,7 +197,9 @@ class TrainEngine:
     def stage_inputs(self, plan: RankPlan):
         """Pinned host -> device copies of this iteration's inputs and kernel tables."""
         dev = self.device
-        host = [plan.tokens.pin_memory(), plan.labels.pin_memory(), plan.positions.pin_memory()]
+        # staged in the pinned arena (no cudaHostAlloc per step); kept alive until the next step's staging
+        host = [self.host_arena.pin(t) for t in (plan.tokens, plan.labels, plan.positions)]
+        self._staged_host = host
         toks, labels, pos = (t.to(dev, non_blocking=True) for t in host)
         self.executor.prepare(plan.program)
         n = sum(t.numel() * t.element_size() for t in host)
@@ -187,11 +220,19 @@ class TrainEngine:
         self.optimizer.step(1.0)
         return loss.detach()
 
-    def train_step(self, plan: Optional[RankPlan] = None) -> float:
-        """Public API: plan (or fetch) the iteration, copy its inputs in, step, read the loss back."""
+    def train_step(self, plan=None) -> float:
+        """Public API: plan (or fetch) the iteration, copy its inputs in, step, read the loss back.
+        ``plan``: None (next synthetic batch from the plan service), a ``RankPlan``, or what
+        ``DCPDataLoader`` yields ((local_batch, fw_plan, bw_plan, fw_workload, bw_workload, spec))."""
         if plan is None:
             plan = self.plans.get(self.iteration)
+        elif isinstance(plan, tuple):
+            lb = plan[0]
+            self.samples_consumed += len(lb["seqlens"])
+            plan = RankPlan(self.iteration, lb["program"], lb["tokens"][0], lb["labels"][0], lb["position_ids"][0],
+                            int(lb["n_global_tokens"]), int(lb["tokens"].numel()), list(lb["seqlens"]), 0.0)
         self.last_global_tokens = plan.n_global_tokens
+        self.last_seqlens = list(plan.seqlens)
         toks, labels, pos = self.stage_inputs(plan)
         loss = self.run_step(toks, labels, pos, plan.n_global_tokens)
         if self.n_cp_ranks > 1:
@@ -216,8 +257,7 @@ class TrainEngine:
         self.plans.close()
         self.spec = dataclasses.replace(self.spec, tokens_per_step=tokens_per_step,
                                         length_dist=length_dist or self.spec.length_dist, mask=mask or self.spec.mask)
-        self.plans = PlanService(self.spec, self.cp_index, self.cfg.planner_workers, self.cfg.lookahead,
-                                 start=self.iteration)
+        self.plans = self._make_plan_service(self.iteration)
 
     def close(self) -> None:
         self.plans.close()
@@ -228,7 +268,7 @@ class TrainEngine:
         path = os.path.join(directory, f"rank{self.rank:03d}.pt")
         state = {"iteration": self.iteration, "optimizer": self.optimizer.state_dict(),
                  "model_cfg": self.cfg.model.__dict__, "world": self.world, "tp_size": self.tp_size,
-                 "seed": self.cfg.seed,
+                 "seed": self.cfg.seed, "samples_consumed": self.samples_consumed,
                  "plan_spec": {k: v for k, v in vars(self.spec).items() if k != "length_dist"},
                  "length_dist": vars(self.spec.length_dist),
                  "rng": torch.get_rng_state(), "cuda_rng": torch.cuda.get_rng_state(self.device)}
@@ -244,6 +284,7 @@ class TrainEngine:
             "resume needs the world size and tensor-parallel size the checkpoint was written with"
         self.optimizer.load_state_dict(state["optimizer"])
         self.iteration = int(state["iteration"])
+        self.samples_consumed = int(state.get("samples_consumed", 0))
         torch.set_rng_state(state["rng"].cpu())
         torch.cuda.set_rng_state(state["cuda_rng"].cpu(), self.device)
         # every rank's bf16 parameters are rebuilt from the sharded fp32 master weights: each rank
@@ -252,7 +293,35 @@ class TrainEngine:
         torch.cuda.synchronize(self.device)
         self.check_status()
         self.plans.close()
-        self.plans = PlanService(self.spec, self.cp_index, self.cfg.planner_workers, self.cfg.lookahead, start=self.iteration)
+        self.plans = self._make_plan_service(self.iteration)
+
+
+def dataset_batches(eng: "TrainEngine", n_samples: int, dist_: synth.LengthDist, seed: int = 24):
+    """Generator of ``DCPDataLoader`` items for ``eng`` over a seeded synthetic corpus: the dataset ->
+    token-budget batch sampler -> planning dataloader route.  Every rank iterates the same sampler
+    (same seed), so all ranks see the same batches; the sampler resumes after the samples the engine
+    has already trained on (``eng.samples_consumed``, part of the checkpoint) and starts a new epoch
+    when the corpus is exhausted."""
+    from .core.common import ModelSpec, get_default_execution_context
+    from .data.dataloader import DCPDataLoader, TrainingSpec
+    from .data.datasets import OrderedBatchSampler, SyntheticLengthDataset
+    m, spec = eng.local_model, eng.spec
+    ds = SyntheticLengthDataset(n_samples, dist_, vocab=m.vocab, seed=seed)
+    sampler = OrderedBatchSampler(ds, spec.tokens_per_step, shuffle=True, seed=seed)
+    per_epoch = sum(len(b) for b in sampler._batches())
+    sampler.epoch, sampler.consumed_samples = divmod(eng.samples_consumed, max(per_epoch, 1)) if per_epoch else (0, 0)
+    ts = TrainingSpec(get_default_execution_context(spec.dcp_size, 1), ModelSpec(m.head_dim, m.n_heads, m.n_kv_heads),
+                      mask_type=spec.mask, block_size=spec.block_size, head_block_size=spec.head_block_size or m.n_heads,
+                      dcp_size=spec.dcp_size, use_block_size_heuristic=0)
+    loader = DCPDataLoader(ts, ds, dcp_rank=eng.cp_index, batch_sampler=sampler, world=spec.world,
+                           num_preprocess_workers=eng.cfg.planner_workers, prefetch_factor=eng.cfg.lookahead,
+                           build_instruction_plans=False)
+    try:
+        while True:
+            for item in loader:
+                yield item
+    finally:
+        loader.close()
 
 
 def init_distributed():
@@ -312,6 +381,11 @@ def main(argv=None):
     ap.add_argument("--save", default=None)
     ap.add_argument("--load", default=None)
     ap.add_argument("--activation-budget-gb", type=float, default=None)
+    ap.add_argument("--dataset", default="none", choices=["none", "synthetic"],
+                    help="none: batches are synthesised inside the plan service; synthetic: a Dataset of seeded "
+                         "variable-length samples goes through OrderedBatchSampler and DCPDataLoader, the route a "
+                         "tokenised corpus takes (benchmark/mlm/pretrain_gpt.py:853-877 in the reference)")
+    ap.add_argument("--dataset-samples", type=int, default=4096)
     add_dcp_args(ap)
     args = ap.parse_args(argv)
     rank, world, local, group = init_distributed()
@@ -333,9 +407,12 @@ def main(argv=None):
     eng = TrainEngine(cfg, torch.device("cuda", local), group)
     if args.load:
         eng.load_checkpoint(args.load)
+    batches = None
+    if args.dataset != "none":
+        batches = iter(dataset_batches(eng, args.dataset_samples, dists[args.length_dist]))
     t_last = time.time()
     for it in range(eng.iteration, eng.iteration + args.iters):
-        loss = eng.train_step()
+        loss = eng.train_step(next(batches) if batches is not None else None)
         if rank == 0 and (it + 1) % args.log_interval == 0:
             now = time.time()
             ms = (now - t_last) * 1000 / args.log_interval

@@ -316,3 +316,41 @@ def test_optimizer_shard_layout_covers_every_bucket_for_any_world_size():
             for s in shards:
                 assert s.state_off == acc
                 acc += s.length
+
+
+def test_shared_planning_gives_every_rank_the_plan_it_would_compute_itself():
+    """One planner (rank 0) plans every batch once in its worker pool and publishes per-rank shares in
+    a key-value store; the other ranks only read.  Every rank must receive exactly the plan it would
+    have computed alone, entries must be deleted after the last reader (two readers per rank here, as
+    with tensor parallelism), and nothing may be planned twice."""
+    import threading
+    import torch
+    from dcp_b200.data import synth
+    from dcp_b200.data.kv_store import KVStore
+    from dcp_b200.data.plan_service import PlanSpec, SharedPlanService, plan_iteration
+    spec = PlanSpec(4, 2, 8192, 8, 2, 128, 512, 0, "causal", synth.LengthDist("lognormal", 1024.0, 0.7, 128, 4096))
+    store = KVStore()
+    readers = 2
+    svcs = {(r, t): SharedPlanService(spec, r, store, (r, t) == (0, 0), n_workers=2, lookahead=2, readers=readers,
+                                      timeout_s=120.0) for r in range(4) for t in range(readers)}
+    got, errs = {}, []
+
+    def run(key):
+        try:
+            got[key] = [svcs[key].get(i) for i in range(3)]
+        except Exception as e:     # surfaced below; a thread must not die silently
+            errs.append((key, repr(e)))
+
+    threads = [threading.Thread(target=run, args=(k,)) for k in svcs]
+    [t.start() for t in threads]
+    [t.join(300) for t in threads]
+    svcs[(0, 0)].close()
+    assert not errs, errs
+    assert svcs[(0, 0)].n_published == 3
+    for (r, t), plans in got.items():
+        for i, p in enumerate(plans):
+            ref = plan_iteration(spec, i, r)
+            assert torch.equal(ref.tokens, p.tokens) and torch.equal(ref.labels, p.labels)
+            assert (ref.program.merge_ops == p.program.merge_ops).all() and ref.program.q_rows == p.program.q_rows
+            assert all(torch.equal(a.tiles, b.tiles) for a, b in zip(ref.program.fwd, p.program.fwd) if a is not None)
+    assert not [k for k in store._local if not k.endswith("/reads")], "plans left in the store after the last reader"
