@@ -353,4 +353,6 @@ def test_shared_planning_gives_every_rank_the_plan_it_would_compute_itself():
             assert torch.equal(ref.tokens, p.tokens) and torch.equal(ref.labels, p.labels)
             assert (ref.program.merge_ops == p.program.merge_ops).all() and ref.program.q_rows == p.program.q_rows
             assert all(torch.equal(a.tiles, b.tiles) for a, b in zip(ref.program.fwd, p.program.fwd) if a is not None)
-    assert not [k for k in store._local if not k.endswith("/reads")], "plans left in the store after the last reader"
+    # iterations planned ahead of the last get() may still sit in the store; the consumed ones must be gone
+    left = [k for k in store._local if int(k.split("/")[1]) < 3]
+    assert not left, f"plans left in the store after the last reader: {left}"
