@@ -4,6 +4,7 @@ larger than L2 or an L2 flush between iterations), with achieved fractions of th
     python -m dcp_b200.bench.kernel_bench attn_fwd --tokens 8192 --kv 8192 --hq 32 --hkv 8 --mask causal
     python -m dcp_b200.bench.kernel_bench attn_bwd ...
     python -m dcp_b200.bench.kernel_bench ops
+    python -m torch.distributed.run --nproc-per-node 2 ... -m dcp_b200.bench.kernel_bench nvlink
 
 Counterpart of the reference's benchmark/ops/{benchmark_fused_memcpy,benchmark_fused_update,
 benchmark_sdpa}.py.
@@ -169,13 +170,88 @@ def bench_ops(args):
     kva = torch.empty(T, 2, 8, 128, device=dev, dtype=torch.bfloat16)
     report("qkv_rope_split", time_fn(lambda: model_ops.qkv_rope_split(qkv, cos, sin, qa, kva, 32, 8), args.iters, 3, flush),
            2 * qkv.numel() * 2)
+    dq = torch.randn(T, 32, 128, device=dev)
+    dkv = torch.randn(T, 2, 8, 128, device=dev)
+    report("qkv_rope_pack_bwd", time_fn(lambda: model_ops.qkv_rope_pack_bwd(dq, dkv, cos, sin, T, 32, 8), args.iters, 3, flush),
+           qkv.numel() * (4 + 2))
+    # merge of 3 partial (out, lse) per token: reads 3 partial rows, writes one
+    n_src, hq = 3, 32
+    tm = min(T, 8192)
+    part_out = torch.randn(n_src * tm, hq, 128, device=dev).bfloat16()
+    part_lse = torch.randn(hq, n_src * tm, device=dev)
+    mo, ml = torch.empty(tm, hq, 128, device=dev, dtype=torch.bfloat16), torch.empty(hq, tm, device=dev)
+    ops_t = torch.tensor([[b0, min(2048, tm - b0), 3 * i, 3] for i, b0 in enumerate(range(0, tm, 2048))], dtype=torch.int32, device=dev)
+    src_t = torch.tensor([s * tm + b0 for b0 in range(0, tm, 2048) for s in range(n_src)], dtype=torch.int32, device=dev)
+    report("merge_out_lse", time_fn(lambda: block_ops.merge_out_lse(ops_t, src_t, part_out, part_lse, mo, ml), args.iters, 3, flush),
+           (n_src + 1) * tm * hq * 128 * 2 + (n_src + 1) * tm * hq * 4)
+    # single-rank fused gradient read + AdamW + parameter store: bf16 grad in, fp32 master / m / v in and out, bf16 param out
+    from ..parallel.dist_optimizer import FlatBuffers, ShardedAdamW
+    n = 256 << 20
+    bufs = FlatBuffers(n, dev)
+    opt = ShardedAdamW(bufs, clip_grad=None)
+    bufs.grads.normal_()
+    report("fused_rs_adamw_ag", time_fn(lambda: opt.step(1.0), args.iters, 3, flush), n * (2 + 12 + 12 + 2))
     for r in res:
-        print(json.dumps(r))
+        if args.only is None or r["op"] == args.only:
+            print(json.dumps(r))
+
+
+def bench_nvlink(args):
+    """Two or more ranks (torch.distributed.run): bandwidth of the in-kernel communication primitives
+    over NVLink, CUDA-event timed, max over ranks: peer -> local copy jobs (the operand fetch),
+    fp32 push-add into a peer accumulator (the gradient return), and the flag barrier's latency."""
+    import torch.distributed as dist
+    from ..planner.lowering import KIND_Q, row_copy_jobs
+    from ..runtime.symm import SymmetricArena
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
+    dev = torch.device("cuda", torch.cuda.current_device())
+    dist.init_process_group("nccl", device_id=dev)
+    rows, hq = 65536, 32                                    # 512 MB of bf16 rows, 1 GB of fp32 rows
+    arena = SymmetricArena({"q": ((2 * rows, hq, 128), torch.bfloat16), "kv": ((8, 2, 8, 128), torch.bfloat16),
+                            "dout": ((8, hq, 128), torch.bfloat16), "lse": ((hq, 2 * rows), torch.float32),
+                            "delta": ((hq, 8), torch.float32), "acc": ((rows, hq, 128), torch.float32)},
+                           dev, dist.group.WORLD)
+    arena.view("q").normal_()
+    peer = (rank + 1) % world
+    pulls = np.asarray([(peer, b0, rows + b0, 2048) for b0 in range(0, rows, 2048)], dtype=np.int32)
+    jobs = torch.from_numpy(row_copy_jobs(pulls, KIND_Q, hq * 16)).to(dev)
+    ctx = A.CopyContext(arena.peer_ptrs, rank, 2 * rows)
+    src = torch.randn(rows // 2, hq, 128, device=dev)
+    push = torch.tensor([(peer, b0, b0, 2048) for b0 in range(0, rows // 2, 2048)], dtype=torch.int32, device=dev)
+
+    def timed(fn, iters=10):
+        arena.barrier(); fn(); arena.barrier()
+        torch.cuda.synchronize(); dist.barrier()
+        e0, e1 = torch.cuda.Event(True), torch.cuda.Event(True)
+        e0.record()
+        for _ in range(iters):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) / iters], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t)
+
+    ms_copy = timed(lambda: A.copy_jobs(jobs, ctx))
+    ms_push = timed(lambda: block_ops.push_add_rows(push, src, arena.peer_ptrs("acc"), hq * 128))
+    ms_bar = timed(arena.barrier, 50)
+    arena.check_status()
+    if rank == 0:
+        nb_c, nb_p = rows * hq * 128 * 2, (rows // 2) * hq * 128 * 4
+        print(json.dumps({"op": "copy_jobs (peer -> local, 64 KB jobs)", "n_gpus": world, "MB": nb_c >> 20, "ms": round(ms_copy, 3),
+                          "GB/s per GPU": round(nb_c / ms_copy / 1e6, 1)}))
+        print(json.dumps({"op": "push_add_rows (local fp32 -> red.add on peer)", "n_gpus": world, "MB": nb_p >> 20,
+                          "ms": round(ms_push, 3), "GB/s per GPU": round(nb_p / ms_push / 1e6, 1)}))
+        print(json.dumps({"op": "signal_barrier", "n_gpus": world, "us": round(ms_bar * 1e3, 1)}))
+    dist.barrier()
+    dist.destroy_process_group()
 
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("kind", choices=["attn_fwd", "attn_bwd", "ops"])
+    ap.add_argument("kind", choices=["attn_fwd", "attn_bwd", "ops", "nvlink"])
+    ap.add_argument("--only", default=None, help="ops: print (and, under a profiler, look at) just this op")
     ap.add_argument("--tokens", type=int, default=8192)
     ap.add_argument("--kv", type=int, default=8192)
     ap.add_argument("--hq", type=int, default=32)
@@ -187,7 +263,9 @@ def main():
     ap.add_argument("--timeline", action="store_true", help="print per-phase cycle counts of one backward CTA")
     ap.add_argument("--skip-dq", action="store_true", help="backward without the dQ drain (upper bound probe)")
     args = ap.parse_args()
-    if args.kind == "ops":
+    if args.kind == "nvlink":
+        bench_nvlink(args)
+    elif args.kind == "ops":
         bench_ops(args)
     else:
         bench_attention(args.kind, args)

@@ -71,43 +71,53 @@ struct MergeOp {
   int n_src;
 };
 
-// one warp per (token, head); lane covers 4 of the 128 channels
+// sixteen lanes per (token, head), each covering 8 of the 128 channels with 16-byte accesses; the
+// loads of all sources of an item are independent, so several rows are in flight per thread
 __global__ void merge_out_lse_kernel(const MergeOp* __restrict__ ops, const int* __restrict__ src_rows,
                                      const __nv_bfloat16* __restrict__ part_out, const float* __restrict__ part_lse,
                                      int part_stride, __nv_bfloat16* __restrict__ out, float* __restrict__ lse,
                                      int out_stride, int hq) {
   const MergeOp op = ops[blockIdx.y];
-  const int lane = threadIdx.x & 31;
-  const int warps_per_block = blockDim.x >> 5;
+  const int sub = threadIdx.x & 15;
+  const int per_block = blockDim.x >> 4;
   const int total = op.n_tok * hq;
-  for (int item = blockIdx.x * warps_per_block + (threadIdx.x >> 5); item < total; item += gridDim.x * warps_per_block) {
+  const int* rows = src_rows + op.src_off;
+  for (int item = blockIdx.x * per_block + (threadIdx.x >> 4); item < total; item += gridDim.x * per_block) {
+    // heads fastest: the 16-lane groups of a block read neighbouring heads of one partial row
     const int t = item / hq, h = item % hq;
     float m = -INFINITY;
+#pragma unroll 4
     for (int s = 0; s < op.n_src; ++s) {
-      const float l = part_lse[size_t(h) * part_stride + src_rows[op.src_off + s] + t];
+      const float l = part_lse[size_t(h) * part_stride + rows[s] + t];
       if (l == l && l != INFINITY) m = fmaxf(m, l);  // skip NaN / +inf partials
     }
-    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
     float wsum = 0.f;
     if (m != -INFINITY) {
+#pragma unroll 4
       for (int s = 0; s < op.n_src; ++s) {
-        const int row = src_rows[op.src_off + s] + t;
+        const int row = rows[s] + t;
         const float l = part_lse[size_t(h) * part_stride + row];
+        const uint4 raw = *reinterpret_cast<const uint4*>(part_out + (size_t(row) * hq + h) * kHeadDim + sub * 8);
         if (!(l == l) || l == INFINITY || l == -INFINITY) continue;
         const float w = __expf(l - m);
         wsum += w;
-        const uint2 raw = *reinterpret_cast<const uint2*>(part_out + (size_t(row) * hq + h) * kHeadDim + lane * 4);
         const __nv_bfloat162* v = reinterpret_cast<const __nv_bfloat162*>(&raw);
-        const float2 a = __bfloat1622float2(v[0]), b = __bfloat1622float2(v[1]);
-        acc[0] += w * a.x; acc[1] += w * a.y; acc[2] += w * b.x; acc[3] += w * b.y;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 a = __bfloat1622float2(v[j]);
+          acc[2 * j] += w * a.x; acc[2 * j + 1] += w * a.y;
+        }
       }
     }
     const float inv = wsum > 0.f ? 1.f / wsum : 0.f;
-    uint2 packed;
+    uint4 packed;
     packed.x = pack_bf16x2(acc[0] * inv, acc[1] * inv);
     packed.y = pack_bf16x2(acc[2] * inv, acc[3] * inv);
-    *reinterpret_cast<uint2*>(out + (size_t(op.dst_row + t) * hq + h) * kHeadDim + lane * 4) = packed;
-    if (lane == 0) lse[size_t(h) * out_stride + op.dst_row + t] = wsum > 0.f ? m + __logf(wsum) : -INFINITY;
+    packed.z = pack_bf16x2(acc[4] * inv, acc[5] * inv);
+    packed.w = pack_bf16x2(acc[6] * inv, acc[7] * inv);
+    *reinterpret_cast<uint4*>(out + (size_t(op.dst_row + t) * hq + h) * kHeadDim + sub * 8) = packed;
+    if (sub == 0) lse[size_t(h) * out_stride + op.dst_row + t] = wsum > 0.f ? m + __logf(wsum) : -INFINITY;
   }
 }
 
@@ -214,7 +224,9 @@ extern "C" int dcpk_merge_out_lse(const void* ops, int n_ops, const void* src_ro
                                   const float* part_lse, int part_stride, void* out, float* lse, int out_stride,
                                   int hq, void* stream) {
   if (n_ops <= 0) return 0;
-  dim3 grid(32, n_ops);
+  // enough CTAs to fill the GPU whatever the number of ops (an op is one Q block, up to block_size tokens)
+  const int per_op = n_ops >= 592 ? 1 : (592 + n_ops - 1) / n_ops;
+  dim3 grid(per_op, n_ops);
   merge_out_lse_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const MergeOp*>(ops), static_cast<const int*>(src_rows),
       static_cast<const __nv_bfloat16*>(part_out), part_lse, part_stride, static_cast<__nv_bfloat16*>(out), lse,

@@ -141,70 +141,94 @@ __global__ void __launch_bounds__(128) rmsnorm_bwd_kernel(const __nv_bfloat16* _
       dxr[threadIdx.x + i * 128] = pack8(g[i]);
     }
   }
+  // one vector reduction per four channels (a quarter of the scalar atomics, which bound this kernel)
 #pragma unroll
   for (int i = 0; i < kVecs; ++i)
 #pragma unroll
-    for (int j = 0; j < 8; ++j) atomicAdd(dw + (threadIdx.x + i * 128) * 8 + j, dwv[i][j]);
+    for (int j = 0; j < 8; j += 4)
+      asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dw + (threadIdx.x + i * 128) * 8 + j),
+                   "f"(dwv[i][j]), "f"(dwv[i][j + 1]), "f"(dwv[i][j + 2]), "f"(dwv[i][j + 3])
+                   : "memory");
 }
 
 // ------------------------------------------------------------------ QKV split + rotary
 // qkv: [T, (hq + 2*hkv) * 128] packed as q heads | k heads | v heads.  cos/sin: [T, 64].
 // rotate-half convention: (x1, x2) -> (x1 cos - x2 sin, x2 cos + x1 sin), x1 = x[:64], x2 = x[64:].
-// one warp per (token, head); lane owns channels 2*lane, 2*lane+1 of each half.
+// eight lanes per (token, head): lane s of the group owns channels 8s .. 8s+7 of each half, so every
+// global access is a 16-byte vector (a warp moves four heads).
 __global__ void qkv_rope_split_fwd_kernel(const __nv_bfloat16* __restrict__ qkv, const float* __restrict__ cs,
                                           const float* __restrict__ sn, __nv_bfloat16* __restrict__ q_out,
                                           __nv_bfloat16* __restrict__ kv_out, int n_tok, int hq, int hkv,
                                           int q_row0, int kv_row0) {
   const int heads = hq + 2 * hkv;
-  const long gw = (long(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
-  const int lane = threadIdx.x & 31;
-  if (gw >= long(n_tok) * heads) return;
-  const int t = int(gw / heads), h = int(gw % heads);
+  const long item = (long(blockIdx.x) * blockDim.x + threadIdx.x) >> 3;
+  const int sub = threadIdx.x & 7;
+  if (item >= long(n_tok) * heads) return;
+  const int t = int(item / heads), h = int(item % heads);
   const __nv_bfloat16* src = qkv + (size_t(t) * heads + h) * 128;
   __nv_bfloat16* dst;
   if (h < hq) dst = q_out + (size_t(q_row0 + t) * hq + h) * 128;
   else if (h < hq + hkv) dst = kv_out + ((size_t(kv_row0 + t) * 2 + 0) * hkv + (h - hq)) * 128;
   else dst = kv_out + ((size_t(kv_row0 + t) * 2 + 1) * hkv + (h - hq - hkv)) * 128;
-  const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(src + 2 * lane);
-  const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(src + 64 + 2 * lane);
+  const uint4 a = *reinterpret_cast<const uint4*>(src + 8 * sub);
+  const uint4 b = *reinterpret_cast<const uint4*>(src + 64 + 8 * sub);
   if (h < hq + hkv) {
-    const float2 c = *reinterpret_cast<const float2*>(cs + size_t(t) * 64 + 2 * lane);
-    const float2 s = *reinterpret_cast<const float2*>(sn + size_t(t) * 64 + 2 * lane);
-    const float2 x1 = __bfloat1622float2(a), x2 = __bfloat1622float2(b);
-    *reinterpret_cast<__nv_bfloat162*>(dst + 2 * lane) = __floats2bfloat162_rn(x1.x * c.x - x2.x * s.x, x1.y * c.y - x2.y * s.y);
-    *reinterpret_cast<__nv_bfloat162*>(dst + 64 + 2 * lane) = __floats2bfloat162_rn(x2.x * c.x + x1.x * s.x, x2.y * c.y + x1.y * s.y);
+    float x1[8], x2[8], c[8], sv[8], o1[8], o2[8];
+    unpack8(a, x1); unpack8(b, x2);
+    *reinterpret_cast<float4*>(c) = *reinterpret_cast<const float4*>(cs + size_t(t) * 64 + 8 * sub);
+    *reinterpret_cast<float4*>(c + 4) = *reinterpret_cast<const float4*>(cs + size_t(t) * 64 + 8 * sub + 4);
+    *reinterpret_cast<float4*>(sv) = *reinterpret_cast<const float4*>(sn + size_t(t) * 64 + 8 * sub);
+    *reinterpret_cast<float4*>(sv + 4) = *reinterpret_cast<const float4*>(sn + size_t(t) * 64 + 8 * sub + 4);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      o1[j] = x1[j] * c[j] - x2[j] * sv[j];
+      o2[j] = x2[j] * c[j] + x1[j] * sv[j];
+    }
+    *reinterpret_cast<uint4*>(dst + 8 * sub) = pack8(o1);
+    *reinterpret_cast<uint4*>(dst + 64 + 8 * sub) = pack8(o2);
   } else {
-    *reinterpret_cast<__nv_bfloat162*>(dst + 2 * lane) = a;
-    *reinterpret_cast<__nv_bfloat162*>(dst + 64 + 2 * lane) = b;
+    *reinterpret_cast<uint4*>(dst + 8 * sub) = a;
+    *reinterpret_cast<uint4*>(dst + 64 + 8 * sub) = b;
   }
 }
 
 // dq: fp32 [rows, hq, 128], dkv: fp32 [rows, 2, hkv, 128] -> dqkv bf16 [T, (hq+2hkv)*128] with the
-// rotation transposed (sin negated) on the q and k parts.
+// rotation transposed (sin negated) on the q and k parts.  Same eight-lanes-per-head layout.
 __global__ void qkv_rope_pack_bwd_kernel(const float* __restrict__ dq, const float* __restrict__ dkv,
                                          const float* __restrict__ cs, const float* __restrict__ sn,
                                          __nv_bfloat16* __restrict__ dqkv, int n_tok, int hq, int hkv, int q_row0,
                                          int kv_row0) {
   const int heads = hq + 2 * hkv;
-  const long gw = (long(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
-  const int lane = threadIdx.x & 31;
-  if (gw >= long(n_tok) * heads) return;
-  const int t = int(gw / heads), h = int(gw % heads);
+  const long item = (long(blockIdx.x) * blockDim.x + threadIdx.x) >> 3;
+  const int sub = threadIdx.x & 7;
+  if (item >= long(n_tok) * heads) return;
+  const int t = int(item / heads), h = int(item % heads);
   const float* src;
   if (h < hq) src = dq + (size_t(q_row0 + t) * hq + h) * 128;
   else if (h < hq + hkv) src = dkv + ((size_t(kv_row0 + t) * 2 + 0) * hkv + (h - hq)) * 128;
   else src = dkv + ((size_t(kv_row0 + t) * 2 + 1) * hkv + (h - hq - hkv)) * 128;
   __nv_bfloat16* dst = dqkv + (size_t(t) * heads + h) * 128;
-  const float2 g1 = *reinterpret_cast<const float2*>(src + 2 * lane);
-  const float2 g2 = *reinterpret_cast<const float2*>(src + 64 + 2 * lane);
+  float g1[8], g2[8];
+  *reinterpret_cast<float4*>(g1) = *reinterpret_cast<const float4*>(src + 8 * sub);
+  *reinterpret_cast<float4*>(g1 + 4) = *reinterpret_cast<const float4*>(src + 8 * sub + 4);
+  *reinterpret_cast<float4*>(g2) = *reinterpret_cast<const float4*>(src + 64 + 8 * sub);
+  *reinterpret_cast<float4*>(g2 + 4) = *reinterpret_cast<const float4*>(src + 64 + 8 * sub + 4);
   if (h < hq + hkv) {
-    const float2 c = *reinterpret_cast<const float2*>(cs + size_t(t) * 64 + 2 * lane);
-    const float2 s = *reinterpret_cast<const float2*>(sn + size_t(t) * 64 + 2 * lane);
-    *reinterpret_cast<__nv_bfloat162*>(dst + 2 * lane) = __floats2bfloat162_rn(g1.x * c.x + g2.x * s.x, g1.y * c.y + g2.y * s.y);
-    *reinterpret_cast<__nv_bfloat162*>(dst + 64 + 2 * lane) = __floats2bfloat162_rn(g2.x * c.x - g1.x * s.x, g2.y * c.y - g1.y * s.y);
+    float c[8], sv[8], o1[8], o2[8];
+    *reinterpret_cast<float4*>(c) = *reinterpret_cast<const float4*>(cs + size_t(t) * 64 + 8 * sub);
+    *reinterpret_cast<float4*>(c + 4) = *reinterpret_cast<const float4*>(cs + size_t(t) * 64 + 8 * sub + 4);
+    *reinterpret_cast<float4*>(sv) = *reinterpret_cast<const float4*>(sn + size_t(t) * 64 + 8 * sub);
+    *reinterpret_cast<float4*>(sv + 4) = *reinterpret_cast<const float4*>(sn + size_t(t) * 64 + 8 * sub + 4);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      o1[j] = g1[j] * c[j] + g2[j] * sv[j];
+      o2[j] = g2[j] * c[j] - g1[j] * sv[j];
+    }
+    *reinterpret_cast<uint4*>(dst + 8 * sub) = pack8(o1);
+    *reinterpret_cast<uint4*>(dst + 64 + 8 * sub) = pack8(o2);
   } else {
-    *reinterpret_cast<__nv_bfloat162*>(dst + 2 * lane) = __floats2bfloat162_rn(g1.x, g1.y);
-    *reinterpret_cast<__nv_bfloat162*>(dst + 64 + 2 * lane) = __floats2bfloat162_rn(g2.x, g2.y);
+    *reinterpret_cast<uint4*>(dst + 8 * sub) = pack8(g1);
+    *reinterpret_cast<uint4*>(dst + 64 + 8 * sub) = pack8(g2);
   }
 }
 
@@ -333,12 +357,20 @@ extern "C" int dcpk_rmsnorm_bwd(const void* x, const void* w, const void* dy, co
   if (n_rows <= 0) return 0;
   auto X = static_cast<const __nv_bfloat16*>(x); auto W = static_cast<const __nv_bfloat16*>(w);
   auto G = static_cast<const __nv_bfloat16*>(dy); auto DX = static_cast<__nv_bfloat16*>(dx);
-  const int grid = n_rows < 592 ? n_rows : 592;
+  // persistent CTAs: exactly as many as are resident at once (registers decide), so no CTA waits for a
+  // slot while others already finished their share
+  auto launch = [&](auto kernel) {
+    int per_sm = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, 128, 0) != cudaSuccess || per_sm < 1) per_sm = 2;
+    const int cap = 148 * per_sm;
+    const int grid = n_rows < cap ? n_rows : cap;
+    kernel<<<grid, 128, 0, STREAM>>>(X, W, G, rstd, DX, dw, n_rows, hidden);
+  };
   switch (hidden) {
-    case 1024: rmsnorm_bwd_kernel<1><<<grid, 128, 0, STREAM>>>(X, W, G, rstd, DX, dw, n_rows, hidden); break;
-    case 2048: rmsnorm_bwd_kernel<2><<<grid, 128, 0, STREAM>>>(X, W, G, rstd, DX, dw, n_rows, hidden); break;
-    case 4096: rmsnorm_bwd_kernel<4><<<grid, 128, 0, STREAM>>>(X, W, G, rstd, DX, dw, n_rows, hidden); break;
-    case 8192: rmsnorm_bwd_kernel<8><<<grid, 128, 0, STREAM>>>(X, W, G, rstd, DX, dw, n_rows, hidden); break;
+    case 1024: launch(rmsnorm_bwd_kernel<1>); break;
+    case 2048: launch(rmsnorm_bwd_kernel<2>); break;
+    case 4096: launch(rmsnorm_bwd_kernel<4>); break;
+    case 8192: launch(rmsnorm_bwd_kernel<8>); break;
     default: return -3;
   }
   return LAUNCH_OK;
@@ -347,8 +379,8 @@ extern "C" int dcpk_rmsnorm_bwd(const void* x, const void* w, const void* dy, co
 extern "C" int dcpk_qkv_rope_split_fwd(const void* qkv, const float* cs, const float* sn, void* q_out, void* kv_out,
                                        int n_tok, int hq, int hkv, int q_row0, int kv_row0, void* stream) {
   if (n_tok <= 0) return 0;
-  const long warps = long(n_tok) * (hq + 2 * hkv);
-  const long blocks = (warps * 32 + 255) / 256;
+  const long items = long(n_tok) * (hq + 2 * hkv);   // eight threads per (token, head)
+  const long blocks = (items * 8 + 255) / 256;
   qkv_rope_split_fwd_kernel<<<unsigned(blocks), 256, 0, STREAM>>>(
       static_cast<const __nv_bfloat16*>(qkv), cs, sn, static_cast<__nv_bfloat16*>(q_out),
       static_cast<__nv_bfloat16*>(kv_out), n_tok, hq, hkv, q_row0, kv_row0);
@@ -358,8 +390,8 @@ extern "C" int dcpk_qkv_rope_split_fwd(const void* qkv, const float* cs, const f
 extern "C" int dcpk_qkv_rope_pack_bwd(const float* dq, const float* dkv, const float* cs, const float* sn, void* dqkv,
                                       int n_tok, int hq, int hkv, int q_row0, int kv_row0, void* stream) {
   if (n_tok <= 0) return 0;
-  const long warps = long(n_tok) * (hq + 2 * hkv);
-  const long blocks = (warps * 32 + 255) / 256;
+  const long items = long(n_tok) * (hq + 2 * hkv);   // eight threads per (token, head)
+  const long blocks = (items * 8 + 255) / 256;
   qkv_rope_pack_bwd_kernel<<<unsigned(blocks), 256, 0, STREAM>>>(dq, dkv, cs, sn, static_cast<__nv_bfloat16*>(dqkv),
                                                                   n_tok, hq, hkv, q_row0, kv_row0);
   return LAUNCH_OK;

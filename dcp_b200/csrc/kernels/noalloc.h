@@ -15,7 +15,9 @@
 //  * Sizes: hidden must be 1024, 2048, 4096 or 8192 and at most DCPK_NOALLOC_MAX_HIDDEN; anything
 //    else is rejected with return code -3 and a message on stderr.
 //  * First call on a device: looks up the device address of the array (once per device, with that
-//    device current).  Make that first call before starting any stream capture.
+//    device current).  Make that first call before starting any stream capture.  The looked-up
+//    address is cached per device without a lock: host threads that race on the first call all
+//    store the same value, which is harmless.
 //  * The buffer is shared by all calls and keeps the previous call's contents; each call clears
 //    the part it uses on `stream` before accumulating.  Two calls that overlap on the GPU (issued
 //    on different streams without ordering) race on it - serialise them.
