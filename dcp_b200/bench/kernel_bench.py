@@ -128,72 +128,88 @@ def bench_attention(kind, args):
 
 
 def bench_ops(args):
+    """HBM-bound kernels: milliseconds, GB/s of algorithmic bytes and the fraction of the measured copy
+    bandwidth.  ``--only NAME`` builds and runs just that op (a small working set for a profiler)."""
     dev = torch.device("cuda")
     hbm, tf, src = measured_peaks()
     T, H, F, V = args.tokens, 4096, 14336, 128256
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
-    res = []
-
-    def report(name, ms, nbytes):
-        gbs = nbytes / ms / 1e6
-        res.append({"op": name, "ms": round(ms, 4), "GB/s": round(gbs, 1), f"frac_of_{src}_hbm": round(gbs / hbm, 3)})
-
-    x = torch.randn(T, H, device=dev).bfloat16()
-    w = torch.ones(H, device=dev).bfloat16()
-    y, rstd = torch.empty_like(x), torch.empty(T, device=dev)
     from ..ops import _lib
     import ctypes
     lib = _lib.load()
-    report("rmsnorm_fwd", time_fn(lambda: lib.dcpk_rmsnorm_fwd(_lib.ptr(x), _lib.ptr(w), _lib.ptr(y), _lib.ptr(rstd),
-                                                              ctypes.c_int(T), ctypes.c_int(H), ctypes.c_float(1e-5),
-                                                              _lib.stream_handle()), args.iters, 3, flush), 2 * x.numel() * 2)
-    dx, dw = torch.empty_like(x), torch.zeros(H, device=dev)
-    report("rmsnorm_bwd", time_fn(lambda: lib.dcpk_rmsnorm_bwd(_lib.ptr(x), _lib.ptr(w), _lib.ptr(y), _lib.ptr(rstd),
-                                                              _lib.ptr(dx), _lib.ptr(dw), ctypes.c_int(T), ctypes.c_int(H),
-                                                              _lib.stream_handle()), args.iters, 3, flush), 3 * x.numel() * 2)
-    gu = torch.randn(T, 2 * F, device=dev).bfloat16()
-    yo = torch.empty(T, F, device=dev, dtype=torch.bfloat16)
-    report("swiglu_fwd", time_fn(lambda: lib.dcpk_swiglu_fwd(_lib.ptr(gu), _lib.ptr(yo), ctypes.c_long(T), ctypes.c_int(F),
-                                                            _lib.stream_handle()), args.iters, 3, flush), 3 * T * F * 2)
-    dgu = torch.empty_like(gu)
-    report("swiglu_bwd", time_fn(lambda: lib.dcpk_swiglu_bwd(_lib.ptr(gu), _lib.ptr(yo), _lib.ptr(dgu), ctypes.c_long(T),
-                                                            ctypes.c_int(F), _lib.stream_handle()), args.iters, 3, flush), 5 * T * F * 2)
-    tc = min(T, 4096)
-    logits = torch.randn(tc, V, device=dev).bfloat16()
-    labels = torch.randint(0, V, (tc,), device=dev)
-    report("cross_entropy_fwd_bwd", time_fn(lambda: model_ops.cross_entropy_inplace(logits, labels, 1.0), args.iters, 3, flush),
-           3 * tc * V * 2)
-    qkv = torch.randn(T, 48 * 128, device=dev).bfloat16()
-    pos = torch.arange(T, device=dev)
-    cos, sin = model_ops.rope_tables(pos)
-    qa = torch.empty(T, 32, 128, device=dev, dtype=torch.bfloat16)
-    kva = torch.empty(T, 2, 8, 128, device=dev, dtype=torch.bfloat16)
-    report("qkv_rope_split", time_fn(lambda: model_ops.qkv_rope_split(qkv, cos, sin, qa, kva, 32, 8), args.iters, 3, flush),
-           2 * qkv.numel() * 2)
-    dq = torch.randn(T, 32, 128, device=dev)
-    dkv = torch.randn(T, 2, 8, 128, device=dev)
-    report("qkv_rope_pack_bwd", time_fn(lambda: model_ops.qkv_rope_pack_bwd(dq, dkv, cos, sin, T, 32, 8), args.iters, 3, flush),
-           qkv.numel() * (4 + 2))
-    # merge of 3 partial (out, lse) per token: reads 3 partial rows, writes one
-    n_src, hq = 3, 32
-    tm = min(T, 8192)
-    part_out = torch.randn(n_src * tm, hq, 128, device=dev).bfloat16()
-    part_lse = torch.randn(hq, n_src * tm, device=dev)
-    mo, ml = torch.empty(tm, hq, 128, device=dev, dtype=torch.bfloat16), torch.empty(hq, tm, device=dev)
-    ops_t = torch.tensor([[b0, min(2048, tm - b0), 3 * i, 3] for i, b0 in enumerate(range(0, tm, 2048))], dtype=torch.int32, device=dev)
-    src_t = torch.tensor([s * tm + b0 for b0 in range(0, tm, 2048) for s in range(n_src)], dtype=torch.int32, device=dev)
-    report("merge_out_lse", time_fn(lambda: block_ops.merge_out_lse(ops_t, src_t, part_out, part_lse, mo, ml), args.iters, 3, flush),
-           (n_src + 1) * tm * hq * 128 * 2 + (n_src + 1) * tm * hq * 4)
-    # single-rank fused gradient read + AdamW + parameter store: bf16 grad in, fp32 master / m / v in and out, bf16 param out
-    from ..parallel.dist_optimizer import FlatBuffers, ShardedAdamW
-    n = 256 << 20
-    bufs = FlatBuffers(n, dev)
-    opt = ShardedAdamW(bufs, clip_grad=None)
-    bufs.grads.normal_()
-    report("fused_rs_adamw_ag", time_fn(lambda: opt.step(1.0), args.iters, 3, flush), n * (2 + 12 + 12 + 2))
-    for r in res:
-        if args.only is None or r["op"] == args.only:
-            print(json.dumps(r))
+    want = lambda name: args.only is None or args.only == name
+
+    def report(name, ms, nbytes):
+        gbs = nbytes / ms / 1e6
+        print(json.dumps({"op": name, "ms": round(ms, 4), "GB/s": round(gbs, 1), f"frac_of_{src}_hbm": round(gbs / hbm, 3)}))
+
+    if want("rmsnorm_fwd") or want("rmsnorm_bwd"):
+        x = torch.randn(T, H, device=dev).bfloat16()
+        w = torch.ones(H, device=dev).bfloat16()
+        y, rstd = torch.empty_like(x), torch.empty(T, device=dev)
+        fwd = lambda: lib.dcpk_rmsnorm_fwd(_lib.ptr(x), _lib.ptr(w), _lib.ptr(y), _lib.ptr(rstd), ctypes.c_int(T),
+                                           ctypes.c_int(H), ctypes.c_float(1e-5), _lib.stream_handle())
+        fwd()
+        if want("rmsnorm_fwd"):
+            report("rmsnorm_fwd", time_fn(fwd, args.iters, 3, flush), 2 * x.numel() * 2)
+        if want("rmsnorm_bwd"):
+            dx, dw = torch.empty_like(x), torch.zeros(H, device=dev)
+            report("rmsnorm_bwd", time_fn(lambda: lib.dcpk_rmsnorm_bwd(_lib.ptr(x), _lib.ptr(w), _lib.ptr(y), _lib.ptr(rstd),
+                                                                      _lib.ptr(dx), _lib.ptr(dw), ctypes.c_int(T), ctypes.c_int(H),
+                                                                      _lib.stream_handle()), args.iters, 3, flush), 3 * x.numel() * 2)
+        del x, y
+    if want("swiglu_fwd") or want("swiglu_bwd"):
+        gu = torch.randn(T, 2 * F, device=dev).bfloat16()
+        yo = torch.empty(T, F, device=dev, dtype=torch.bfloat16)
+        if want("swiglu_fwd"):
+            report("swiglu_fwd", time_fn(lambda: lib.dcpk_swiglu_fwd(_lib.ptr(gu), _lib.ptr(yo), ctypes.c_long(T), ctypes.c_int(F),
+                                                                    _lib.stream_handle()), args.iters, 3, flush), 3 * T * F * 2)
+        if want("swiglu_bwd"):
+            dgu = torch.empty_like(gu)
+            report("swiglu_bwd", time_fn(lambda: lib.dcpk_swiglu_bwd(_lib.ptr(gu), _lib.ptr(yo), _lib.ptr(dgu), ctypes.c_long(T),
+                                                                    ctypes.c_int(F), _lib.stream_handle()), args.iters, 3, flush), 5 * T * F * 2)
+            del dgu
+        del gu, yo
+    if want("cross_entropy_fwd_bwd"):
+        tc = min(T, 4096)
+        logits = torch.randn(tc, V, device=dev).bfloat16()
+        labels = torch.randint(0, V, (tc,), device=dev)
+        report("cross_entropy_fwd_bwd", time_fn(lambda: model_ops.cross_entropy_inplace(logits, labels, 1.0), args.iters, 3, flush),
+               3 * tc * V * 2)
+        del logits
+    if want("qkv_rope_split") or want("qkv_rope_pack_bwd"):
+        qkv = torch.randn(T, 48 * 128, device=dev).bfloat16()
+        pos = torch.arange(T, device=dev)
+        cos, sin = model_ops.rope_tables(pos)
+        if want("qkv_rope_split"):
+            qa = torch.empty(T, 32, 128, device=dev, dtype=torch.bfloat16)
+            kva = torch.empty(T, 2, 8, 128, device=dev, dtype=torch.bfloat16)
+            report("qkv_rope_split", time_fn(lambda: model_ops.qkv_rope_split(qkv, cos, sin, qa, kva, 32, 8), args.iters, 3, flush),
+                   2 * qkv.numel() * 2)
+        if want("qkv_rope_pack_bwd"):
+            dq = torch.randn(T, 32, 128, device=dev)
+            dkv = torch.randn(T, 2, 8, 128, device=dev)
+            report("qkv_rope_pack_bwd", time_fn(lambda: model_ops.qkv_rope_pack_bwd(dq, dkv, cos, sin, T, 32, 8), args.iters, 3, flush),
+                   qkv.numel() * (4 + 2))
+    if want("merge_out_lse"):
+        # merge of 3 partial (out, lse) per token: reads 3 partial rows, writes one
+        n_src, hq = 3, 32
+        tm = min(T, 8192)
+        part_out = torch.randn(n_src * tm, hq, 128, device=dev).bfloat16()
+        part_lse = torch.randn(hq, n_src * tm, device=dev)
+        mo, ml = torch.empty(tm, hq, 128, device=dev, dtype=torch.bfloat16), torch.empty(hq, tm, device=dev)
+        ops_t = torch.tensor([[b0, min(2048, tm - b0), 3 * i, 3] for i, b0 in enumerate(range(0, tm, 2048))], dtype=torch.int32, device=dev)
+        src_t = torch.tensor([s * tm + b0 for b0 in range(0, tm, 2048) for s in range(n_src)], dtype=torch.int32, device=dev)
+        report("merge_out_lse", time_fn(lambda: block_ops.merge_out_lse(ops_t, src_t, part_out, part_lse, mo, ml), args.iters, 3, flush),
+               (n_src + 1) * tm * hq * 128 * 2 + (n_src + 1) * tm * hq * 4)
+    if want("fused_rs_adamw_ag"):
+        # single-rank fused gradient read + AdamW + parameter store: bf16 grad in, fp32 master / m / v in and out, bf16 param out
+        from ..parallel.dist_optimizer import FlatBuffers, ShardedAdamW
+        n = args.opt_elems
+        bufs = FlatBuffers(n, dev)
+        opt = ShardedAdamW(bufs, clip_grad=None)
+        bufs.grads.normal_()
+        report("fused_rs_adamw_ag", time_fn(lambda: opt.step(1.0), args.iters, 3, flush), n * (2 + 12 + 12 + 2))
 
 
 def bench_nvlink(args):
@@ -251,7 +267,8 @@ def bench_nvlink(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("kind", choices=["attn_fwd", "attn_bwd", "ops", "nvlink"])
-    ap.add_argument("--only", default=None, help="ops: print (and, under a profiler, look at) just this op")
+    ap.add_argument("--only", default=None, help="ops: build and run just this op (small working set for a profiler)")
+    ap.add_argument("--opt-elems", type=int, default=256 << 20, help="ops: parameters of the optimizer-kernel benchmark")
     ap.add_argument("--tokens", type=int, default=8192)
     ap.add_argument("--kv", type=int, default=8192)
     ap.add_argument("--hq", type=int, default=32)

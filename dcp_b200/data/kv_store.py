@@ -27,6 +27,10 @@ class KVServer:
         self.host, self.port = host, port
 
 
+_CHUNK = 4 << 20                 # TCPStore refuses payloads above 8 MiB; larger values travel in pieces
+_CHUNK_MARK = b"\x00dcp-chunked:"
+
+
 class KVStore:
     def __init__(self, host: Optional[str] = None, port: int = 29650, timeout_s: float = 60.0, store=None):
         self.timeout_s = timeout_s
@@ -48,8 +52,14 @@ class KVStore:
             with self._cv:
                 self._local[key] = data
                 self._cv.notify_all()
-        else:
+        elif len(data) <= _CHUNK:
             self._store.set(key, data)
+        else:
+            # pieces first, the header (which readers wait for) last
+            n = -(-len(data) // _CHUNK)
+            for i in range(n):
+                self._store.set(f"{key}#{i}", data[i * _CHUNK:(i + 1) * _CHUNK])
+            self._store.set(key, _CHUNK_MARK + str(n).encode())
 
     def get(self, key: str, timeout_s: Optional[float] = None) -> Any:
         timeout_s = self.timeout_s if timeout_s is None else timeout_s
@@ -67,7 +77,11 @@ class KVStore:
             self._store.wait([key], timedelta(seconds=timeout_s))
         except Exception as e:  # torch raises a generic error type on timeout
             raise KVTimeout(f"key {key!r} was not set within {timeout_s}s") from e
-        return pickle.loads(self._store.get(key))
+        data = self._store.get(key)
+        if data.startswith(_CHUNK_MARK):
+            n = int(data[len(_CHUNK_MARK):])
+            data = b"".join(self._store.get(f"{key}#{i}") for i in range(n))
+        return pickle.loads(data)
 
     def exists(self, key: str) -> bool:
         if self._local is not None:
@@ -90,4 +104,9 @@ class KVStore:
             with self._cv:
                 self._local.pop(key, None)
         else:
+            if self._store.check([key]):
+                data = self._store.get(key)
+                if data.startswith(_CHUNK_MARK):
+                    for i in range(int(data[len(_CHUNK_MARK):])):
+                        self._store.delete_key(f"{key}#{i}")
             self._store.delete_key(key)

@@ -303,7 +303,10 @@ class PlanService:
 def _pickle_plans(spec: PlanSpec, iteration: int) -> Dict[int, bytes]:
     """Worker-process job of shared planning: plan once, hand back one pickled plan per rank."""
     import pickle
-    return {r: pickle.dumps(p, protocol=pickle.HIGHEST_PROTOCOL) for r, p in plan_iteration_all(spec, iteration).items()}
+    import zlib
+    # index tables compress three- to five-fold at level 1, which costs less than sending them
+    return {r: zlib.compress(pickle.dumps(p, protocol=pickle.HIGHEST_PROTOCOL), 1)
+            for r, p in plan_iteration_all(spec, iteration).items()}
 
 
 class SharedPlanService:
@@ -376,7 +379,8 @@ class SharedPlanService:
             if self.store.add(key + "/reads", 1) >= self.readers:
                 self.store.delete(key)
                 self.store.delete(key + "/reads")
-        plan = pickle.loads(blob)
+        import zlib
+        plan = pickle.loads(zlib.decompress(blob))
         waited = time.time() - t0
         self.wait_seconds += waited
         self.waits.append(waited)

@@ -346,7 +346,7 @@ def test_shared_planning_gives_every_rank_the_plan_it_would_compute_itself():
     [t.join(300) for t in threads]
     svcs[(0, 0)].close()
     assert not errs, errs
-    assert svcs[(0, 0)].n_published == 3
+    assert 3 <= svcs[(0, 0)].n_published <= 5      # each batch once; up to two planned ahead may be out already
     for (r, t), plans in got.items():
         for i, p in enumerate(plans):
             ref = plan_iteration(spec, i, r)
@@ -356,3 +356,21 @@ def test_shared_planning_gives_every_rank_the_plan_it_would_compute_itself():
     # iterations planned ahead of the last get() may still sit in the store; the consumed ones must be gone
     left = [k for k in store._local if int(k.split("/")[1]) < 3]
     assert not left, f"plans left in the store after the last reader: {left}"
+
+
+def test_kv_store_moves_values_larger_than_the_tcp_store_payload_limit():
+    """Plans of long batches pickle to more than the 8 MiB a TCPStore message may carry: such values
+    travel in pieces behind a header key, read back whole, and deleting removes the pieces too."""
+    import os
+    from dcp_b200.data.kv_store import KVServer, KVStore
+    port = 29700 + os.getpid() % 200
+    srv = KVServer("127.0.0.1", port)
+    a, b = KVStore("127.0.0.1", port, 10.0), KVStore("127.0.0.1", port, 10.0)
+    big = os.urandom(19 << 20)
+    a.set("big", big)
+    assert b.get("big") == big
+    b.delete("big")
+    assert not a.exists("big") and not a.exists("big#0")
+    a.set("small", b"x" * 100)
+    assert b.get("small") == b"x" * 100 and a.add("n", 2) == 2 and b.add("n", 1) == 3
+    del srv
