@@ -223,6 +223,17 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         m[h] = make_int4(0, 0, 0, 0);
         if (qv && !itx.full) m[h] = masks[itx.mask_row + qi];
       }
+      if (lane == 0 && i + kStages < n_items) {
+        // the ring holds kStages items; the one after them is pulled into L2 now, so that its TMA load
+        // (issued when a slot frees up) finds it there
+        const BwdItem nx = load_item(my_items, i + kStages, group, kv_head);
+        if (nx.q_row >= 0 && nx.q_row < q_rows && nx.head < hq) {
+          tma_prefetch_l2_3d(&tm_q, 0, nx.head, nx.q_row);
+          tma_prefetch_l2_3d(&tm_q, 64, nx.head, nx.q_row);
+          tma_prefetch_l2_3d(&tm_do, 0, nx.head, nx.q_row);
+          tma_prefetch_l2_3d(&tm_do, 64, nx.head, nx.q_row);
+        }
+      }
       ok = mbar_wait(&sm.qdo_empty[st], (u & 1) ^ 1, abort_word);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
