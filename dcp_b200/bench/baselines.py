@@ -11,6 +11,10 @@ and a stock kernel" implementation looks like on the same box and exist to be be
   ``p2p``): K/V chunks travel around the ring with NCCL point-to-point while the library kernel
   attends to the chunk at hand; partial results are merged by log-sum-exp and in the backward
   dK/dV travel with their chunk.  The ring logic is tested on CPU (gloo) against dense attention.
+* double ring            - ``RingAttention(window=w)``: LoongTrain's context ring in which a chunk circles an inner
+  ring of ``w`` ranks and changes rings once per ``w`` steps (baselines/loong_train/loong_train.py:111-165).
+* ``HierarchicalA2AP2P`` - head all-to-all inside groups of adjacent ranks, zigzag ring across groups (TE
+  ``a2a+p2p``).
 * ``NcclPlanAttention`` - the DCP instruction plans interpreted with NCCL point-to-point
   exchanges and torch ops (the plan interpreter, see ``runtime/interface.py``).
 
@@ -192,10 +196,13 @@ def _merge(out, lse, o2, l2, rows=None):
         lse[:, rows] = new
 
 
-def _ring_exchange(tensors, group):
-    """Send ``tensors`` to the next rank of the ring and receive the previous rank's (same shapes)."""
+def _ring_exchange(tensors, group, send_to=None, recv_from=None):
+    """Send ``tensors`` to group rank ``send_to`` (default: the next rank of the ring) and receive the
+    same shapes from ``recv_from`` (default: the previous rank)."""
     P, rank = dist.get_world_size(group), dist.get_rank(group)
-    nxt, prv = dist.get_global_rank(group, (rank + 1) % P), dist.get_global_rank(group, (rank - 1) % P)
+    send_to = (rank + 1) % P if send_to is None else send_to
+    recv_from = (rank - 1) % P if recv_from is None else recv_from
+    nxt, prv = dist.get_global_rank(group, send_to), dist.get_global_rank(group, recv_from)
     recv = [torch.empty_like(t) for t in tensors]
     ops = [dist.P2POp(dist.isend, t.contiguous(), nxt, group) for t in tensors] + \
           [dist.P2POp(dist.irecv, r, prv, group) for r in recv]
@@ -211,15 +218,16 @@ class _RingFn(torch.autograd.Function):
         out = torch.zeros(q.shape, dtype=torch.float32, device=q.device)
         lse = torch.full((q.shape[1], q.shape[0]), float("-inf"), dtype=torch.float32, device=q.device)
         kc, vc = k, v
+        sched = ring.schedule()
         for step in range(P):
-            src = (r - step) % P
+            src, send_to, recv_from = sched[step]
             for rows, cu_q, cols, cu_k, causal in ring.step_plan(step, src):
                 qs = q if rows is None else q[rows]
                 ks, vs = (kc, vc) if cols is None else (kc[cols], vc[cols])
                 o2, l2 = _block_fwd(qs, ks, vs, cu_q, cu_k, ring.scale, causal)
                 _merge(out, lse, o2, l2, rows)
             if step + 1 < P:
-                kc, vc = _ring_exchange([kc, vc], ring.group)
+                kc, vc = _ring_exchange([kc, vc], ring.group, send_to, recv_from)
         res = out.to(q.dtype)
         ctx.ring = ring
         ctx.save_for_backward(q, k, v, res, lse)
@@ -235,8 +243,9 @@ class _RingFn(torch.autograd.Function):
         kc, vc = k, v
         dkc = torch.zeros(k.shape, dtype=torch.float32, device=q.device)
         dvc = torch.zeros_like(dkc)
+        sched = ring.schedule()
         for step in range(P):
-            src = (r - step) % P
+            src, send_to, recv_from = sched[step]
             for rows, cu_q, cols, cu_k, causal in ring.step_plan(step, src):
                 sel = (lambda t: t) if rows is None else (lambda t: t[rows])
                 ks, vs = (kc, vc) if cols is None else (kc[cols], vc[cols])
@@ -252,9 +261,9 @@ class _RingFn(torch.autograd.Function):
                     dkc[cols] += gk; dvc[cols] += gv
             # the chunk and its gradient move on together; after P hops the gradient is home
             if step + 1 < P:
-                kc, vc, dkc, dvc = _ring_exchange([kc, vc, dkc, dvc], ring.group)
+                kc, vc, dkc, dvc = _ring_exchange([kc, vc, dkc, dvc], ring.group, send_to, recv_from)
             else:
-                dkc, dvc = _ring_exchange([dkc, dvc], ring.group)
+                dkc, dvc = _ring_exchange([dkc, dvc], ring.group, send_to, recv_from)
         return dq.to(q.dtype), dkc.to(k.dtype), dvc.to(v.dtype), None
 
 
@@ -263,9 +272,15 @@ class RingAttention:
     of every sequence) or zigzag (rank r holds chunks r and 2P-1-r, which evens out the causal
     work).  Sequence lengths must be multiples of 2P (``adjust_seqlens``)."""
 
-    def __init__(self, group, seqlens: Sequence[int], head_dim: int = 128, zigzag: bool = True):
+    def __init__(self, group, seqlens: Sequence[int], head_dim: int = 128, zigzag: bool = True, window: int = 0):
+        """``window`` > 0 turns the ring into a double ring (LoongTrain's 2D-attention context ring,
+        benchmark/microbenchmark/baselines/loong_train/loong_train.py:111-165): the ranks form
+        P / window inner rings of ``window`` ranks; a K/V chunk circles its inner ring and hops to
+        the next inner ring every ``window`` steps, so only one step in ``window`` crosses rings."""
         self.group, self.zigzag = group, zigzag
         self.P, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        self.window = window if 0 < window < self.P else self.P
+        assert self.P % self.window == 0, "the double-ring window must divide the ring size"
         assert all(n % (2 * self.P) == 0 for n in seqlens), "lengths must be multiples of 2 x ranks"
         self.seqlens = [int(n) for n in seqlens]
         self.scale = head_dim ** -0.5
@@ -302,11 +317,30 @@ class RingAttention:
             off += n
         return torch.cat(idx)
 
+    def schedule(self):
+        """Per step (rank whose chunk is attended to, rank the chunk goes to afterwards, rank the next
+        chunk comes from).  With one inner ring this is the plain ring: chunk of rank r - step, pass
+        to r + 1.  In a double ring the rank is (outer o, inner i) = divmod(r, window); step
+        oo * window + ii looks at the chunk of (o - oo, i - ii); hops stay in the inner ring except
+        after the last inner step, when the chunk moves to the next inner ring (and one place on)."""
+        w, n_outer = self.window, self.P // self.window
+        o, i = divmod(self.rank, w)
+        out = []
+        for step in range(self.P):
+            oo, ii = divmod(step, w)
+            src = ((o - oo) % n_outer) * w + (i - ii) % w
+            if ii != w - 1:
+                hop = (o * w + (i + 1) % w, o * w + (i - 1) % w)
+            else:
+                hop = (((o + 1) % n_outer) * w + (i + 1) % w, ((o - 1) % n_outer) * w + (i - 1) % w)
+            out.append((src, hop[0], hop[1]))
+        return out
+
     def step_plan(self, step: int, src: int):
         """Attention calls of one ring step, as (query rows or None = all, cu_q, key rows or None,
         cu_k, causal)."""
         dev_rows = lambda t: t
-        if step == 0:
+        if src == self.rank:
             if not self.zigzag:
                 return [(None, self.cu, None, self.cu, True)]
             # local chunks (r, 2P-1-r): the early chunk attends causally to itself; the late chunk
@@ -327,6 +361,56 @@ class RingAttention:
         return _RingFn.apply(q, k, v, self)
 
 
+class HierarchicalA2AP2P:
+    """Head-parallel all-to-all inside groups of ``a2a_size`` adjacent ranks, zigzag ring (NCCL
+    point-to-point) across the groups: TransformerEngine's hierarchical ``a2a+p2p`` context
+    parallelism, the strongest library baseline of the reference's figures
+    (benchmark/microbenchmark/baselines/transformer_engine/transformer_engine.py:82-92,
+    benchmark/mlm/run_experiments.py:571-583).  Rank r = ring index * a2a_size + a2a index.  Ring
+    member g owns the zigzag chunks g and 2R-1-g of every sequence; the a2a ranks of a member hold
+    equal contiguous slices of that member's token stream and trade them for all its tokens of
+    H / a2a_size heads, on which the ring attention runs."""
+
+    def __init__(self, group, seqlens: Sequence[int], n_heads: int, n_kv_heads: int, a2a_size: int, head_dim: int = 128):
+        P, rank = dist.get_world_size(group), dist.get_rank(group)
+        assert P % a2a_size == 0 and n_heads % a2a_size == 0 and n_kv_heads % a2a_size == 0
+        self.A, self.R = a2a_size, P // a2a_size
+        self.g, self.a = divmod(rank, a2a_size)
+        ranks = [dist.get_global_rank(group, r) for r in range(P)] if group is not dist.group.WORLD else list(range(P))
+        # every rank creates every sub-group, in the same order (new_group is collective)
+        self.a2a_group = self.ring_group = None
+        for g in range(self.R):
+            grp = dist.new_group([ranks[g * a2a_size + a] for a in range(a2a_size)])
+            if g == self.g:
+                self.a2a_group = grp
+        for a in range(a2a_size):
+            grp = dist.new_group([ranks[g * a2a_size + a] for g in range(self.R)])
+            if a == self.a:
+                self.ring_group = grp
+        self.ring = RingAttention(self.ring_group, seqlens, head_dim=head_dim, zigzag=True)
+        t_member = self.ring.cu[-1]                          # tokens of one ring member
+        assert t_member % a2a_size == 0, "the member's token stream must split evenly over the a2a ranks"
+        self.counts = [t_member // a2a_size] * a2a_size
+        self.n_local = t_member // a2a_size
+
+    @staticmethod
+    def adjust_seqlens(seqlens: Sequence[int], world: int, a2a_size: int) -> List[int]:
+        m = 2 * world                                         # 2 x ring x a2a: every rank slice stays whole
+        return [max(m, (int(n) // m) * m) for n in seqlens]
+
+    def local_indices(self) -> torch.Tensor:
+        """Global token indices of this rank's tokens (its slice of its ring member's stream)."""
+        member = self.ring.local_indices()
+        return member[self.a * self.n_local:(self.a + 1) * self.n_local]
+
+    def __call__(self, q, k, v):
+        qh = _SeqAllToAll.apply(q, self.a2a_group, True, self.counts)
+        kh = _SeqAllToAll.apply(k, self.a2a_group, True, self.counts)
+        vh = _SeqAllToAll.apply(v, self.a2a_group, True, self.counts)
+        out = self.ring(qh, kh, vh)
+        return _SeqAllToAll.apply(out, self.a2a_group, False, self.counts)
+
+
 def make_baseline(framework: str, group, seqlens: Sequence[int], n_heads: int, n_kv_heads: int, rank: int, world: int):
     """-> (attention callable (q, k, v) -> out, number of local tokens) for a baseline framework."""
     if framework == "ulysses":
@@ -337,4 +421,16 @@ def make_baseline(framework: str, group, seqlens: Sequence[int], n_heads: int, n
         # lengths are rounded down to multiples of 2 x ranks (at most 2P - 1 tokens per sequence)
         ra = RingAttention(group, RingAttention.adjust_seqlens(seqlens, world), zigzag=framework == "zigzag")
         return ra, ra.cu[-1]
+    if framework == "double-ring":
+        assert group is not None, "ring attention needs at least two ranks"
+        window = 2 if world % 2 == 0 and world > 2 else world       # inner rings of two ranks (four rings on 8 GPUs)
+        ra = RingAttention(group, RingAttention.adjust_seqlens(seqlens, world), zigzag=True, window=window)
+        return ra, ra.cu[-1]
+    if framework == "a2a+p2p":
+        assert group is not None, "needs at least two ranks"
+        a2a = 2 if world % 2 == 0 else 1
+        while a2a * 2 <= min(n_kv_heads, 4) and world % (a2a * 2) == 0 and world // (a2a * 2) >= 2:
+            a2a *= 2                                                 # 4 x 2 on 8 GPUs, 2 x 2 on 4
+        ha = HierarchicalA2AP2P(group, HierarchicalA2AP2P.adjust_seqlens(seqlens, world, a2a), n_heads, n_kv_heads, a2a)
+        return ha, ha.n_local
     raise ValueError(f"unknown baseline framework {framework!r}")

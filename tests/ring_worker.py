@@ -9,7 +9,7 @@ import torch.distributed as dist
 
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
-from dcp_b200.bench.baselines import RingAttention, _dense_block_fwd  # noqa: E402
+from dcp_b200.bench.baselines import HierarchicalA2AP2P, RingAttention  # noqa: E402
 
 
 def main():
@@ -37,8 +37,14 @@ def main():
     ref = torch.cat(outs)
     ref.backward(dout)
     ok = True
-    for zigzag in (False, True):
-        ring = RingAttention(dist.group.WORLD, seqlens, head_dim=d, zigzag=zigzag)
+    variants = [("ring", lambda: RingAttention(dist.group.WORLD, seqlens, head_dim=d, zigzag=False)),
+                ("zigzag", lambda: RingAttention(dist.group.WORLD, seqlens, head_dim=d, zigzag=True))]
+    if world >= 4:
+        variants += [("double ring", lambda: RingAttention(dist.group.WORLD, seqlens, head_dim=d, zigzag=True, window=2)),
+                     ("plain double ring", lambda: RingAttention(dist.group.WORLD, seqlens, head_dim=d, zigzag=False, window=2)),
+                     ("a2a+p2p", lambda: HierarchicalA2AP2P(dist.group.WORLD, seqlens, H, Hkv, 2, head_dim=d))]
+    for zigzag, make in variants:
+        ring = make()
         idx = ring.local_indices()
         ql, kl, vl = (t[idx].clone().requires_grad_(True) for t in (q, k, v))
         out = ring(ql, kl, vl)

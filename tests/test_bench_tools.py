@@ -58,11 +58,14 @@ def test_ring_baselines_match_dense_attention():
     import subprocess
     import sys
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
-           "127.0.0.1", "--master-port", "29631", os.path.join(root, "tests", "ring_worker.py")]
-    res = subprocess.run(cmd, env=dict(os.environ, PYTHONPATH=root, OMP_NUM_THREADS="2"), stdout=subprocess.PIPE,
-                         stderr=subprocess.STDOUT, text=True, timeout=600)
-    assert res.returncode == 0 and "RING_OK" in res.stdout, res.stdout[-3000:]
+    # 2 ranks: plain and zigzag ring; 4 ranks: also the double ring (two inner rings of two) and the
+    # hierarchical all-to-all (2) x ring (2) pattern
+    for world, port in ((2, 29631), (4, 29633)):
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr",
+               "127.0.0.1", "--master-port", str(port), os.path.join(root, "tests", "ring_worker.py")]
+        res = subprocess.run(cmd, env=dict(os.environ, PYTHONPATH=root, OMP_NUM_THREADS="2"), stdout=subprocess.PIPE,
+                             stderr=subprocess.STDOUT, text=True, timeout=600)
+        assert res.returncode == 0 and "RING_OK" in res.stdout, res.stdout[-3000:]
 
 
 def test_dry_run_grid_and_best_config(tmp_path):
