@@ -125,6 +125,10 @@ class DCPDataLoader:
                  mask_fn_extra_keys=None, is_dryrun: bool = False, world: Optional[int] = None,
                  build_instruction_plans: bool = True):
         assert batch_sampler is not None, "pass an OrderedBatchSampler (token-budget batches)"
+        assert 0 <= pp_rank < max(1, training_spec.pipeline_parallel_size), \
+            f"pp_rank ({pp_rank}) must be smaller than pipeline_parallel_size ({training_spec.pipeline_parallel_size})"
+        assert 0 <= tp_rank < max(1, training_spec.tensor_parallel_size), \
+            f"tp_rank ({tp_rank}) must be smaller than tensor_parallel_size ({training_spec.tensor_parallel_size})"
         self.training_spec, self.dataset, self.batch_sampler = training_spec, dataset, batch_sampler
         self.dcp_rank, self.pin_memory, self.is_dryrun = dcp_rank, pin_memory, is_dryrun
         # pipeline stages read the same plans as their first stage (attention placement does not depend

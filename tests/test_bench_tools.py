@@ -82,3 +82,18 @@ def test_dry_run_grid_and_best_config(tmp_path):
         assert c["inter_node_MB_per_device"] >= 0 and c["n_work_units"] > 0
     assert res["best"][0]["modelled_pipeline_ms"] == min(c["modelled_pipeline_ms"] for c in res["cells"])
     assert json.load(open(out))["best"] == res["best"]
+
+
+def test_pipeline_stage_boundary():
+    """Pipeline-parallel stage links (NCCL / gloo point-to-point with early-posted receives) in
+    one-forward-one-backward order on 2 and 3 stages: gradients and losses equal the unsplit model."""
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    for world, port in ((2, 29641), (3, 29643)):
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr",
+               "127.0.0.1", "--master-port", str(port), os.path.join(root, "tests", "pp_worker.py")]
+        res = subprocess.run(cmd, env=dict(os.environ, PYTHONPATH=root, OMP_NUM_THREADS="1"), stdout=subprocess.PIPE,
+                             stderr=subprocess.STDOUT, text=True, timeout=300)
+        assert res.returncode == 0 and "PP_OK" in res.stdout, res.stdout[-3000:]
