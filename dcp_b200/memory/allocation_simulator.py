@@ -1,9 +1,12 @@
 """Address-space simulator of a caching allocator: best-fit blocks, splitting, coalescing on free.
 
 Used to size and to drive the pinned host arena (and to estimate paged-buffer footprints in dry
-runs) without touching real memory.  Plays the role of
-dcp/memory/allocation_simulator.py:69-348 with a simpler design: one sorted free list over a
-linear address space instead of a re-implementation of torch's multi-pool allocator.
+runs) without touching real memory.  Two models: ``AllocationSimulator`` is the arena's own policy
+(one sorted free list over a linear address space); ``TorchCachingAllocatorSimulator`` follows the
+framework's CUDA caching allocator (size rounding, small / large pools with their segment sizes,
+best fit, split thresholds, per-segment coalescing), which is what the reference's simulator
+models (dcp/memory/allocation_simulator.py:69-348), to predict reserved memory from an
+allocation trace.
 """
 from __future__ import annotations
 
@@ -69,5 +72,105 @@ class AllocationSimulator:
         self.__init__(self.capacity, self.alignment)
 
 
-# name used by the reference
-TorchCachingAllocatorSimulator = AllocationSimulator
+class TorchCachingAllocatorSimulator:
+    """Model of the framework's CUDA caching allocator, for predicting how much device memory a
+    sequence of allocations and frees will *reserve* (not just use): the question the reference asks
+    its simulator before sizing pinned buffers (dcp/memory/allocation_simulator.py:69-348).
+
+    Modelled behaviour: requests are rounded up to 512 bytes; requests of at most 1 MiB are served
+    from the small pool, whose segments are 2 MiB; larger ones from the large pool, whose segments
+    are 20 MiB for requests below 10 MiB and the request rounded up to 2 MiB otherwise; a request
+    takes the smallest cached free block of its pool that fits (best fit), a new segment is
+    reserved when none does; a block is split when the remainder is worth keeping (at least 512
+    bytes in the small pool, more than 1 MiB in the large pool); freed blocks merge with free
+    neighbours of the same segment; ``empty_cache`` returns fully free segments.  ``capacity``
+    bounds the reserved bytes (OutOfArena beyond it, after one ``empty_cache`` retry, as the real
+    allocator retries after releasing its cache)."""
+
+    ROUND, SMALL_LIMIT, SMALL_SEGMENT = 512, 1 << 20, 2 << 20
+    LARGE_SEGMENT, LARGE_DIRECT, LARGE_ROUND = 20 << 20, 10 << 20, 2 << 20
+
+    def __init__(self, capacity: int = 1 << 62):
+        self.capacity = int(capacity)
+        self._segments: Dict[int, Dict] = {}      # id -> {"size", "pool", "blocks": sorted [offset, size, free]}
+        self._next_id = 0
+        self._live: Dict[int, Tuple[int, int]] = {}   # handle -> (segment id, offset)
+        self._next_handle = 0
+        self.allocated = self.reserved = self.peak_allocated = self.peak_reserved = 0
+        self.n_segments_reserved = 0
+
+    def _round(self, n: int) -> int:
+        return max(self.ROUND, -(-int(n) // self.ROUND) * self.ROUND)
+
+    def _segment_size(self, size: int) -> int:
+        if size <= self.SMALL_LIMIT:
+            return self.SMALL_SEGMENT
+        if size < self.LARGE_DIRECT:
+            return self.LARGE_SEGMENT
+        return -(-size // self.LARGE_ROUND) * self.LARGE_ROUND
+
+    def _find(self, pool: str, size: int):
+        best = None
+        for sid, seg in self._segments.items():
+            if seg["pool"] != pool:
+                continue
+            for i, (off, sz, free) in enumerate(seg["blocks"]):
+                if free and sz >= size and (best is None or sz < best[2]):
+                    best = (sid, i, sz)
+        return best
+
+    def alloc(self, nbytes: int) -> int:
+        """-> handle to pass to ``free``."""
+        size = self._round(nbytes)
+        pool = "small" if size <= self.SMALL_LIMIT else "large"
+        hit = self._find(pool, size)
+        if hit is None:
+            seg_size = self._segment_size(size)
+            if self.reserved + seg_size > self.capacity:
+                self.empty_cache()
+                if self.reserved + seg_size > self.capacity:
+                    raise OutOfArena(f"cannot reserve {seg_size} bytes (reserved {self.reserved} of {self.capacity})")
+            sid, self._next_id = self._next_id, self._next_id + 1
+            self._segments[sid] = {"size": seg_size, "pool": pool, "blocks": [[0, seg_size, True]]}
+            self.reserved += seg_size
+            self.n_segments_reserved += 1
+            self.peak_reserved = max(self.peak_reserved, self.reserved)
+            hit = (sid, 0, seg_size)
+        sid, i, sz = hit
+        blocks = self._segments[sid]["blocks"]
+        off = blocks[i][0]
+        rest = sz - size
+        keep = rest >= self.ROUND if pool == "small" else rest > self.SMALL_LIMIT
+        if keep:
+            blocks[i] = [off, size, False]
+            blocks.insert(i + 1, [off + size, rest, True])
+        else:
+            blocks[i][2] = False
+        used = blocks[i][1]
+        self.allocated += used
+        self.peak_allocated = max(self.peak_allocated, self.allocated)
+        h, self._next_handle = self._next_handle, self._next_handle + 1
+        self._live[h] = (sid, off)
+        return h
+
+    def free(self, handle: int) -> None:
+        sid, off = self._live.pop(handle)
+        blocks = self._segments[sid]["blocks"]
+        i = next(j for j, b in enumerate(blocks) if b[0] == off)
+        self.allocated -= blocks[i][1]
+        blocks[i][2] = True
+        if i + 1 < len(blocks) and blocks[i + 1][2]:
+            blocks[i][1] += blocks.pop(i + 1)[1]
+        if i > 0 and blocks[i - 1][2]:
+            blocks[i - 1][1] += blocks.pop(i)[1]
+
+    def empty_cache(self) -> int:
+        """Release segments that are entirely free; -> bytes returned."""
+        gone = [sid for sid, seg in self._segments.items() if len(seg["blocks"]) == 1 and seg["blocks"][0][2]]
+        freed = sum(self._segments.pop(sid)["size"] for sid in gone)
+        self.reserved -= freed
+        return freed
+
+    def stats(self) -> Dict[str, int]:
+        return {"allocated": self.allocated, "reserved": self.reserved, "peak_allocated": self.peak_allocated,
+                "peak_reserved": self.peak_reserved, "segments": len(self._segments)}

@@ -374,3 +374,34 @@ def test_kv_store_moves_values_larger_than_the_tcp_store_payload_limit():
     a.set("small", b"x" * 100)
     assert b.get("small") == b"x" * 100 and a.add("n", 2) == 2 and b.add("n", 1) == 3
     del srv
+
+
+def test_torch_caching_allocator_model():
+    """Pools, segment sizes, split thresholds, coalescing and cache release of the allocator model."""
+    from dcp_b200.memory.allocation_simulator import OutOfArena, TorchCachingAllocatorSimulator as Sim
+    MiB = 1 << 20
+    sim = Sim()
+    a = sim.alloc(1000)                      # small pool: rounded to 1024, one 2 MiB segment
+    assert sim.stats() == {"allocated": 1024, "reserved": 2 * MiB, "peak_allocated": 1024, "peak_reserved": 2 * MiB, "segments": 1}
+    b = sim.alloc(MiB)                       # still small (<= 1 MiB): same segment, no new reservation
+    assert sim.reserved == 2 * MiB
+    c = sim.alloc(3 * MiB)                   # large pool: a 20 MiB segment, split (17 MiB remainder kept)
+    assert sim.reserved == 22 * MiB and sim.allocated == 1024 + MiB + 3 * MiB
+    d = sim.alloc(16 * MiB + 512 * 1024)     # fits the 17 MiB remainder; its 0.5 MiB tail is not split off
+    assert sim.reserved == 22 * MiB and sim.allocated == 1024 + MiB + 20 * MiB
+    e = sim.alloc(25 * MiB + 1)              # >= 10 MiB: own segment rounded up to 2 MiB
+    assert sim.reserved == 22 * MiB + 26 * MiB
+    sim.free(c); sim.free(d)                 # neighbours merge back into one 20 MiB block
+    assert sim.empty_cache() == 20 * MiB and sim.reserved == 28 * MiB
+    sim.free(a); sim.free(b); sim.free(e)
+    assert sim.allocated == 0 and sim.empty_cache() == 28 * MiB and sim.stats()["segments"] == 0
+    assert sim.peak_reserved == 48 * MiB
+    small = Sim(capacity=4 * MiB)            # a cap on reserved bytes: cached segments are released before giving up
+    h = [small.alloc(MiB) for _ in range(4)]
+    for x in h:
+        small.free(x)
+    assert small.reserved == 4 * MiB         # two cached 2 MiB segments
+    import pytest
+    with pytest.raises(OutOfArena):          # a 20 MiB segment cannot be had even after releasing the cache ...
+        small.alloc(3 * MiB + MiB // 2)
+    assert small.reserved == 0               # ... but the cache was released in the attempt
