@@ -9,6 +9,7 @@ reference's (dcp/data/hf_dataset.py:249-312).
 """
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass, field
 from typing import Dict, Iterator, List, Optional
 
@@ -85,41 +86,100 @@ class DummyMultiModelDataset(Dataset):
 
 @dataclass
 class HuggingFaceDatasetConfig:
-    dataset_name: str = ""
-    tokenizer_name: str = ""
+    dataset_name: str = ""           # a `datasets` name / local path, or "" when `texts` are passed directly
+    tokenizer_name: str = ""         # a `transformers` tokenizer name / path, or "bytes" for the built-in byte tokenizer
     split: str = "train"
     text_key: str = "text"
     max_seq_len: int = 131072
     min_seq_len: int = 16
-    cache_dir: Optional[str] = None
+    cache_dir: Optional[str] = None  # tokenised samples are cached here (one .npz per configuration)
     seqlen_scale: float = 1.0        # the benchmark's x0.5 / x2 / x4 length scaling
 
 
-class HuggingFaceDataset(Dataset):
-    """Text dataset tokenised on first use.  Needs the optional ``datasets`` and ``transformers``
-    packages and local copies of the data (there is no network in the build image)."""
+def byte_tokenizer(text: str) -> List[int]:
+    """UTF-8 bytes + 1 with 0 as the begin-of-text id: a dependency-free tokenizer (vocabulary 257)."""
+    return [0] + [b + 1 for b in text.encode("utf-8")]
 
-    def __init__(self, config: HuggingFaceDatasetConfig):
-        try:
-            import datasets  # noqa: F401
-            from transformers import AutoTokenizer
-        except ImportError as e:  # pragma: no cover - optional dependency
-            raise ImportError("HuggingFaceDataset needs the `datasets` and `transformers` packages") from e
-        import datasets as hf
+
+class HuggingFaceDataset(Dataset):
+    """Text dataset, tokenised once and cached (dcp/data/hf_dataset.py:24-312).
+
+    Sources: a ``datasets`` dataset (optional package, local copy: there is no network in the build
+    image) or an in-memory list of ``texts``; tokenizer: a ``transformers`` tokenizer, a callable
+    text -> ids, or the built-in byte tokenizer.  Tokenisation, length scaling and the length
+    filter run once; the result is written to ``cache_dir`` as one ``.npz`` keyed by everything
+    that determines it and loaded from there afterwards.  Under ``torch.distributed`` rank 0
+    builds the cache while the other ranks wait at a barrier, then they load it (the reference's
+    rank-0-first protocol, hf_dataset.py:174-247)."""
+
+    def __init__(self, config: HuggingFaceDatasetConfig, texts: Optional[List[str]] = None, tokenizer=None):
         self.config = config
-        tok = AutoTokenizer.from_pretrained(config.tokenizer_name)
-        ds = hf.load_dataset(config.dataset_name, split=config.split, cache_dir=config.cache_dir)
+        self.built_from_cache = False
+        path = self._cache_path(texts)
+        rank0, distributed = True, False
+        try:
+            import torch.distributed as dist
+            distributed = dist.is_available() and dist.is_initialized()
+            rank0 = not distributed or dist.get_rank() == 0
+        except Exception:  # pragma: no cover - torch without distributed support
+            pass
+        if path is not None and not rank0:
+            dist.barrier()                      # rank 0 is tokenising
+        if path is not None and os.path.exists(path):
+            data = np.load(path)
+            flat, cu = data["tokens"], data["offsets"]
+            self.ids = [flat[cu[i]:cu[i + 1]] for i in range(len(cu) - 1)]
+            self.built_from_cache = True
+        else:
+            self.ids = self._tokenise(texts, tokenizer)
+            if path is not None and rank0:
+                os.makedirs(os.path.dirname(path), exist_ok=True)
+                cu = np.zeros(len(self.ids) + 1, dtype=np.int64)
+                np.cumsum([len(t) for t in self.ids], out=cu[1:])
+                tmp = f"{path}.{os.getpid()}.tmp.npz"
+                np.savez(tmp, tokens=np.concatenate(self.ids) if self.ids else np.zeros(0, np.int64), offsets=cu)
+                os.replace(tmp, path)           # atomic: readers never see a partial file
+        if path is not None and rank0 and distributed:
+            dist.barrier()                      # the cache is complete: let the other ranks load it
+        self.seqlens = [len(t) - 1 for t in self.ids]
+
+    def _cache_path(self, texts) -> Optional[str]:
+        c = self.config
+        if not c.cache_dir:
+            return None
+        import hashlib
+        key = repr((c.dataset_name, c.tokenizer_name, c.split, c.text_key, c.max_seq_len, c.min_seq_len, c.seqlen_scale,
+                    None if texts is None else hashlib.sha1("\x00".join(texts).encode()).hexdigest()))
+        return os.path.join(c.cache_dir, "tokenised_" + hashlib.sha1(key.encode()).hexdigest()[:16] + ".npz")
+
+    def _tokenise(self, texts, tokenizer) -> List[np.ndarray]:
+        c = self.config
+        if tokenizer is None:
+            if c.tokenizer_name in ("", "bytes"):
+                tokenizer = byte_tokenizer
+            else:
+                try:
+                    from transformers import AutoTokenizer
+                except ImportError as e:  # pragma: no cover - optional dependency
+                    raise ImportError("a named tokenizer needs the `transformers` package") from e
+                tok = AutoTokenizer.from_pretrained(c.tokenizer_name)
+                tokenizer = lambda text: tok(text, add_special_tokens=True)["input_ids"]
+        if texts is None:
+            try:
+                import datasets as hf
+            except ImportError as e:  # pragma: no cover - optional dependency
+                raise ImportError("loading a named dataset needs the `datasets` package") from e
+            texts = (row[c.text_key] for row in hf.load_dataset(c.dataset_name, split=c.split, cache_dir=c.cache_dir))
         ids = []
-        for row in ds:
-            t = tok(row[config.text_key], add_special_tokens=True)["input_ids"]
-            if config.seqlen_scale != 1.0:
-                reps = int(np.ceil(config.seqlen_scale))
-                t = (t * reps)[:max(2, int(len(t) * config.seqlen_scale))]
-            t = t[:config.max_seq_len + 1]
-            if len(t) - 1 >= config.min_seq_len:
+        for text in texts:
+            t = list(tokenizer(text))
+            if c.seqlen_scale != 1.0:
+                reps = int(np.ceil(c.seqlen_scale))
+                t = (t * reps)[:max(2, int(len(t) * c.seqlen_scale))]
+            t = t[:c.max_seq_len + 1]
+            if len(t) - 1 >= c.min_seq_len:
                 ids.append(np.asarray(t, dtype=np.int64))
-        self.ids = ids
-        self.seqlens = [len(t) - 1 for t in ids]
+        return ids
 
     def __len__(self):
         return len(self.ids)

@@ -405,3 +405,24 @@ def test_torch_caching_allocator_model():
     with pytest.raises(OutOfArena):          # a 20 MiB segment cannot be had even after releasing the cache ...
         small.alloc(3 * MiB + MiB // 2)
     assert small.reserved == 0               # ... but the cache was released in the attempt
+
+
+def test_text_dataset_tokenises_once_and_loads_its_cache(tmp_path):
+    """HuggingFaceDataset on in-memory texts with the byte tokenizer: samples, length filter, x2 length
+    scaling, the on-disk cache (second construction does not tokenise) and batching by the sampler."""
+    from dcp_b200.data.datasets import HuggingFaceDataset, HuggingFaceDatasetConfig, OrderedBatchSampler, byte_tokenizer
+    texts = ["hello world " * k for k in (1, 3, 9, 27, 81)] + ["x"]
+    cfg = HuggingFaceDatasetConfig(tokenizer_name="bytes", min_seq_len=8, max_seq_len=400, cache_dir=str(tmp_path))
+    ds = HuggingFaceDataset(cfg, texts=texts)
+    assert not ds.built_from_cache and len(ds) == 5                      # "x" is filtered out
+    assert ds.seqlens == [min(12 * k, 400) for k in (1, 3, 9, 27, 81)]
+    s = ds[1]
+    assert s["tokens"].tolist() == byte_tokenizer(texts[1])[:-1] and s["labels"].tolist() == byte_tokenizer(texts[1])[1:]
+    calls = []
+    ds2 = HuggingFaceDataset(cfg, texts=texts, tokenizer=lambda t: calls.append(t) or [0])
+    assert ds2.built_from_cache and not calls and ds2.seqlens == ds.seqlens
+    assert all((a == b).all() for a, b in zip(ds.ids, ds2.ids))
+    scaled = HuggingFaceDataset(HuggingFaceDatasetConfig(tokenizer_name="bytes", min_seq_len=8, seqlen_scale=2.0), texts=texts)
+    assert scaled.seqlens[0] == 2 * 13 - 1
+    batches = list(OrderedBatchSampler(ds, 512, shuffle=False, min_fill=0.0))
+    assert sorted(i for b in batches for i in b) == list(range(5))
