@@ -17,6 +17,7 @@
 // (local accumulator) or one 128-byte bulk reduce per query row (peer accumulator).  dK/dV stay
 // in TMEM for the CTA's lifetime and are added once with red.global.add.v4.f32.
 // TMEM columns: S^T [0,64) dP^T [64,128) dQ^T [128,192) [192,256) dK [256,384) dV [384,512).
+// Warps: 0-15 gradient (warp = 32 key rows x 16 query columns), 16 TMA producer, 17 UMMA issuer.
 // The first `n_copy_rows` rows of the grid are fetch CTAs: they compute nothing and bring the next plan
 // stage's remote operands (Q, dO, KV rows and the lse / delta statistics of the queries) from peer
 // GPUs into this GPU's staging rows (copy_jobs.cuh) while the other CTAs of the same launch work
@@ -35,7 +36,7 @@
 
 namespace dcpk {
 
-static constexpr int kBwdThreads = 320;  // 8 gradient warps + TMA producer + UMMA issuer
+static constexpr int kBwdThreads = 576;  // 16 gradient warps + TMA producer + UMMA issuer
 static constexpr int kQTile = 64;
 static constexpr int kStages = 3;  // depth of the Q / dO / statistics ring
 static constexpr int kKvHalf = 128 * 64 * 2;  // [128 x 64] bf16 half tile, 16 KB
@@ -89,7 +90,7 @@ struct __align__(1024) BwdSmem {
   // dQ staging, one private [16 queries x 32 channels] fp32 tile per gradient warp; drained to the
   // fp32 accumulator with bulk reduce-add copies (L2 handles those a line at a time, scalar
   // red.add is limited to one element per L2 slice per clock)
-  float dq_stage[8][16 * 32];
+  float dq_stage[16][8 * 32];
   // per-stage item descriptor and per-query statistics, staged by the producer warp next to Q / dO
   // so the gradient warps never touch global memory on their critical path
   BwdItem item[kStages];
@@ -159,7 +160,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     }
   }
 
-  if (threadIdx.x == 256) {
+  if (threadIdx.x == 512) {
     tma_prefetch_desc(&tm_q);
     tma_prefetch_desc(&tm_do);
     tma_prefetch_desc(&tm_kv);
@@ -167,13 +168,13 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     mbar_init(&sm.kv_full, 1);
     for (int i = 0; i < kStages; ++i) { mbar_init(&sm.qdo_full[i], 1); mbar_init(&sm.qdo_empty[i], 1); mbar_init(&sm.stats_full[i], 1); }
     mbar_init(&sm.sdp_full, 1);
-    mbar_init(&sm.s_free, 256);
-    mbar_init(&sm.p_ready, 256);
+    mbar_init(&sm.s_free, 512);
+    mbar_init(&sm.p_ready, 512);
     mbar_init(&sm.dq_full, 1);
     sm.abort_word = 0;
     mbar_fence_init();
   }
-  if (warp == 9) {
+  if (warp == 17) {
     tmem_alloc(&sm.tmem_base, 512);
     tmem_relinquish();
   }
@@ -184,9 +185,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   volatile int* abort_word = &sm.abort_word;
   constexpr uint32_t cS = 0, cdP = 64, cdQ = 128 /* two 64-column buffers */, cdK = 256, cdV = 384;
 
-  long long* tl = (kTL && blockIdx.x == 0 && int(blockIdx.y) == n_copy_rows && (warp == 0 || warp == 9)) ? g_bwd_timeline : nullptr;
+  long long* tl = (kTL && blockIdx.x == 0 && int(blockIdx.y) == n_copy_rows && (warp == 0 || warp == 17)) ? g_bwd_timeline : nullptr;
   long long tl_t = kTL ? clock64() : 0;
-  if (warp == 8) {
+  if (warp == 16) {
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
       mbar_expect_tx(&sm.kv_full, 4 * kKvHalf);
@@ -264,7 +265,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         if (pending[s2] >= 0)
           for (int spin = 0; spin < 200000 && !mbar_try_wait(&sm.qdo_full[s2], pending[s2]); ++spin) {}
     }
-  } else if (warp == 9) {
+  } else if (warp == 17) {
     // ------------------------------------------------------------ UMMA issuer
     constexpr uint32_t idesc_sdp = make_idesc_bf16(128, 64, 0, 0);
     constexpr uint32_t idesc_acc = make_idesc_bf16(128, 128, 0, 1);
@@ -336,7 +337,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     if (ok && n_items > 0) mbar_wait(&sm.dq_full, (n_items - 1) & 1, abort_word);
   } else {
     // ------------------------------------------------------------ softmax-gradient threads
-    // 8 warps: warp w works on TMEM lanes 32*(w&3).. (key rows) and on query columns 32*(w>>2)..+31
+    // 16 warps: warp w works on TMEM lanes 32*(w&3).. (key rows) and on query columns 16*(w>>2)..+15; four
+    // warps per scheduler hide each other's TMEM / shared-memory / special-function latencies
     const int quad = warp & 3, hf = warp >> 2;
     const int r = quad * 32 + lane;  // key row inside the tile == TMEM lane
     const uint32_t lane_base = uint32_t(quad * 32) << 16;
@@ -344,22 +346,22 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     const bool key_valid = r < cta.n_valid;
     bool ok = true;
     BwdItem prev{};
-    // adds half (16 queries) of this warp's [32 d x 32 q] part of dQ^T of an item into the fp32
+    // adds half (8 queries) of this warp's [32 d x 16 q] part of dQ^T of an item into the fp32
     // accumulator: transpose through the warp's staging tile, then one TMA reduce-add of the
-    // [16 q x 32 d] tile (local accumulator) or one 128-byte bulk reduce per query row (peer)
+    // [8 q x 32 d] tile (local accumulator) or one 128-byte bulk reduce per query row (peer)
     auto flush_dq = [&](const BwdItem& itx, int buf, int half) {
       if (itx.dq_dev < 0) return;  // dQ not wanted (used to measure the cost of the drain)
       float* stage = sm.dq_stage[warp];
       asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");  // the earlier drain has left smem
       __syncwarp();
-      uint32_t reg[16];
-      tmem_ld16(tmem + lane_base + cdQ + buf * 64 + hf * 32 + half * 16, reg);
+      uint32_t reg[8];
+      tmem_ld8(tmem + lane_base + cdQ + buf * 64 + hf * 16 + half * 8, reg);
       tmem_wait_ld();
 #pragma unroll
-      for (int i = 0; i < 16; ++i) stage[i * 32 + lane] = __uint_as_float(reg[i]);
+      for (int i = 0; i < 8; ++i) stage[i * 32 + lane] = __uint_as_float(reg[i]);
       fence_proxy_async_smem();
       __syncwarp();
-      const int q0 = hf * 32 + half * 16;
+      const int q0 = hf * 16 + half * 8;
       if (itx.dq_dev == 0) {
         // rows past n_rows hold exact zeros (their probabilities are masked to 0): adding them is harmless
         if (lane == 0) {
@@ -371,7 +373,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         }
       } else {
         const int qi = q0 + lane;
-        if (lane < 16 && qi < itx.n_rows) {
+        if (lane < 8 && qi < itx.n_rows) {
           float* dq = ptrs.dq[itx.dq_dev] + (size_t(itx.dq_row + qi) * hq + itx.head) * kHeadDim + quad * 32;
           asm volatile("cp.reduce.async.bulk.global.shared::cta.bulk_group.add.f32 [%0], [%1], %2;"
                        ::"l"(dq), "r"(smem_u32(stage + lane * 32)), "r"(128)
@@ -383,15 +385,15 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     // S^T / dP^T of an item are pulled into registers as early as possible (right after the
     // previous item's operands were handed to the tensor core), which frees their TMEM columns for
     // the next-but-one item while this warp still drains dQ and does the math
-    uint32_t sreg[32], dreg[32];
+    uint32_t sreg[16], dreg[16];
     auto load_sdp = [&](int t) -> bool {
       bool k = mbar_wait(&sm.sdp_full, t & 1, abort_word);
       k = __all_sync(0xffffffffu, k);
       if (!k) return false;
       TL_ADD(1, tl_t);
       tc_fence_after();
-      tmem_ld32(tmem + lane_base + cS + hf * 32, sreg);
-      tmem_ld32(tmem + lane_base + cdP + hf * 32, dreg);
+      tmem_ld16(tmem + lane_base + cS + hf * 16, sreg);
+      tmem_ld16(tmem + lane_base + cdP + hf * 16, dreg);
       tmem_wait_ld();
       tc_fence_before();
       mbar_arrive(&sm.s_free);
@@ -407,19 +409,19 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       const BwdItem itx = sm.item[st];
       TL_ADD(0, tl_t);
       const int kpos = itx.kv_pos0 + r;
-      const int n_rows_h = itx.n_rows - hf * 32;  // valid queries inside this warp's column half
-      uint32_t preg[16], dsreg[16];
+      const int n_rows_h = itx.n_rows - hf * 16;  // valid queries inside this warp's column quarter
+      uint32_t preg[8], dsreg[8];
       // The tile-level "no masking needed" switch is taken once, outside the element loop: with a
       // branch per element every element becomes its own basic block and the compiler cannot
       // interleave the independent exp / multiply chains.
-      const float* lse2_w = sm.lse2[st] + hf * 32;
-      const float* delta_w = sm.delta[st] + hf * 32;
+      const float* lse2_w = sm.lse2[st] + hf * 16;
+      const float* delta_w = sm.delta[st] + hf * 16;
       const uint64_t sl2_2 = pack_f32x2(sl2, sl2), scale_2 = pack_f32x2(scale, scale);
       const uint64_t* nlse_w = reinterpret_cast<const uint64_t*>(lse2_w);
       const uint64_t* ndel_w = reinterpret_cast<const uint64_t*>(delta_w);
       if (itx.full) {
 #pragma unroll
-        for (int c = 0; c < 16; ++c) {
+        for (int c = 0; c < 8; ++c) {
           // two queries per instruction: exponent argument and (dP - delta) * scale in packed fp32
           const uint64_t x2 = fma_f32x2(pack_f32x2(__uint_as_float(sreg[2 * c]), __uint_as_float(sreg[2 * c + 1])), sl2_2, nlse_w[c]);
           const uint64_t g2 = fma_f32x2(pack_f32x2(__uint_as_float(dreg[2 * c]), __uint_as_float(dreg[2 * c + 1])), scale_2, ndel_w[c]);
@@ -434,9 +436,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           dsreg[c] = pack_bf16x2(d0, d1);
         }
       } else {
-        const int4* rng_w = sm.rng[st] + hf * 32;
+        const int4* rng_w = sm.rng[st] + hf * 16;
 #pragma unroll
-        for (int c = 0; c < 16; ++c) {
+        for (int c = 0; c < 8; ++c) {
           const uint64_t x2 = fma_f32x2(pack_f32x2(__uint_as_float(sreg[2 * c]), __uint_as_float(sreg[2 * c + 1])), sl2_2, nlse_w[c]);
           const uint64_t g2 = fma_f32x2(pack_f32x2(__uint_as_float(dreg[2 * c]), __uint_as_float(dreg[2 * c + 1])), scale_2, ndel_w[c]);
           float x0, x1;
@@ -462,8 +464,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       }
       TL_ADD(3, tl_t);
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const int ch = hf * 4 + i;
+      for (int i = 0; i < 2; ++i) {
+        const int ch = hf * 2 + i;
         const uint32_t off = r * 128 + ((ch ^ (r & 7)) << 4);
         *reinterpret_cast<uint4*>(sm.p + off) = make_uint4(preg[4 * i], preg[4 * i + 1], preg[4 * i + 2], preg[4 * i + 3]);
         *reinterpret_cast<uint4*>(sm.ds + off) = make_uint4(dsreg[4 * i], dsreg[4 * i + 1], dsreg[4 * i + 2], dsreg[4 * i + 3]);
@@ -489,28 +491,25 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         tc_fence_after();
         flush_dq(prev, (n_items - 1) & 1, 0);
         flush_dq(prev, (n_items - 1) & 1, 1);
-        // dK / dV: lane = key row; this warp adds channels 64*hf .. 64*hf+63 of both
-        float* dk = ptrs.dkv[cta.dkv_dev] + ((size_t(cta.dkv_row + r) * 2 + 0) * hkv + kv_head) * kHeadDim + hf * 64;
-        float* dv = ptrs.dkv[cta.dkv_dev] + ((size_t(cta.dkv_row + r) * 2 + 1) * hkv + kv_head) * kHeadDim + hf * 64;
+        // dK / dV: lane = key row; this warp adds channels 32*hf .. 32*hf+31 of both
+        float* dk = ptrs.dkv[cta.dkv_dev] + ((size_t(cta.dkv_row + r) * 2 + 0) * hkv + kv_head) * kHeadDim + hf * 32;
+        float* dv = ptrs.dkv[cta.dkv_dev] + ((size_t(cta.dkv_row + r) * 2 + 1) * hkv + kv_head) * kHeadDim + hf * 32;
+        uint32_t reg[32];
+        tmem_ld32(tmem + lane_base + cdK + hf * 32, reg);
+        tmem_wait_ld();
+        if (key_valid) {
 #pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          uint32_t reg[32];
-          tmem_ld32(tmem + lane_base + cdK + hf * 64 + c * 32, reg);
-          tmem_wait_ld();
-          if (key_valid) {
+          for (int i = 0; i < 8; ++i)
+            red_add_v4(dk + 4 * i, __uint_as_float(reg[4 * i]), __uint_as_float(reg[4 * i + 1]),
+                       __uint_as_float(reg[4 * i + 2]), __uint_as_float(reg[4 * i + 3]));
+        }
+        tmem_ld32(tmem + lane_base + cdV + hf * 32, reg);
+        tmem_wait_ld();
+        if (key_valid) {
 #pragma unroll
-            for (int i = 0; i < 8; ++i)
-              red_add_v4(dk + c * 32 + 4 * i, __uint_as_float(reg[4 * i]), __uint_as_float(reg[4 * i + 1]),
-                         __uint_as_float(reg[4 * i + 2]), __uint_as_float(reg[4 * i + 3]));
-          }
-          tmem_ld32(tmem + lane_base + cdV + hf * 64 + c * 32, reg);
-          tmem_wait_ld();
-          if (key_valid) {
-#pragma unroll
-            for (int i = 0; i < 8; ++i)
-              red_add_v4(dv + c * 32 + 4 * i, __uint_as_float(reg[4 * i]), __uint_as_float(reg[4 * i + 1]),
-                         __uint_as_float(reg[4 * i + 2]), __uint_as_float(reg[4 * i + 3]));
-          }
+          for (int i = 0; i < 8; ++i)
+            red_add_v4(dv + 4 * i, __uint_as_float(reg[4 * i]), __uint_as_float(reg[4 * i + 1]),
+                       __uint_as_float(reg[4 * i + 2]), __uint_as_float(reg[4 * i + 3]));
         }
       }
     }
@@ -519,7 +518,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 9) {
+  if (warp == 17) {
     tc_fence_after();
     tmem_dealloc(tmem, 512);
   }
@@ -587,7 +586,7 @@ extern "C" int dcpk_attn_bwd(const void* q_arena, const void* do_arena, long q_r
   if (n_ctas <= 0) return n_jobs > 0 ? -6 : 0;   // copy jobs need a kernel to ride on
   if (n_dst > kMaxPeers || hq % hkv != 0) return -3;
   CUtensorMap tm_q, tm_do, tm_kv, tm_dq;
-  if (encode_f32_tile_map(&tm_dq, dq_ptrs[0], uint64_t(q_rows), uint32_t(hq), kHeadDim, 16, 32)) return -1;
+  if (encode_f32_tile_map(&tm_dq, dq_ptrs[0], uint64_t(q_rows), uint32_t(hq), kHeadDim, 8, 32)) return -1;
   if (encode_arena_map(&tm_q, q_arena, uint64_t(q_rows), uint32_t(hq), kHeadDim, kQTile)) return -1;
   if (encode_arena_map(&tm_do, do_arena, uint64_t(q_rows), uint32_t(hq), kHeadDim, kQTile)) return -1;
   if (encode_arena_map(&tm_kv, kv_arena, uint64_t(kv_rows), uint32_t(2 * hkv), kHeadDim, 128)) return -1;

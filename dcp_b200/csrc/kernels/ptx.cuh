@@ -209,6 +209,15 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t* r) {
       : "memory");
 }
 
+// 8-column variant
+__device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+      : "r"(taddr)
+      : "memory");
+}
+
 // ---------------------------------------------------------------- descriptors
 // Instruction descriptor for kind::f16 with bf16 A/B and fp32 accumulate.
 // Bit layout: [4,6) D format (1 = f32); [7,10) A format (1 = bf16); [10,13) B format;

@@ -149,10 +149,16 @@ class TrainEngine:
             from .data.kv_store import KVServer, KVStore
             host = os.environ.get("DCP_KV_HOST", os.environ.get("MASTER_ADDR", "127.0.0.1"))
             port = int(os.environ.get("DCP_KV_PORT", int(os.environ.get("MASTER_PORT", "29500")) + 29))
+            ok = [True]
             if self.rank == 0:
-                self._kv_server = KVServer(host, port)
-            dist.barrier(group=world_group)
-            self._kv = KVStore(host, port, timeout_s=600.0)
+                try:
+                    self._kv_server = KVServer(host, port)
+                except Exception as e:      # port taken, no permission, ...: every rank plans for itself instead
+                    print(f"[dcp] shared planning disabled: cannot open the plan store on {host}:{port} ({e!r})", flush=True)
+                    ok = [False]
+            dist.broadcast_object_list(ok, src=dist.get_global_rank(world_group, 0), group=world_group)
+            if ok[0]:
+                self._kv = KVStore(host, port, timeout_s=600.0)
         self.plans = self._make_plan_service(0)
         self.samples_consumed = 0       # dataset samples trained on (checkpointed for the batch sampler)
         self.iteration = 0
