@@ -114,6 +114,8 @@ def parse_args(argv=None):
     ap.add_argument("--stages", type=int, default=None)
     ap.add_argument("--lookahead", type=int, default=3, help="iterations the planner works ahead")
     ap.add_argument("--planner-workers", type=int, default=2)
+    ap.add_argument("--no-verify", action="store_true",
+                    help="skip the numerical self-check of the cross-GPU attention path (runs on 2 or more GPUs)")
     ap.add_argument("--no-extras", action="store_true",
                     help="at 8 GPUs: skip the two 131072-token configurations and the attention microbenchmark")
     ap.add_argument("--activation-budget-gb", type=float, default=None,
@@ -190,6 +192,14 @@ def main() -> None:
     dev = torch.device("cuda", local)
     cfg, scaling = build_engine_config(args, world)
     tokens, dist_, mask = cfg.tokens_per_step, cfg.length_dist, cfg.mask
+    # on two or more GPUs: the cross-GPU attention path (peer operand fetch, partial-result stores,
+    # merge, gradient push) is compared once with dense fp64 attention before anything is timed
+    verify = None
+    if world > 1 and not args.no_verify:
+        from dcp_b200.runtime.selfcheck import fused_self_check
+        verify = fused_self_check(rank, world, group)
+        if not verify["passed"]:
+            raise RuntimeError(f"fused attention self-check failed: {verify}")
     eng = TrainEngine(cfg, dev, group)
     W, K = args.warmup, args.steps
 
@@ -312,6 +322,8 @@ def main() -> None:
                     "planner_wait_s_in_region": round(wait_sum, 3)},
             "gpu_launches": int(launches), "final_loss": last_loss,
         }
+        if verify is not None:
+            out["verify"] = verify
         if attn_micro is not None:
             out["attn_microbench_131k_causal"] = attn_micro
         if extra:

@@ -78,6 +78,39 @@ def shard_layout(buckets: Sequence[Tuple[int, int]], world: int, rank: int) -> L
     return out
 
 
+def reshard_state(old_states, buckets: Sequence[Tuple[int, int]], new_world: int, new_rank: int) -> dict:
+    """Optimizer state of rank ``new_rank`` of a group of ``new_world`` ranks, cut out of the state
+    dictionaries written by a group of another size (resume on a different number of GPUs).
+
+    ``old_states`` yields the ``state_dict()`` of every old rank, in any order and one at a time (a
+    generator that loads one checkpoint file per item keeps a single file in host memory); each
+    names its own ``rank`` and ``world``.  For every bucket the new rank's slice is filled from the
+    overlapping parts of the old ranks' slices, both located with ``shard_layout``."""
+    buckets = [tuple(b) for b in buckets]
+    mine = shard_layout(buckets, new_world, new_rank)
+    n = sum(s.length for s in mine)
+    out = {k: torch.zeros(n, dtype=torch.float32) for k in ("master", "m", "v")}
+    filled, step, seen = 0, None, set()
+    for sd in old_states:
+        assert [tuple(b) for b in sd["buckets"]] == buckets, "checkpoint was written with other gradient buckets"
+        assert sd["rank"] not in seen, f"old rank {sd['rank']} given twice"
+        seen.add(sd["rank"])
+        step = int(sd["step"]) if step is None else step
+        assert step == int(sd["step"]), "checkpoint files of different steps"
+        for new, old in zip(mine, shard_layout(buckets, sd["world"], sd["rank"])):
+            lo, hi = max(new.flat_off, old.flat_off), min(new.flat_off + new.length, old.flat_off + old.length)
+            if hi <= lo:
+                continue
+            dst = slice(new.state_off + lo - new.flat_off, new.state_off + hi - new.flat_off)
+            src = slice(old.state_off + lo - old.flat_off, old.state_off + hi - old.flat_off)
+            for k in out:
+                out[k][dst] = sd[k][src].to("cpu", torch.float32)
+            filled += hi - lo
+        old_world = sd["world"]
+    assert seen == set(range(old_world)) and filled == n, "the old ranks' files do not cover this rank's slices"
+    return {**out, "step": step, "buckets": buckets, "world": new_world, "rank": new_rank}
+
+
 class ShardedAdamW:
     def __init__(self, bufs: FlatBuffers, lr: float = 3e-4, betas=(0.9, 0.95), eps: float = 1e-8,
                  weight_decay: float = 0.1, clip_grad: Optional[float] = 1.0, group=None, tp_group=None,

@@ -1,22 +1,74 @@
 """Symmetric (peer-mapped) device memory for the fused executor.
 
-One byte arena per rank is allocated through ``torch.distributed._symmetric_memory`` and
-rendezvoused once, which gives every rank the device address of every peer's arena over
-NVLink.  Named regions are carved at identical offsets on all ranks, so "region X of rank r" is
-``ptrs[r] + offset(X)`` everywhere.  With a single rank the arena is ordinary device memory.
+One byte arena per rank is allocated and mapped once into every peer, which gives every rank the
+device address of every peer's arena over NVLink.  Two allocation routes exist:
+``torch.distributed._symmetric_memory`` (allocate + rendezvous; the default where that module has
+``empty`` and ``rendezvous``) and CUDA IPC handles through the in-tree library (``dcpk_ipc_*``:
+cudaMalloc, handle exchange over the process group, cudaIpcOpenMemHandle), taken when the module is
+missing or when ``DCP_B200_PEER_MEMORY=ipc``.  Named regions are carved at identical offsets on all
+ranks, so "region X of rank r" is ``ptrs[r] + offset(X)`` everywhere.  With a single rank the arena
+is ordinary device memory.
 
 Cross-GPU synchronisation uses a flag row per rank inside the arena and the bounded
 ``signal_barrier`` kernel: a peer that never arrives turns into a status code, not a hang.
 """
 from __future__ import annotations
 
+import ctypes
+import os
 from typing import Dict, List, Tuple
 
 import torch
 
-from ..ops import block_ops
+from ..ops import _lib, block_ops
 
 _ALIGN = 1024
+
+
+def peer_memory_route() -> str:
+    """"symm" or "ipc": which of the two routes ``SymmetricArena`` takes in this process."""
+    want = os.environ.get("DCP_B200_PEER_MEMORY", "").lower()
+    if want in ("symm", "ipc"):
+        return want
+    try:
+        import torch.distributed._symmetric_memory as symm_mem
+        return "symm" if hasattr(symm_mem, "empty") and hasattr(symm_mem, "rendezvous") else "ipc"
+    except ImportError:
+        return "ipc"
+
+
+class _RawDeviceBuffer:
+    """Device memory owned by the in-tree library, exposed to torch through the CUDA array interface."""
+
+    def __init__(self, ptr: int, nbytes: int):
+        self.ptr, self.nbytes = ptr, nbytes
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 2}
+
+
+def _ipc_allocate(nbytes: int, device: torch.device, group):
+    """(own buffer as a uint8 tensor, device addresses of every rank's buffer, owner object)."""
+    import torch.distributed as dist
+    lib = _lib.load()
+    world, rank = dist.get_world_size(group), dist.get_rank(group)
+    with torch.cuda.device(device):
+        ptr, handle = ctypes.c_void_p(), ctypes.create_string_buffer(64)
+        rc = lib.dcpk_ipc_alloc(ctypes.c_size_t(nbytes), ctypes.byref(ptr), handle)
+        if rc != 0:
+            raise RuntimeError(f"dcpk_ipc_alloc({nbytes}) failed with code {rc}")
+        handles = [None] * world
+        dist.all_gather_object(handles, bytes(handle.raw), group=group)
+        ptrs = []
+        for r, h in enumerate(handles):
+            if r == rank:
+                ptrs.append(int(ptr.value))
+                continue
+            peer = ctypes.c_void_p()
+            rc = lib.dcpk_ipc_open(ctypes.create_string_buffer(h, 64), ctypes.byref(peer))
+            if rc != 0:
+                raise RuntimeError(f"dcpk_ipc_open of rank {r}'s buffer failed with code {rc}")
+            ptrs.append(int(peer.value))
+    owner = _RawDeviceBuffer(int(ptr.value), nbytes)
+    return torch.as_tensor(owner, device=device), ptrs, owner
 
 
 class SymmetricArena:
@@ -44,7 +96,11 @@ class SymmetricArena:
         self.offsets["__flags__"] = off
         off += _ALIGN
         self.nbytes = off
-        if self.world > 1:
+        self.route = peer_memory_route() if self.world > 1 else "local"
+        if self.route == "ipc":
+            # buffers live until the process exits: peers may still hold mappings of them
+            self.buf, self.ptrs, self.handle = _ipc_allocate(self.nbytes, device, group)
+        elif self.world > 1:
             import torch.distributed._symmetric_memory as symm_mem
             self.buf = symm_mem.empty(self.nbytes, dtype=torch.uint8, device=device)
             self.buf.zero_()

@@ -284,15 +284,39 @@ class TrainEngine:
         return path
 
     def load_checkpoint(self, directory: str) -> None:
-        path = os.path.join(directory, f"rank{self.rank:03d}.pt")
-        state = torch.load(path, map_location=self.device, weights_only=False)
-        assert state["world"] == self.world and state.get("tp_size", 1) == self.tp_size, \
-            "resume needs the world size and tensor-parallel size the checkpoint was written with"
-        self.optimizer.load_state_dict(state["optimizer"])
+        """Resume from ``save_checkpoint`` files.  The number of ranks may differ from the run that
+        wrote them as long as the tensor-parallel size is the same: the sharded fp32 optimizer state
+        is then re-cut from the files of the old ranks that held this rank's parameters (the
+        directory must be readable by every rank), and the random-number state starts afresh."""
+        probe = os.path.join(directory, f"rank{self.rank:03d}.pt")
+        if not os.path.exists(probe):
+            probe = os.path.join(directory, "rank000.pt")
+        meta = torch.load(probe, map_location="cpu", weights_only=False, mmap=True)
+        assert meta.get("tp_size", 1) == self.tp_size, "resume needs the tensor-parallel size the checkpoint was written with"
+        old_world = int(meta["world"])
+        if old_world == self.world:
+            state = torch.load(os.path.join(directory, f"rank{self.rank:03d}.pt"), map_location=self.device,
+                               weights_only=False)
+            self.optimizer.load_state_dict(state["optimizer"])
+            torch.set_rng_state(state["rng"].cpu())
+            torch.cuda.set_rng_state(state["cuda_rng"].cpu(), self.device)
+        else:
+            from .parallel.dist_optimizer import reshard_state
+            tp = self.tp_size
+            tp_index = self.rank % tp
+            old_group = [c * tp + tp_index for c in range(old_world // tp)]   # old ranks with this rank's parameters
+            state = meta
+
+            def old_states():
+                for r in old_group:
+                    f = torch.load(os.path.join(directory, f"rank{r:03d}.pt"), map_location="cpu", weights_only=False,
+                                   mmap=True)
+                    yield f["optimizer"]
+
+            o = self.optimizer
+            self.optimizer.load_state_dict(reshard_state(old_states(), o.buckets, o.bufs.world, o.bufs.rank))
         self.iteration = int(state["iteration"])
         self.samples_consumed = int(state.get("samples_consumed", 0))
-        torch.set_rng_state(state["rng"].cpu())
-        torch.cuda.set_rng_state(state["cuda_rng"].cpu(), self.device)
         # every rank's bf16 parameters are rebuilt from the sharded fp32 master weights: each rank
         # stores its slices (same slicing formula as the optimizer) into every peer's buffer
         self.optimizer.rebuild_params()

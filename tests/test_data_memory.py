@@ -318,6 +318,33 @@ def test_optimizer_shard_layout_covers_every_bucket_for_any_world_size():
                 acc += s.length
 
 
+def test_optimizer_state_is_recut_for_another_world_size():
+    """Resume on a different number of ranks: the state of every new rank, cut out of the old ranks'
+    state dictionaries, equals the slice of the full state that the new layout gives it."""
+    import torch
+    from dcp_b200.parallel.dist_optimizer import reshard_state, shard_layout
+    buckets = [(0, 4096), (4096, 8 * 1001), (4096 + 8 * 1001, 8), (4096 + 8 * 1002, 8 * 3333)]
+    n = sum(b[1] for b in buckets)
+    full = {k: torch.randn(n) for k in ("master", "m", "v")}
+
+    def state_of(world, rank):
+        parts = {k: torch.cat([full[k][s.flat_off:s.flat_off + s.length] for s in shard_layout(buckets, world, rank)])
+                 for k in full}
+        return {**parts, "step": 7, "buckets": buckets, "world": world, "rank": rank}
+
+    for old_world, new_world in ((8, 2), (2, 8), (3, 5), (6, 1), (1, 7)):
+        for new_rank in range(new_world):
+            got = reshard_state((state_of(old_world, r) for r in reversed(range(old_world))), buckets, new_world, new_rank)
+            want = state_of(new_world, new_rank)
+            assert got["step"] == 7 and got["world"] == new_world and got["rank"] == new_rank
+            for k in full:
+                assert torch.equal(got[k], want[k]), (old_world, new_world, new_rank, k)
+    # a missing old rank is an error, not a silently zero-filled slice
+    import pytest
+    with pytest.raises(AssertionError):
+        reshard_state((state_of(4, r) for r in (0, 1, 3)), buckets, 2, 1)
+
+
 def test_shared_planning_gives_every_rank_the_plan_it_would_compute_itself():
     """One planner (rank 0) plans every batch once in its worker pool and publishes per-rank shares in
     a key-value store; the other ranks only read.  Every rank must receive exactly the plan it would

@@ -39,6 +39,19 @@ def test_fused_executor_multi_gpu(world):
     assert res.returncode == 0 and "FUSED_OK" in res.stdout, res.stdout[-3000:]
 
 
+def test_fused_executor_two_gpus_over_ipc_mapped_memory():
+    """The second peer-memory route: arenas allocated by the in-tree library and mapped into the
+    peer through CUDA IPC handles instead of the framework's symmetric-memory module."""
+    _need_gpu()
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
+           "127.0.0.1", "--master-port", "29553", os.path.join(ROOT, "tests", "fused_worker.py")]
+    res = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=900,
+                         env=dict(os.environ, PYTHONPATH=ROOT, DCP_B200_PEER_MEMORY="ipc"))
+    assert res.returncode == 0 and "FUSED_OK" in res.stdout, res.stdout[-3000:]
+
+
 def test_overlapped_sharded_optimizer_two_gpus():
     """Bucketed reduce-scatter on a side stream + sharded AdamW + all-gather against fp32
     torch.optim.AdamW on the rank-summed gradients, parameter rebuild from the master shards, and
@@ -132,6 +145,32 @@ def test_checkpoint_resume_continues_identically(tmp_path):
     got = b.train_step()
     assert abs(got - want) <= 1e-5 * max(1.0, abs(want)), (got, want)
     a.close(); b.close()
+
+
+def test_checkpoint_written_by_two_ranks_resumes_on_one(tmp_path):
+    """Resume on another number of GPUs: two ranks train two steps and save; one engine loads the
+    files, re-cuts the sharded fp32 optimizer state and rebuilds exactly the bf16 parameters that
+    the two ranks held, then trains on."""
+    _need_gpu()
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
+           "127.0.0.1", "--master-port", "29567", os.path.join(ROOT, "tests", "ckpt_worker.py"), str(tmp_path)]
+    res = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=600,
+                         env=dict(os.environ, PYTHONPATH=ROOT))
+    assert res.returncode == 0 and "CKPT_OK" in res.stdout, res.stdout[-3000:]
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    from ckpt_worker import engine_config
+    from dcp_b200.train import TrainEngine
+    dev = torch.device("cuda", 0)
+    eng = TrainEngine(engine_config(), dev)
+    eng.load_checkpoint(str(tmp_path))
+    saved = torch.load(os.path.join(str(tmp_path), "rank000.pt"), map_location=dev, weights_only=False)
+    assert eng.iteration == 2 and eng.optimizer.step_count == saved["optimizer"]["step"]
+    assert torch.equal(eng.bufs.params, saved["params_bf16"])
+    loss = eng.train_step()
+    assert loss == loss
+    eng.close()
 
 
 def test_loss_trajectory_matches_fp32_pytorch_training():
