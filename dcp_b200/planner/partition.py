@@ -184,17 +184,68 @@ def construct_and_partition_graph_multiconstraint(
     else:
         node_part, km1 = _solve(graph.vw_comp, graph.vw_mem, graph.net_offsets, graph.net_pins, graph.net_weight,
                                 n_nodes, mem_epsilon, comp_epsilon * inter_node_comp_epsilon_factor, seed, n_tries)
+        n_orphans = 0
         for node in range(n_nodes):
-            verts = [v for v, p in enumerate(node_part) if p == node]
-            if not verts:
-                continue
-            vc, vm, off, pins, wts = graph.sub(verts)
-            part, _ = _solve(vc, vm, off, pins, wts, dpn, mem_epsilon, comp_epsilon, seed + node + 1, n_tries)
-            for v, p in zip(verts, part):
-                vertex_dev[v] = (node, p)
+            prob = second_level_problem(graph, node_part, node)
+            if prob.vertices:
+                vc, vm, off, pins, wts = graph.sub(prob.vertices)
+                for i in range(len(prob.vertices) - prob.n_foreign, len(prob.vertices)):
+                    vm[i] = 1                  # held by another node: no memory here, free to sit with its users
+                part, _ = _solve(vc, vm, off, pins, wts, dpn, mem_epsilon, comp_epsilon, seed + node + 1, n_tries)
+                for v, p in zip(prob.vertices[:len(prob.vertices) - prob.n_foreign], part):
+                    vertex_dev[v] = (node, p)
+            n_orphans += len(prob.orphans)
+            place_orphans(graph, prob.orphans, node, dpn, vertex_dev, node_part)
+        if logger is not None:
+            logger.debug("second level: %d data groups needed only by other nodes placed by memory", n_orphans)
     if logger is not None:
         logger.debug("placement km1=%d (x%d bytes)", km1, BYTE_UNIT)
     return _materialise(context, workload, graph, vertex_dev)
+
+
+class SecondLevelProblem:
+    """Per-node placement problem of the two-level (multi-node) scheme.
+
+    ``vertices``: the node's work units, then the node's data groups that its own work touches, then
+    (the last ``n_foreign`` entries) data groups held by OTHER nodes that this node's work reads or
+    writes.  The foreign groups take part with memory weight 1 only: they do not occupy memory on
+    this node, but keeping them in the nets makes every device that needs such a block count in
+    the connectivity objective, exactly as a local block would.  ``orphans``: data groups assigned
+    to this node that none of its own work touches (only other nodes need them); no net of the
+    per-node problem reaches them, so they are placed afterwards by memory alone.
+    (dcp/graph_partition/graph.py:239-250 foreign weights, :1240-1362 manual assignment.)"""
+
+    def __init__(self, vertices: List[int], n_foreign: int, orphans: List[int]):
+        self.vertices, self.n_foreign, self.orphans = vertices, n_foreign, orphans
+
+
+def second_level_problem(graph: "PlacementGraph", node_part: Sequence[int], node: int) -> SecondLevelProblem:
+    n_work = graph.n_work
+    touched = set()                 # data-group vertices used by work of this node
+    for e in range(len(graph.net_weight)):
+        pins = graph.net_pins[graph.net_offsets[e]:graph.net_offsets[e + 1]]
+        data = [p for p in pins if p >= n_work]
+        if any(p < n_work and node_part[p] == node for p in pins):
+            touched.update(data)
+    work = [v for v in range(n_work) if node_part[v] == node]
+    own_data = [v for v in range(n_work, graph.n_vertices) if node_part[v] == node]
+    local = [v for v in own_data if v in touched]
+    orphans = [v for v in own_data if v not in touched]
+    foreign = sorted(v for v in touched if node_part[v] != node)
+    return SecondLevelProblem(work + local + foreign, len(foreign), orphans)
+
+
+def place_orphans(graph: "PlacementGraph", orphans: Sequence[int], node: int, dpn: int, vertex_dev: List[Device],
+                  node_part: Sequence[int]) -> None:
+    """Largest first, each onto the device of ``node`` that holds the least memory so far."""
+    mem, skip = [0] * dpn, set(orphans)
+    for v in range(graph.n_work, graph.n_vertices):
+        if node_part[v] == node and v not in skip:
+            mem[vertex_dev[v][1]] += graph.vw_mem[v]
+    for v in sorted(orphans, key=lambda v: (-graph.vw_mem[v], v)):
+        d = mem.index(min(mem))
+        vertex_dev[v] = (node, d)
+        mem[d] += graph.vw_mem[v]
 
 
 def _rebalance_compute(workload: WorkloadSpec, graph: "PlacementGraph", vertex_dev: List[Device], devices,

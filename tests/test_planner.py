@@ -192,6 +192,88 @@ def test_compiled_plans_validate(mask, n_dev, n_nodes, hbs):
                                                  if m.type == "Q" and fw_wl.input_to_device_map[i] == d)
 
 
+def test_second_level_problem_foreign_blocks_and_orphans():
+    """Two-level placement: the per-node problem holds the node's work, the node's data its work
+    touches and (weight 1) the other nodes' data it touches; data of the node that only other nodes
+    use is placed afterwards on the emptiest device.  The full placement keeps every block on the
+    node the first level chose and the plans still compute dense attention (checked elsewhere)."""
+    from dcp_b200.planner.partition import PlacementGraph, place_orphans, second_level_problem
+    ctx = get_default_execution_context(4, 2)
+    wl, _, _ = _workload([1024, 512, 256], 128, hbs=4, mask="causal", ctx=ctx)
+    g = PlacementGraph(wl)
+    # all work on node 0; the data groups alternate between the nodes
+    node_part = [0] * g.n_work + [(v - g.n_work) % 2 for v in range(g.n_work, g.n_vertices)]
+    p0, p1 = second_level_problem(g, node_part, 0), second_level_problem(g, node_part, 1)
+    data1 = [v for v in range(g.n_work, g.n_vertices) if node_part[v] == 1]
+    assert p0.orphans == [] and p0.n_foreign == len(data1) and p0.vertices[-p0.n_foreign:] == data1
+    assert p1.vertices == [] and p1.orphans == data1          # node 1 computes nothing: all its data are orphans
+    vertex_dev = [(0, 0)] * g.n_vertices
+    place_orphans(g, p1.orphans, 1, 2, vertex_dev, node_part)
+    loads = [sum(g.vw_mem[v] for v in data1 if vertex_dev[v] == (1, d)) for d in range(2)]
+    assert all(vertex_dev[v][0] == 1 for v in data1) and abs(loads[0] - loads[1]) <= max(g.vw_mem[v] for v in data1)
+    # a full two-level placement: complete, and every co-location group sits on one device
+    d2w, d2i, d2o = construct_and_partition_graph_multiconstraint(ctx, wl)
+    assert sorted(w for ws in d2w.values() for w in ws) == list(range(len(wl.workloads)))
+    assert sorted(i for v in d2i.values() for i in v) == list(range(len(wl.input_sizes)))
+    for ins, outs in wl.colocation_constraints:
+        assert len({wl.input_to_device_map[i] for i in ins} | {wl.output_to_device_map[o] for o in outs}) == 1
+
+
+def test_tree_packing_is_optimal_on_small_instances():
+    """The branch-and-bound packer against exhaustive enumeration of every tree combination, with
+    free and with fixed arrival stages; it never does worse than the greedy packing it starts from."""
+    import itertools
+    import random
+    from dcp_b200.planner.steiner import pack_multicast_trees, packing_cost
+
+    def all_trees(req, n_stages, arrival):
+        blk, src, dsts, _ = req
+        out = set()
+
+        def rec(have, rem, edges):
+            if not rem:
+                out.add(tuple(sorted(edges)))
+                return
+            for d in rem:
+                for h, got in have.items():
+                    stages = range(got + 1, n_stages) if arrival is None else [arrival[(blk, d)]]
+                    for st in stages:
+                        if st > got:
+                            rec({**have, d: st}, [x for x in rem if x != d], edges + [(st, h, d)])
+        rec({src: -1}, sorted(set(dsts) - {src}), [])
+        return sorted(out)
+
+    rng = random.Random(3)
+    improved = 0
+    for trial in range(30):
+        n_nodes, n_stages = rng.choice([3, 4]), rng.choice([2, 3])
+        reqs = []
+        for b in range(rng.choice([2, 3])):
+            src = rng.randrange(n_nodes)
+            dsts = set(rng.sample(range(n_nodes), rng.choice([2, 3]))) - {src} or {(src + 1) % n_nodes}
+            reqs.append((b, src, dsts, float(rng.choice([1, 2, 3, 5]))))
+        arrival = None if trial % 2 == 0 else {(b, d): rng.randrange(n_stages) for b, _, ds, _ in reqs for d in ds}
+        trees, info = pack_multicast_trees(reqs, n_nodes, n_stages, arrival=arrival, return_info=True)
+        want = min(packing_cost({r[0]: list(t) for r, t in zip(reqs, combo)}, reqs, n_nodes, n_stages)
+                   for combo in itertools.product(*[all_trees(r, n_stages, arrival) for r in reqs]))
+        assert info["proven_optimal"] and info["cost"] == pytest.approx(want)
+        assert packing_cost(trees, reqs, n_nodes, n_stages) == pytest.approx(info["cost"])
+        assert info["cost"] <= info["greedy_cost"] + 1e-9
+        improved += info["cost"] < info["greedy_cost"] - 1e-9
+        for b, src, dsts, _ in reqs:                  # every destination reached once, from a node that holds the block
+            got = {src: -1}
+            for st, h, d in sorted(trees[b]):
+                assert h in got and got[h] < st and d not in got
+                got[d] = st
+                assert arrival is None or arrival[(b, d)] == st
+            assert set(got) == set(dsts) | {src}
+    assert improved > 0
+    # a budget that is too small still returns a valid packing, marked as not proven
+    big = [(b, rng.randrange(8), set(rng.sample(range(8), 4)), 1.0 + b % 3) for b in range(30)]
+    _, info = pack_multicast_trees(big, 8, 4, search_budget=200, return_info=True)
+    assert not info["proven_optimal"] and info["cost"] <= info["greedy_cost"]
+
+
 def test_block_size_heuristic_and_cost_models():
     assert block_size_heuristic([100000, 300, 200], 8, 0.2) < block_size_heuristic([8000] * 8, 8, 0.2)
     assert block_size_heuristic([8192] * 8, 8) == 8192
