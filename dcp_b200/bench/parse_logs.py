@@ -1,5 +1,5 @@
-"""Log parsers and result tables (CSV / JSON instead of the reference's matplotlib figures,
-benchmark/plotting/utils.py:10-31, plot_microbenchmark_results.py:380-399).
+"""Log parsers and result tables (benchmark/plotting/utils.py:10-31,
+plot_microbenchmark_results.py:380-399); ``bench/plotting.py`` draws the figures from them.
 
 * training logs: mean "elapsed time per iteration (ms)" skipping the first two log lines, and the
   "Training loss:" curve;

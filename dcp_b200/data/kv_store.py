@@ -1,8 +1,9 @@
 """Small key-value control plane.
 
-Plans never travel through it (every rank plans deterministically for itself); it carries control
-state for multi-process jobs: iteration counts, abort flags, experiment barriers.  In-process it
-is a dict guarded by a condition variable; across processes it wraps ``torch.distributed.TCPStore``.
+It carries the planner's published per-rank plans (shared planning: one planner, every rank reads
+its share; values above the store's payload limit travel in pieces) and control state for
+multi-process jobs: iteration counts, abort flags, experiment barriers.  In-process it is a dict
+guarded by a condition variable; across processes it wraps ``torch.distributed.TCPStore``.
 Blocking ``get`` calls take a timeout and raise instead of polling forever (the reference's Redis
 client polls without one, dcp/data/kv_redis.py:22-135).
 """

@@ -35,6 +35,81 @@ def test_grid_runner_detects_failure_and_stall(tmp_path):
     assert (ok, bad, stalled) == ("ok", "failed", "stalled")
 
 
+def test_grid_runner_two_nodes_lock_step(tmp_path):
+    """Two runner processes act as two nodes: node 0 publishes the cell through the key-value server,
+    both launch their share under torch.distributed.run (one rank each, gloo all-reduce across the
+    nodes), node 0 gathers the statuses and writes the summary."""
+    import subprocess
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    base = [sys.executable, "-m", "dcp_b200.bench.run_experiments", "--kind", "selftest", "--gpus", "1", "--nnodes", "2",
+            "--coordinator", "127.0.0.1:29733", "--base-port", "29735", "--out", str(tmp_path), "--batches", "1"]
+    env = dict(os.environ, PYTHONPATH=root)
+    procs = [subprocess.Popen(base + ["--node-rank", str(r)], env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT,
+                              text=True) for r in (0, 1)]
+    outs = [p.communicate(timeout=300)[0] for p in procs]
+    assert all(p.returncode == 0 for p in procs), outs
+    rows = list(__import__("csv").DictReader(open(tmp_path / "summary.csv")))
+    assert len(rows) == 1 and rows[0]["status"] == "ok" and float(rows[0]["ms_per_batch_Selftest"]) > 0
+    assert (tmp_path / "kind-selftest_gpus-1.node1.log").exists()
+
+
+def test_grid_runner_abort_reaches_the_other_node(tmp_path):
+    """A cell that one node gives up is ended on the other node too: the second node's child would
+    sleep for a minute, but its watchdog sees the abort key."""
+    import threading
+    import time
+    from dcp_b200.data.kv_store import KVStore
+    from dcp_b200.bench.run_experiments import NodeCoordinator, overall_status
+    store = KVStore()
+    a, b = NodeCoordinator(store, 0, 2), NodeCoordinator(store, 1, 2)
+    result = {}
+
+    def node_b():
+        result["b"] = run_cell([sys.executable, "-c", "import time; time.sleep(60)"], str(tmp_path / "b.log"),
+                               no_progress_s=120, abort_check=lambda: b.aborted(0))
+        b.report(0, result["b"])
+
+    t = threading.Thread(target=node_b)
+    t0 = time.time()
+    t.start()
+    a.report(0, run_cell([sys.executable, "-c", "raise SystemExit(3)"], str(tmp_path / "a.log")))
+    t.join(timeout=60)
+    assert not t.is_alive() and result["b"] == "aborted" and time.time() - t0 < 45
+    assert a.gather(0) == ["failed", "aborted"] and overall_status(a.gather(0)) == "failed"
+    assert overall_status(["ok", "ok"]) == "ok" and overall_status(["aborted", "stalled"]) == "stalled"
+
+
+def test_figures_are_written_as_svg(tmp_path):
+    """The four figures (microbenchmark bars, iteration-time bars, loss curves, dry-run lines) from
+    the runner's tables: well-formed SVG with one bar / line per data point / series."""
+    import xml.etree.ElementTree as ET
+    from dcp_b200.bench import plotting
+    rows = [{"kind": "attention", "framework": fw, "mask": m, "length_dist": "lognormal8k", "block_size": 2048,
+             "status": "ok", "ms_per_batch_Forward": 5.0 + i, "ms_per_batch_Backward": 9.0 + i}
+            for i, (fw, m) in enumerate([("dcp", "causal"), ("ring", "causal"), ("ulysses", "causal"), ("dcp", "lambda")])]
+    rows.append(dict(rows[0], framework="zigzag", status="failed"))          # failed cells are left out
+    rows += [{"kind": "train", "mask": "causal", "length_dist": "mixture", "block_size": bs, "ms_per_iteration": 4000 + bs}
+             for bs in (1024, 2048)]
+    parse_logs.write_table(rows, str(tmp_path / "summary.csv"))
+    ns = {"s": "http://www.w3.org/2000/svg"}
+    plotting.main(["microbench", str(tmp_path / "summary.csv"), "--out", str(tmp_path / "mb.svg")])
+    root = ET.parse(tmp_path / "mb.svg").getroot()
+    assert len(root.findall(".//s:rect[@class='bar']", ns)) == 4
+    plotting.main(["e2e", str(tmp_path / "summary.csv"), "--out", str(tmp_path / "e2e.svg")])
+    assert len(ET.parse(tmp_path / "e2e.svg").getroot().findall(".//s:rect[@class='bar']", ns)) == 2
+    for name, shift in (("a.log", 0.0), ("b.log", 0.01)):
+        (tmp_path / name).write_text("".join(f"Training loss: {10 - 0.1 * i + shift}\n" for i in range(20)))
+    plotting.main(["loss", str(tmp_path / "a.log"), str(tmp_path / "b.log"), "--out", str(tmp_path / "loss.svg")])
+    lines = ET.parse(tmp_path / "loss.svg").getroot().findall(".//s:polyline[@class='line']", ns)
+    assert len(lines) == 2 and len(lines[0].get("points").split()) == 20
+    json.dump({"cells": [{"mask": "causal", "length_dist": "mixture", "n_stages": 4, "block_size": b,
+                          "modelled_pipeline_ms": 10.0 + b / 1024} for b in (1024, 2048, 4096)]},
+              open(tmp_path / "dry.json", "w"))
+    plotting.main(["dryrun", str(tmp_path / "dry.json"), "--out", str(tmp_path / "dry.svg")])
+    assert len(ET.parse(tmp_path / "dry.svg").getroot().findall(".//s:polyline[@class='line']", ns)) == 1
+    assert plotting._nice_ticks(0, 17.3)[-1] >= 17.3 and plotting._nice_ticks(3, 3)[0] <= 3
+
+
 def test_replay_of_saved_plans(tmp_path):
     import torch
     from dcp_b200.bench.replay import replay_plans
