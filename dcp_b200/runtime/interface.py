@@ -109,7 +109,15 @@ class FusedPlanExecutor:
         the placed and staged workload, which every rank holds."""
         from ..planner.lowering import lower_all, lower_plans
         from .executor_fused import FusedAttentionExecutor
-        assert head_dim == 128, "the sm_100a attention kernels are built for head_dim 128"
+        # The sm_100a kernels are built for 128 channels per head in bf16.  Smaller head dimensions run
+        # on them zero-padded to 128: padded Q/K columns add nothing to the scores, padded V / dO
+        # columns give zero output and gradient columns, which are cut off again; the softmax scale
+        # stays 1/sqrt(head_dim).  fp16 / fp32 tensors are converted to bf16 on the way in and results
+        # are returned in the caller's dtype (accumulation is fp32 throughout).
+        assert head_dim % 8 == 0 and 8 <= head_dim <= 128, \
+            "the fused executor covers head dimensions up to 128 (multiples of 8); use executor_impl='python' beyond"
+        if softmax_scale is None:
+            softmax_scale = head_dim ** -0.5
         dev = (fw_exec_plan.node_id, fw_exec_plan.local_device_id)
         if all_fw_exec_plans is not None:
             self.program = lower_plans(exec_context, fw_workload, all_fw_exec_plans, build_backward=True, only=dev)[dev]
@@ -132,19 +140,32 @@ class FusedPlanExecutor:
     def switch_to_backward(self) -> None:
         self.is_forward = False
 
+    def _put(self, dst: torch.Tensor, src: torch.Tensor) -> None:
+        """``src`` [..., head_dim] of any float dtype into the kernel buffer ``dst`` [..., 128] bf16."""
+        d = self.head_dim
+        src = src.reshape(dst.shape[:-1] + (d,))
+        if d == dst.shape[-1]:
+            dst.copy_(src)
+        else:
+            dst[..., :d].copy_(src)
+            dst[..., d:].zero_()
+
     def _write_inputs(self, q, kv) -> None:
         ex = self.impl
-        ex.q_local().copy_(q.reshape(ex.q_local().shape))
-        ex.kv_local().copy_(kv.reshape(ex.kv_local().shape))
+        self._put(ex.q_local(), q)
+        self._put(ex.kv_local(), kv)
         ex.inputs_written()
         self._epoch = ex.arena_epoch
 
     def forward(self, q: torch.Tensor, kv: torch.Tensor):
         self._write_inputs(q, kv)
-        return self.impl.forward()
+        out, lse = self.impl.forward()
+        if self.head_dim != out.shape[-1] or out.dtype != q.dtype:
+            out = out[..., :self.head_dim].to(q.dtype)
+        return out, lse
 
     def set_local_out_lse(self, out: torch.Tensor, lse: torch.Tensor) -> None:
-        self.impl.out_local().copy_(out.reshape(self.impl.out_local().shape))
+        self._put(self.impl.out_local(), out)
         self.impl.lse_local().copy_(lse.reshape(self.impl.lse_local().shape))
 
     def backward(self, q, kv, out, dout, lse):
@@ -152,8 +173,14 @@ class FusedPlanExecutor:
         if ex.arena_epoch != self._epoch or not ex._staging_valid:
             self._write_inputs(q, kv)
         self.set_local_out_lse(out, lse)
-        dq, dkv = ex.backward(dout.reshape(ex.q_local().shape))
-        return dq.to(q.dtype), dkv.to(kv.dtype)
+        if self.head_dim == ex.q_local().shape[-1]:
+            dout_k = dout.reshape(ex.q_local().shape)
+        else:
+            dout_k = torch.zeros(ex.q_local().shape, dtype=ex.q_local().dtype, device=dout.device)
+            self._put(dout_k, dout)
+        dq, dkv = ex.backward(dout_k)
+        d = self.head_dim
+        return dq[..., :d].to(q.dtype).contiguous(), dkv[..., :d].to(kv.dtype).contiguous()
 
     def capture_cudagraph(self, *a, **k) -> None:
         """Nothing to capture: a call is a handful of launches whose tables change every batch."""
@@ -173,7 +200,7 @@ def get_executor(n_heads_per_block: int, head_dim: int, exec_context: ExecutionC
                  process_group=None, synchronous: bool = False, iteration_idx=None, tp_rank=None,
                  use_cudagraph: bool = False, comm=None, device=None, all_fw_exec_plans=None) -> AttentionExecutor:
     if executor_impl == "fused":
-        # the B200-native path behind the same interface (CUDA only, head_dim 128)
+        # the B200-native path behind the same interface (CUDA only; head_dim <= 128, computed in bf16)
         return FusedPlanExecutor(n_heads_per_block, head_dim, exec_context, fw_exec_plan, fw_workload, bw_exec_plan,
                                  bw_workload, process_group, synchronous, device, all_fw_exec_plans=all_fw_exec_plans)
     if executor_impl not in ("python", "reference"):

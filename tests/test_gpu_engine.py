@@ -266,3 +266,31 @@ def test_reference_api_with_fused_backend(impl):
     # one device, one head block: local order == global order
     assert rel(out.detach(), ro) < 3e-2 and rel(lq.grad, rdq) < 3e-2 and rel(lkv.grad, rdkv) < 3e-2
     assert set(ex.log_memory_usage()) >= {"q", "kv", "dq", "dkv"}
+
+
+@pytest.mark.parametrize("head_dim,dtype", [(64, torch.float16), (96, torch.bfloat16), (128, torch.float32)])
+def test_fused_backend_other_head_dims_and_dtypes(head_dim, dtype):
+    """Head dimensions below 128 run zero-padded on the 128-channel kernels and fp16 / fp32 tensors
+    are converted on the way in and out: results equal dense attention of the same inputs with the
+    softmax scale of the real head dimension, in the caller's shapes and dtype."""
+    _need_gpu()
+    from dcp_b200.core.common import get_default_execution_context
+    from dcp_b200.planner import masks
+    from dcp_b200.runtime.interface import DCPAttention, prepare_dcp_distributed_attn_for_test
+    from dcp_b200.runtime.simulate import dense_reference
+    dev = torch.device("cuda", 0)
+    ctx = get_default_execution_context(1, 1)
+    raw = [500, 1300, 260]
+    ex, lq, lkv, ldo, q, kv, dout, _, pad = prepare_dcp_distributed_attn_for_test(
+        raw, 8, 2, head_dim, 256, 8, ctx, 0, "causal", dtype, device=dev, executor_impl="fused")
+    lq.requires_grad_(True); lkv.requires_grad_(True)
+    out = DCPAttention.apply(ex, False, False, lq, lkv)
+    out.backward(ldo)
+    torch.cuda.synchronize()
+    ex.impl.check_status()
+    assert out.dtype == dtype and out.shape[-1] == head_dim and lq.grad.shape == lq.shape and lkv.grad.shape == lkv.shape
+    m = masks.get_mask_fn("causal")(raw, pad, torch.int32)
+    ro, _, rdq, rdkv = dense_reference(q.float(), kv.float(), raw, pad, m, head_dim ** -0.5, dout.float())
+    rel = lambda a, b: ((a.float().cpu() - b).abs().max() / (b.abs().max() + 1e-9)).item()
+    errs = (rel(out.detach(), ro), rel(lq.grad, rdq), rel(lkv.grad, rdkv))
+    assert max(errs) < 3e-2, errs
