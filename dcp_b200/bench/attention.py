@@ -158,7 +158,8 @@ FRAMEWORK_NAMES = {"dcp": "DCP", "ulysses": "Ulysses", "ring": "Ring", "zigzag":
 
 def main(argv=None):
     ap = argparse.ArgumentParser()
-    ap.add_argument("--framework", default="dcp", choices=sorted(FRAMEWORK_NAMES))
+    ap.add_argument("--framework", default=["dcp"], nargs="+", choices=sorted(FRAMEWORK_NAMES),
+                    help="one or more frameworks, run one after the other on the same batches")
     ap.add_argument("--mask", default="causal")
     ap.add_argument("--tokens", type=int, default=131072)
     ap.add_argument("--batches", type=int, default=3)
@@ -181,10 +182,20 @@ def main(argv=None):
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
         group = dist.group.WORLD
-    summary = run_batches(args, group, dev, rank, world)
-    if rank == 0:
-        print(f"{FRAMEWORK_NAMES[args.framework]}: total time {summary['total_ms']:.3f} ms")
-        print(json.dumps(summary), flush=True)
+    for framework in args.framework:
+        one = argparse.Namespace(**{**vars(args), "framework": framework})
+        try:
+            summary = run_batches(one, group, dev, rank, world)
+        except (AssertionError, RuntimeError, ValueError) as e:     # e.g. a baseline that cannot split this shape
+            if len(args.framework) == 1:
+                raise
+            if rank == 0:
+                print(f"{FRAMEWORK_NAMES[framework]}: failed ({type(e).__name__}: {str(e)[:200]})", flush=True)
+            continue
+        if rank == 0:
+            print(f"{FRAMEWORK_NAMES[framework]}: total time {summary['total_ms']:.3f} ms")
+            print(json.dumps(summary), flush=True)
+        torch.cuda.empty_cache()
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()

@@ -170,7 +170,7 @@ def main(argv=None):
     ap.add_argument("--base-port", type=int, default=29700)
     ap.add_argument("--selftest-worker", action="store_true", help=argparse.SUPPRESS)
     ap.add_argument("--gpus", type=int, default=8)
-    ap.add_argument("--frameworks", nargs="+", default=["dcp", "ulysses", "zigzag", "ring"])
+    ap.add_argument("--frameworks", nargs="+", default=["dcp", "ulysses", "zigzag", "ring", "double-ring", "a2a+p2p"])
     ap.add_argument("--masks", nargs="+", default=["causal", "lambda", "causal_blockwise", "shared_question"])
     ap.add_argument("--length-dists", nargs="+", default=["lognormal8k"])
     ap.add_argument("--block-sizes", nargs="+", type=int, default=[1024, 2048, 4096])
