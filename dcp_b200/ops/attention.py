@@ -328,14 +328,25 @@ def build_bwd_tables(rows: Sequence[AttnRow], block_size: int, hq: int, hkv: int
             lo, hi = p0[:, None], (p0 + nv)[:, None]
             need = ((lo < u0e[None]) & (hi > u0s[None])) | ((lo < u1e[None]) & (hi > u1s[None]))   # [n_sub, n_qt]
             full = (nv[:, None] == TILE_N) & (((i0s[None] <= lo) & (i0e[None] >= hi)) | ((i1s[None] <= lo) & (i1e[None] >= hi)))
-            for t in np.nonzero(need.any(axis=1))[0].tolist():
-                ii = qt[need[t]]
-                arr = np.stack([row.q_row + ii * Q_TILE_BWD, n_rows_t[ii], np.full(ii.size, p0[t]),
-                                mask_row + ii * Q_TILE_BWD, np.full(ii.size, row.dq_dev),
-                                row.dq_row + ii * Q_TILE_BWD, full[t][ii].astype(np.int64),
-                                np.zeros(ii.size, dtype=np.int64)], axis=1)
+            # all (key tile, query tile) pairs of this KV block at once, key-tile major; the per-key-tile
+            # item lists are slices of it
+            ts, ii = np.nonzero(need)
+            if ts.size == 0:
+                continue
+            arr = np.empty((ts.size, 8), dtype=np.int64)
+            arr[:, 0] = row.q_row + ii * Q_TILE_BWD
+            arr[:, 1] = n_rows_t[ii]
+            arr[:, 2] = p0[ts]
+            arr[:, 3] = mask_row + ii * Q_TILE_BWD
+            arr[:, 4] = row.dq_dev
+            arr[:, 5] = row.dq_row + ii * Q_TILE_BWD
+            arr[:, 6] = full[ts, ii]
+            arr[:, 7] = 0
+            counts = np.bincount(ts, minlength=n_sub)
+            ends = np.cumsum(counts)
+            for t in np.nonzero(counts)[0].tolist():
                 key = (kv_row + t * TILE_N, int(nv[t]), dkv_dev, dkv_row + t * TILE_N)
-                cta_items.setdefault(key, []).append(arr)
+                cta_items.setdefault(key, []).append(arr[ends[t] - counts[t]:ends[t]])
         mask_row += row.n_tokens
     ctas, item_chunks, off = [], [], 0
     for key, chunks in sorted(cta_items.items(), key=lambda kv: -sum(c.shape[0] for c in kv[1])):

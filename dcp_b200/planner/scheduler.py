@@ -80,16 +80,18 @@ def _local_block(wl: WorkloadSpec, dev: Device, block_id: int, meta: DataBlockMe
 def _concat_row_mask(units: Sequence[ComputationBlockMeta], n_q: int, block_size: int) -> np.ndarray:
     """Ranges of one q row against the concatenation of its KV blocks -> int32 [2, 2, n_q]."""
     big = np.iinfo(np.int64).max
-    start = np.full((2, n_q), big, dtype=np.int64)
-    end = np.zeros((2, n_q), dtype=np.int64)
-    for pos, u in enumerate(units):
-        m = u.local_attn_mask.numpy().astype(np.int64)
+    ms = []
+    for u in units:
+        m = u.local_attn_mask.numpy()
         if m.ndim == 2:
             m = np.stack([m, np.zeros_like(m)], axis=0)
-        s, e = m[:, 0, :n_q], m[:, 1, :n_q]
-        live = e > s
-        start = np.where(live, np.minimum(start, s + pos * block_size), start)
-        end = np.where(live, np.maximum(end, e + pos * block_size), end)
+        ms.append(m[:, :, :n_q])
+    m = np.stack(ms).astype(np.int64)                       # [unit, range, bound, n_q]
+    off = (np.arange(len(ms), dtype=np.int64) * block_size)[:, None, None]
+    s, e = m[:, :, 0] + off, m[:, :, 1] + off
+    live = m[:, :, 1] > m[:, :, 0]
+    start = np.where(live, s, big).min(axis=0)
+    end = np.where(live, e, 0).max(axis=0)
     empty = end <= np.where(start == big, 0, start)
     start = np.where((start == big) | empty, 0, start)
     end = np.where(empty, 0, end)
