@@ -3,6 +3,8 @@
 (pure-torch reference, NCCL baseline, fused sm_100a) register their handlers on top of this."""
 from __future__ import annotations
 
+import os
+
 from typing import Callable, Dict, Optional, Type
 
 import torch
@@ -22,6 +24,11 @@ class DCPExecutor:
         self.n_nodes, self.n_devices_per_node = n_nodes, n_devices_per_node
         self.synchronous = synchronous
         self.device = device or torch.device("cpu")
+        if logger is None and os.environ.get("DCP_DEBUG_LOG_EXECUTOR", "0") not in ("0", "", "false", "False"):
+            # one log per device of every instruction executed (dcp/core/executor.py:59-73)
+            from ..utils.logger import create_logger
+            logger = create_logger(f"executor.N{node_id}D{local_device_id}", prefix=f"N{node_id}D{local_device_id}",
+                                   log_file=f"executor/N{node_id}D{local_device_id}.log")
         self.logger = logger
         self.buffers: Dict[str, torch.Tensor] = {}
         self.buffer_info: Dict[str, BufferInfo] = {}

@@ -108,9 +108,10 @@ class HuggingFaceDataset(Dataset):
     image) or an in-memory list of ``texts``; tokenizer: a ``transformers`` tokenizer, a callable
     text -> ids, or the built-in byte tokenizer.  Tokenisation, length scaling and the length
     filter run once; the result is written to ``cache_dir`` as one ``.npz`` keyed by everything
-    that determines it and loaded from there afterwards.  Under ``torch.distributed`` rank 0
-    builds the cache while the other ranks wait at a barrier, then they load it (the reference's
-    rank-0-first protocol, hf_dataset.py:174-247)."""
+    that determines it and loaded from there afterwards.  Under ``torch.distributed`` the first
+    rank of every node (``LOCAL_RANK`` 0; with ``DCP_DATASET_INIT_WITH_GLOBAL_RANK=1`` only global
+    rank 0, for a cache directory all nodes share) builds the cache while the other ranks wait at a
+    barrier, then they load it (the reference's rank-0-first protocol, hf_dataset.py:118-135,174-247)."""
 
     def __init__(self, config: HuggingFaceDatasetConfig, texts: Optional[List[str]] = None, tokenizer=None):
         self.config = config
@@ -120,7 +121,10 @@ class HuggingFaceDataset(Dataset):
         try:
             import torch.distributed as dist
             distributed = dist.is_available() and dist.is_initialized()
-            rank0 = not distributed or dist.get_rank() == 0
+            if distributed:
+                by_global = os.environ.get("DCP_DATASET_INIT_WITH_GLOBAL_RANK", "0") not in ("0", "", "false", "False")
+                rank0 = dist.get_rank() == 0 if by_global or "LOCAL_RANK" not in os.environ \
+                    else int(os.environ["LOCAL_RANK"]) == 0
         except Exception:  # pragma: no cover - torch without distributed support
             pass
         if path is not None and not rank0:

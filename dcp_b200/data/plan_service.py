@@ -336,6 +336,15 @@ class SharedPlanService:
         self.waits: List[float] = []
         self.plan_seconds: List[float] = []
         self.n_published = 0
+        # DCP_DATALOADER_LOG_KV: every put / get / delete on the plan store goes to the dataloader log
+        self._kv_log = None
+        if os.environ.get("DCP_DATALOADER_LOG_KV", "0") not in ("0", "", "false", "False"):
+            from ..utils.logger import create_logger
+            self._kv_log = create_logger(f"dataloader.kv.r{rank}", prefix=f"kv r{rank}", log_file=f"dataloader/kv_r{rank}.log")
+
+    def _log_kv(self, what: str, key: str, nbytes: int = 0) -> None:
+        if self._kv_log is not None:
+            self._kv_log.debug("%s %s (%d bytes)", what, key, nbytes)
 
     def _key(self, iteration: int, rank: int) -> str:
         return f"{self.name}/{iteration}/{rank}"
@@ -347,6 +356,7 @@ class SharedPlanService:
                 mine = blob             # the planner's own share needs no round trip
                 continue
             self.store.set(self._key(iteration, r), blob)
+            self._log_kv("put", self._key(iteration, r), len(blob))
             if r == self.rank:
                 mine = blob
         self.n_published += 1
@@ -373,12 +383,14 @@ class SharedPlanService:
             blob = self._done.pop(iteration)
         else:
             blob = self.store.get(self._key(iteration, self.rank), self.timeout_s)
+            self._log_kv("get", self._key(iteration, self.rank), len(blob))
         if not (self.is_planner and self.readers == 1):
             # reader acknowledgement: the last of the `readers` consumers removes the entry
             key = self._key(iteration, self.rank)
             if self.store.add(key + "/reads", 1) >= self.readers:
                 self.store.delete(key)
                 self.store.delete(key + "/reads")
+                self._log_kv("delete", key)
         import zlib
         plan = pickle.loads(zlib.decompress(blob))
         waited = time.time() - t0

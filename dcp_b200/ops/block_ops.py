@@ -92,6 +92,40 @@ def merge_out_lse_reference(outs: torch.Tensor, lses: torch.Tensor):
     return (outs.float() * w[..., None]).sum(0), lse
 
 
+def merge_tables_reference(ops: torch.Tensor, src_rows: torch.Tensor, part_out: torch.Tensor, part_lse: torch.Tensor):
+    """What the merge kernel must produce for the table ``ops`` / ``src_rows`` (see ``merge_out_lse``), with
+    torch ops: a list of (dst_row, out [n_tok, h, d] fp32, lse [h, n_tok] fp32), one entry per table row."""
+    res = []
+    src = src_rows.tolist()
+    for dst_row, n_tok, src_off, n_src in ops.tolist():
+        rows = [src[src_off + j] for j in range(n_src)]
+        outs = torch.stack([part_out[r:r + n_tok] for r in rows])                 # [n, t, h, d]
+        lses = torch.stack([part_lse[:, r:r + n_tok].t() for r in rows])          # [n, t, h]
+        o, l = merge_out_lse_reference(outs, lses)
+        res.append((dst_row, o, l.t()))
+    return res
+
+
+def check_merge_against_reference(ops, src_rows, part_out, part_lse, out, lse, dump_dir: str, tol: float = 2e-2) -> None:
+    """Debug cross-check of the merge kernel (reference switch DCP_DEBUG_LOG_REDUCTION_ARGS_ON_ERROR,
+    dcp/runtime/flash_attention/executor.py:1285-1409): recompute every merged row with torch ops
+    and, on a mismatch, save the kernel's arguments and both results to ``dump_dir`` and raise."""
+    import os
+    for i, (dst_row, o_ref, l_ref) in enumerate(merge_tables_reference(ops, src_rows, part_out, part_lse)):
+        n_tok = o_ref.shape[0]
+        o_got, l_got = out[dst_row:dst_row + n_tok].float(), lse[:, dst_row:dst_row + n_tok]
+        fin = torch.isfinite(l_ref)
+        bad_o = (o_got - o_ref).abs().max().item() > tol * max(1.0, o_ref.abs().max().item())
+        bad_l = bool(fin.any()) and (l_got[fin] - l_ref[fin]).abs().max().item() > tol
+        if bad_o or bad_l:
+            os.makedirs(dump_dir, exist_ok=True)
+            path = os.path.join(dump_dir, f"reduction_args_op{i}_row{dst_row}.pt")
+            torch.save({"ops": ops.cpu(), "src_rows": src_rows.cpu(), "op_index": i, "part_out": part_out.cpu(),
+                        "part_lse": part_lse.cpu(), "out_kernel": o_got.cpu(), "lse_kernel": l_got.cpu(),
+                        "out_reference": o_ref.cpu(), "lse_reference": l_ref.cpu()}, path)
+            raise RuntimeError(f"merge kernel disagrees with the torch reference at table row {i}; arguments saved to {path}")
+
+
 # --------------------------------------------------------------------------- reference-named aliases
 def flash_attn_update_out_lse(out_blocks: torch.Tensor, lse_blocks: torch.Tensor):
     """Merge partial (out, lse): out_blocks [n, t, h, d] bf16, lse_blocks [n, t, h] fp32 -> (out, lse).

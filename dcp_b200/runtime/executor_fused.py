@@ -58,6 +58,8 @@ class FusedAttentionExecutor:
         # reusing last call's bytes
         self.synchronous = os.environ.get("DCP_B200_SYNCHRONOUS", "0") == "1"
         self.poison = os.environ.get("DCP_B200_POISON", "0") == "1"
+        # debug: recompute every merged row with torch ops and dump the kernel's arguments on a mismatch
+        self.check_reductions = os.environ.get("DCP_DEBUG_LOG_REDUCTION_ARGS_ON_ERROR", "0") not in ("0", "", "false", "False")
         # time_calls: one CUDA-event pair around every forward() / backward() call (read with call_times())
         self.time_calls = False
         self._call_events = []
@@ -251,6 +253,10 @@ class FusedAttentionExecutor:
         self._mark("fwd:wait partials of peers")
         if self.merge_ops.shape[0]:
             block_ops.merge_out_lse(self.merge_ops, self.merge_src, self.part_out, self.part_lse, self.out, self.lse)
+            if self.check_reductions:
+                block_ops.check_merge_against_reference(
+                    self.merge_ops, self.merge_src, self.part_out, self.part_lse, self.out, self.lse,
+                    os.path.join(os.environ.get("DCP_LOGGING_DEBUG_DIR", "./debug"), "executor"))
             self.kernel_launches += 1
         self._mark("fwd:merge")
         torch.cuda.nvtx.range_pop()

@@ -345,6 +345,38 @@ def test_optimizer_state_is_recut_for_another_world_size():
         reshard_state((state_of(4, r) for r in (0, 1, 3)), buckets, 2, 1)
 
 
+def test_merge_cross_check_dumps_arguments_on_mismatch(tmp_path):
+    """DCP_DEBUG_LOG_REDUCTION_ARGS_ON_ERROR: the table-driven torch recomputation of the merge agrees
+    with the dense formula, passes a correct result and, for a wrong one, saves the arguments and raises."""
+    import pytest
+    import torch
+    from dcp_b200.ops import block_ops
+    torch.manual_seed(0)
+    n_src, t, h, d = 3, 5, 2, 8
+    part_out = torch.randn(64, h, d)
+    part_lse = torch.randn(h, 64)
+    part_lse[:, 20:22] = float("-inf")                       # a source that saw no key for two tokens
+    src_rows = torch.tensor([3, 20, 40, 50], dtype=torch.int32)
+    ops = torch.tensor([[7, t, 0, n_src], [30, 2, 3, 1]], dtype=torch.int32)
+    ref = block_ops.merge_tables_reference(ops, src_rows, part_out, part_lse)
+    outs = torch.stack([part_out[r:r + t] for r in (3, 20, 40)])
+    lses = torch.stack([part_lse[:, r:r + t].t() for r in (3, 20, 40)])
+    o, l = block_ops.merge_out_lse_reference(outs, lses)
+    assert ref[0][0] == 7 and torch.allclose(ref[0][1], o) and torch.allclose(ref[0][2], l.t())
+    assert torch.allclose(ref[1][1], part_out[50:52])          # a single source is copied
+    out, lse = torch.zeros(64, h, d), torch.zeros(h, 64)
+    for dst, oo, ll in ref:
+        out[dst:dst + oo.shape[0]] = oo
+        lse[:, dst:dst + oo.shape[0]] = ll
+    block_ops.check_merge_against_reference(ops, src_rows, part_out, part_lse, out, lse, str(tmp_path))
+    assert not list(tmp_path.iterdir())
+    out[8, 1, 3] += 1.0
+    with pytest.raises(RuntimeError, match="disagrees"):
+        block_ops.check_merge_against_reference(ops, src_rows, part_out, part_lse, out, lse, str(tmp_path))
+    saved = torch.load(next(tmp_path.iterdir()), weights_only=False)
+    assert saved["op_index"] == 0 and torch.equal(saved["ops"], ops)
+
+
 def test_shared_planning_gives_every_rank_the_plan_it_would_compute_itself():
     """One planner (rank 0) plans every batch once in its worker pool and publishes per-rank shares in
     a key-value store; the other ranks only read.  Every rank must receive exactly the plan it would
