@@ -24,11 +24,24 @@ from dcp_b200.runtime.simulate import dense_reference
     (8, [2048, 3100, 900], 256, 4, 1, "causal_blockwise", 4),
 ])
 def test_emulated_programs_match_dense_attention(world, raw, bs, H, Hkv, mask_name, n_stages):
+    _check_emulated_case(world, raw, bs, H, Hkv, mask_name, n_stages, H)
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_self_check_cases_are_valid_at_every_world_size(world):
+    """The batches that ``bench.py`` runs through the GPU self-check on 2 or more GPUs: at every world
+    size the driver uses, their kernel tables validate and the emulated programs equal dense attention."""
+    from dcp_b200.runtime.selfcheck import DEFAULT_CASES
+    for raw, bs, H, Hkv, mask_name, hbs, n_stages in DEFAULT_CASES:
+        _check_emulated_case(world, list(raw), bs, H, Hkv, mask_name, n_stages, hbs)
+
+
+def _check_emulated_case(world, raw, bs, H, Hkv, mask_name, n_stages, hbs):
     d = 32
     ctx = get_default_execution_context(world, 1)
     pad = pad_seqlens(raw, bs)
     m = masks.get_mask_fn(mask_name)(raw, pad, torch.int32)
-    wl = generate_workload((sum(pad), H, d), (sum(pad), 2, Hkv, d), raw, pad, bs, H, ctx.comp_cost_model, m,
+    wl = generate_workload((sum(pad), H, d), (sum(pad), 2, Hkv, d), raw, pad, bs, hbs, ctx.comp_cost_model, m,
                            torch.bfloat16)
     fw_wl, _, _, _ = InstrCompiler(ctx, CompilerConfig(n_stages=n_stages)).compile(wl, generate_backward=False)
     progs = lower_all(ctx, fw_wl)
