@@ -158,6 +158,7 @@ def timed_steps(eng, K: int, barrier):
     dev_ms, tokens = 0.0, 0
     eng.executor.time_calls = True
     eng.executor.call_times()
+    eng.time_optimizer, eng._optimizer_events = True, []
     for _ in range(K):
         plan = eng.plans.get(eng.iteration)
         toks, labels, pos = eng.stage_inputs(plan)
@@ -172,6 +173,8 @@ def timed_steps(eng, K: int, barrier):
         eng.iteration += 1
     ct = eng.executor.call_times()
     eng.executor.time_calls = False
+    eng.last_optimizer_ms = eng.optimizer_ms()
+    eng.time_optimizer = False
     eng.check_status()
     return dev_ms, tokens, ct["fwd_ms"], ct["bwd_ms"], max(1, ct["n_fwd"])
 
@@ -229,6 +232,7 @@ def main() -> None:
         sampler.start()
     launches0 = _lib.LAUNCHES
     dev_ms, tokens_timed, attn_f, attn_b, n_attn = timed_steps(eng, K, barrier)
+    opt_ms = eng.last_optimizer_ms
     launches = _lib.LAUNCHES - launches0
     if profiling:
         # per-step milliseconds of the attention executor's phases on this rank (stderr, every rank)
@@ -253,8 +257,8 @@ def main() -> None:
     waits = eng.plans.waits[n_waits0:]
     plan_s = eng.plans.plan_seconds[n_waits0:]
 
-    dev_ms, e2e_s, attn_f, attn_b, plan_max, wait_sum = _max_over_ranks(
-        [dev_ms, e2e_s, attn_f, attn_b, max(plan_s) if plan_s else 0.0, sum(waits)], dev, group, world)
+    dev_ms, e2e_s, attn_f, attn_b, plan_max, wait_sum, opt_ms = _max_over_ranks(
+        [dev_ms, e2e_s, attn_f, attn_b, max(plan_s) if plan_s else 0.0, sum(waits), opt_ms], dev, group, world)
 
     # ---- at 8 GPUs also the two fixed 131072-token configurations and the attention
     # microbenchmark, so that every headline configuration has a number from the same run
@@ -314,7 +318,15 @@ def main() -> None:
                                 "bwd_per_layer": round(attn_b / K / n_layers, 2),
                                 "note": "attention executor calls inside the timed steps (CUDA events, max over ranks, "
                                         "cross-GPU waits included)"},
-            "e2e": {"value": round(e2e_tokens / e2e_s, 1), "unit": "tokens/s", "h2d_bytes_per_step": int(h2d),
+            "optimizer_step_ms": {"per_step": round(opt_ms / K, 2),
+                                  "note": "optimizer.step after the backward (CUDA events, max over ranks): last gradient "
+                                          "bucket, norm all-reduce, AdamW and parameter stores; the per-layer "
+                                          "reduce-scatters run beside the backward"},
+            "e2e": {"value": round(e2e_tokens / e2e_s, 1), "unit": "tokens/s", "ms_per_step": round(1e3 * e2e_s / K, 2),
+                    "tokens": int(e2e_tokens),
+                    "batches": "the K iterations after the device-timed ones (variable-length batches differ in "
+                               "attention work, so the two figures are not the same batches)",
+                    "h2d_bytes_per_step": int(h2d),
                     "d2h_bytes_per_step": int(d2h), "fresh_plans": True, "planner_lookahead": cfg.lookahead,
                     "planner_workers": cfg.planner_workers,
                     "plan_ms_mean": round(1e3 * sum(plan_s) / max(1, len(plan_s)), 1), "plan_ms_max": round(1e3 * plan_max, 1),

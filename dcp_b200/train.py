@@ -200,6 +200,9 @@ class TrainEngine:
         return levels
 
     # ---- one iteration
+    time_optimizer = False
+    _optimizer_events: list = []
+
     def stage_inputs(self, plan: RankPlan):
         """Pinned host -> device copies of this iteration's inputs and kernel tables."""
         dev = self.device
@@ -223,8 +226,25 @@ class TrainEngine:
         self.model.zero_grad()
         loss = self.model.loss(toks, labels, pos, 1.0 / max(n_global_tokens, 1))
         loss.backward()
-        self.optimizer.step(1.0)
+        if self.time_optimizer:
+            # what the optimizer still costs after the backward: the reduce-scatters of the layer buckets
+            # ran beside the backward, so this is the last bucket, the norm, AdamW and the parameter stores
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            self.optimizer.step(1.0)
+            e1.record()
+            self._optimizer_events.append((e0, e1))
+        else:
+            self.optimizer.step(1.0)
         return loss.detach()
+
+    def optimizer_ms(self) -> float:
+        """Sum of the timed ``optimizer.step`` calls since the last call of this method (CUDA events;
+        synchronises).  Timing is on while ``time_optimizer`` is set."""
+        torch.cuda.synchronize(self.device)
+        ms = sum(a.elapsed_time(b) for a, b in self._optimizer_events)
+        self._optimizer_events = []
+        return ms
 
     def train_step(self, plan=None) -> float:
         """Public API: plan (or fetch) the iteration, copy its inputs in, step, read the loss back.
