@@ -29,3 +29,9 @@ def connectivity_minus_one(n_vertices: int, net_offsets: Sequence[int], net_pins
 def slice_mask_pairs(rng: np.ndarray, q_lo: int, q_hi: int, n_blk: int, block_size: int
                      ) -> Tuple[List[int], List[int], np.ndarray]:
     """Per query block: KV blocks with allowed pairs, their pair counts, rebased intervals int32 [n, 2, 2, n_q]."""
+
+def pack_multicast_trees(requests: Sequence[Tuple[int, int, Sequence[int], float, Sequence[int]]], n_nodes: int,
+                         n_stages: int, exact: bool = True, search_budget: int = 50000) -> Dict[str, Any]:
+    """Multicast tree packing; requests = (block, source node, destination nodes, size, arrival stage per
+    destination or empty).  Returns {"trees": {block: [(stage, from node, to node)]}, "cost", "greedy_cost",
+    "proven_optimal"}."""

@@ -6,6 +6,7 @@
 #include "hypergraph.hpp"
 #include "mask_slices.hpp"
 #include "stage_greedy.hpp"
+#include "tree_packing.hpp"
 
 namespace py = pybind11;
 using namespace dcpp;
@@ -101,6 +102,38 @@ int64_t py_km1(int n_vertices, const std::vector<int>& net_offsets, const std::v
   return connectivity_minus_one(hg, part, k);
 }
 
+// requests: (block, source node, destination nodes, size, arrival stage per destination or empty)
+py::dict py_pack_trees(const std::vector<std::tuple<int, int, std::vector<int>, double, std::vector<int>>>& requests,
+                       int n_nodes, int n_stages, bool exact, int64_t search_budget) {
+  std::vector<TreeRequest> reqs;
+  for (auto& r : requests) {
+    TreeRequest t;
+    t.block = std::get<0>(r);
+    t.src = std::get<1>(r);
+    t.dsts = std::get<2>(r);
+    t.size = std::get<3>(r);
+    t.arrival = std::get<4>(r);
+    reqs.push_back(std::move(t));
+  }
+  TreePacking p;
+  {
+    py::gil_scoped_release release;
+    p = pack_multicast_trees(reqs, n_nodes, n_stages, exact, search_budget);
+  }
+  py::dict trees;
+  for (auto& kv : p.trees) {
+    py::list l;
+    for (auto& e : kv.second) l.append(py::make_tuple(e.stage, e.from, e.to));
+    trees[py::int_(kv.first)] = l;
+  }
+  py::dict out;
+  out["trees"] = trees;
+  out["cost"] = p.cost;
+  out["greedy_cost"] = p.greedy_cost;
+  out["proven_optimal"] = p.proven_optimal;
+  return out;
+}
+
 }  // namespace
 
 namespace {
@@ -135,6 +168,8 @@ PYBIND11_MODULE(_planner, m) {
         py::arg("cap_mem"), py::arg("seed") = 42, py::arg("n_tries") = 4, py::arg("fixed") = std::vector<int>(),
         py::arg("initial") = std::vector<int>());
   m.def("connectivity_minus_one", &py_km1);
+  m.def("pack_multicast_trees", &py_pack_trees, py::arg("requests"), py::arg("n_nodes"), py::arg("n_stages"),
+        py::arg("exact") = true, py::arg("search_budget") = 50000);
   m.def("slice_mask_pairs", &py_slice_mask_pairs, py::arg("rng"), py::arg("q_lo"), py::arg("q_hi"), py::arg("n_blk"),
         py::arg("block_size"));
 }

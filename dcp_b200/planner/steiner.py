@@ -40,7 +40,7 @@ def _pack_greedy(requests: Sequence[Request], n_nodes: int, n_stages: int, arriv
     send = [[0.0] * n_nodes for _ in range(n_stages)]
     recv = [[0.0] * n_nodes for _ in range(n_stages)]
     trees: Dict[int, List[Tuple[int, int, int]]] = {}
-    for blk, src, dsts, size in sorted(requests, key=lambda r: (-r[3] * len(r[2]), r[0])):
+    for blk, src, dsts, size in sorted(requests, key=lambda r: (-r[3] * len(set(r[2]) - {r[1]}), r[0])):
         have = {src: -1}              # node -> stage in which it obtained the block
         edges = []
         remaining = set(dsts) - {src}
@@ -72,7 +72,7 @@ def _pack_exact(requests: Sequence[Request], n_nodes: int, n_stages: int, arriva
     enumerated in increasing (stage, destination) order, which reaches every tree exactly once (a
     relay always obtained the block in an earlier stage than it forwards it).  A branch is cut as
     soon as its partial maximum reaches the best complete packing.  Returns (trees, cost, proven)."""
-    reqs = sorted(requests, key=lambda r: (-r[3] * len(r[2]), r[0]))
+    reqs = sorted(requests, key=lambda r: (-r[3] * len(set(r[2]) - {r[1]}), r[0]))
     send = [[0.0] * n_nodes for _ in range(n_stages)]
     recv = [[0.0] * n_nodes for _ in range(n_stages)]
     # no packing can beat: the largest single block, and a node's mandatory receive volume spread over
@@ -144,7 +144,8 @@ def _pack_exact(requests: Sequence[Request], n_nodes: int, n_stages: int, arriva
 
 
 def pack_multicast_trees(requests: Sequence[Request], n_nodes: int, n_stages: int, arrival: Optional[Arrival] = None,
-                         exact: bool = True, search_budget: int = 50000, return_info: bool = False):
+                         exact: bool = True, search_budget: int = 50000, return_info: bool = False,
+                         native: bool = True):
     """requests: (block id, source node, destination nodes, size).  Returns
     {block id: [(stage, src node, dst node)]} with every destination reached and each edge's source
     holding the block before the edge's stage; with ``arrival`` a destination receives exactly in
@@ -152,9 +153,21 @@ def pack_multicast_trees(requests: Sequence[Request], n_nodes: int, n_stages: in
     branch-and-bound search then looks for the packing with the smallest per-node, per-stage
     maximum and proves it optimal when it finishes within ``search_budget`` search nodes (the
     role of the CP-SAT model in dcp/core/steiner_tree_packing.py:14-167, which is also run under
-    a time limit and falls back to the best feasible packing).
+    a time limit and falls back to the best feasible packing).  ``native`` runs the C++
+    implementation (csrc/planner/tree_packing.cpp); the Python one below is its twin and oracle.
     ``return_info`` -> (trees, {"cost", "greedy_cost", "proven_optimal"})."""
     requests = [(b, s, set(d), float(z)) for b, s, d, z in requests]
+    if native:
+        from .. import _planner
+        packed = []
+        for b, s, dsts, z in requests:
+            ds = sorted(dsts)
+            arr = [] if arrival is None else [arrival.get((b, d), -1) for d in ds]
+            packed.append((b, s, ds, z, arr))
+        res = _planner.pack_multicast_trees(packed, n_nodes, n_stages, exact, search_budget)
+        trees = {int(b): [tuple(e) for e in edges] for b, edges in res["trees"].items()}
+        info = {"cost": res["cost"], "greedy_cost": res["greedy_cost"], "proven_optimal": bool(res["proven_optimal"])}
+        return (trees, info) if return_info else trees
     trees = _pack_greedy(requests, n_nodes, n_stages, arrival)
     greedy_cost = cost = packing_cost(trees, requests, n_nodes, n_stages)
     proven = False

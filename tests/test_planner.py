@@ -274,6 +274,29 @@ def test_tree_packing_is_optimal_on_small_instances():
     assert not info["proven_optimal"] and info["cost"] <= info["greedy_cost"]
 
 
+def test_native_tree_packer_equals_its_python_twin():
+    """csrc/planner/tree_packing.cpp against the Python implementation: same cost, same optimality
+    verdict and the same trees on random instances, greedy only and with the exact search."""
+    import random
+    from dcp_b200.planner.steiner import pack_multicast_trees
+    rng = random.Random(5)
+    for trial in range(120):
+        n_nodes, n_stages = rng.choice([2, 3, 4, 6, 8]), rng.choice([2, 3, 4, 5])
+        reqs = []
+        for b in range(rng.choice([1, 2, 3, 5, 8])):
+            src = rng.randrange(n_nodes)
+            reqs.append((b, src, set(rng.sample(range(n_nodes), rng.randint(1, min(4, n_nodes)))), float(rng.choice([1, 2, 3, 5, 8]))))
+        arrival = None
+        if trial % 2:
+            arrival = {(b, d): rng.randrange(n_stages) for b, _, ds, _ in reqs for d in ds if rng.random() < 0.8}
+        for exact in (False, True):
+            a, ia = pack_multicast_trees(reqs, n_nodes, n_stages, arrival=arrival, exact=exact, return_info=True,
+                                         native=True, search_budget=3000)
+            b, ib = pack_multicast_trees(reqs, n_nodes, n_stages, arrival=arrival, exact=exact, return_info=True,
+                                         native=False, search_budget=3000)
+            assert ia == pytest.approx(ib) and {k: sorted(v) for k, v in a.items()} == {k: sorted(v) for k, v in b.items()}
+
+
 def test_block_size_heuristic_and_cost_models():
     assert block_size_heuristic([100000, 300, 200], 8, 0.2) < block_size_heuristic([8000] * 8, 8, 0.2)
     assert block_size_heuristic([8192] * 8, 8) == 8192
