@@ -35,3 +35,15 @@ def pack_multicast_trees(requests: Sequence[Tuple[int, int, Sequence[int], float
     """Multicast tree packing; requests = (block, source node, destination nodes, size, arrival stage per
     destination or empty).  Returns {"trees": {block: [(stage, from node, to node)]}, "cost", "greedy_cost",
     "proven_optimal"}."""
+
+AttnRowTuple = Tuple[int, int, Sequence[int], Sequence[Tuple[int, int]], np.ndarray, int, int, int, int, Sequence[Tuple[int, int]]]
+
+def build_fwd_tables(rows: Sequence[AttnRowTuple], block_size: int, tile_m: int
+                     ) -> Tuple[np.ndarray, np.ndarray, np.ndarray, float]:
+    """Forward kernel tables of one stage: (tiles int32 [n, 8], kv entries int32 [m, 2 | 4], masks int32 [r, 4],
+    allowed pairs x heads).  A row = (q_row, n_tokens, heads, [(kv row, tokens)], ranges int32 [n_tokens, 4],
+    out_dev, out_row, dq_dev, dq_row, [(dkv device, dkv row)])."""
+
+def build_bwd_tables(rows: Sequence[AttnRowTuple], block_size: int, hq: int
+                     ) -> Tuple[np.ndarray, np.ndarray, np.ndarray, float]:
+    """Backward kernel tables: (ctas int32 [n, 8], items int32 [m, 8], masks int32 [r, 4], allowed pairs x heads)."""

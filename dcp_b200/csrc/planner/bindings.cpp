@@ -4,6 +4,7 @@
 #include <pybind11/stl.h>
 
 #include "hypergraph.hpp"
+#include "kernel_tables.hpp"
 #include "mask_slices.hpp"
 #include "stage_greedy.hpp"
 #include "tree_packing.hpp"
@@ -134,6 +135,53 @@ py::dict py_pack_trees(const std::vector<std::tuple<int, int, std::vector<int>, 
   return out;
 }
 
+// one attention row = (q_row, n_tokens, heads, [(kv row, tokens)], ranges int32 [n_tokens, 4], out_dev, out_row,
+// dq_dev, dq_row, [(dkv device, dkv row)])
+using PyAttnRow = std::tuple<int64_t, int64_t, std::vector<int>, std::vector<std::pair<int64_t, int64_t>>,
+                             py::array_t<int32_t, py::array::c_style | py::array::forcecast>, int64_t, int64_t, int64_t,
+                             int64_t, std::vector<std::pair<int64_t, int64_t>>>;
+
+std::vector<AttnRowDesc> to_rows(const std::vector<PyAttnRow>& rows) {
+  std::vector<AttnRowDesc> out;
+  out.reserve(rows.size());
+  for (const PyAttnRow& r : rows) {
+    AttnRowDesc d;
+    d.q_row = std::get<0>(r);
+    d.n_tokens = std::get<1>(r);
+    d.heads = std::get<2>(r);
+    d.kv = std::get<3>(r);
+    const auto& rng = std::get<4>(r);
+    if (rng.size() != 4 * d.n_tokens) throw std::invalid_argument("ranges must be [n_tokens, 4]");
+    d.ranges = rng.data();
+    d.out_dev = std::get<5>(r);
+    d.out_row = std::get<6>(r);
+    d.dq_dev = std::get<7>(r);
+    d.dq_row = std::get<8>(r);
+    d.dkv = std::get<9>(r);
+    if (!d.dkv.empty() && d.dkv.size() != d.kv.size()) throw std::invalid_argument("dkv must match kv");
+    out.push_back(std::move(d));
+  }
+  return out;
+}
+
+py::array_t<int32_t> to_array(const std::vector<int32_t>& v, int width) {
+  py::array_t<int32_t> a({py::ssize_t(v.size() / size_t(width)), py::ssize_t(width)});
+  std::copy(v.begin(), v.end(), a.mutable_data());
+  return a;
+}
+
+py::tuple py_build_fwd_tables(const std::vector<PyAttnRow>& rows, int64_t block_size, int tile_m) {
+  const auto desc = to_rows(rows);     // `rows` keeps the range arrays alive
+  FwdTablesOut t = build_fwd_tables(desc, block_size, tile_m);
+  return py::make_tuple(to_array(t.tiles, 8), to_array(t.entries, tile_m == 128 ? 2 : 4), to_array(t.masks, 4), t.pairs);
+}
+
+py::tuple py_build_bwd_tables(const std::vector<PyAttnRow>& rows, int64_t block_size, int hq) {
+  const auto desc = to_rows(rows);
+  BwdTablesOut t = build_bwd_tables(desc, block_size, hq);
+  return py::make_tuple(to_array(t.ctas, 8), to_array(t.items, 8), to_array(t.masks, 4), t.pairs);
+}
+
 }  // namespace
 
 namespace {
@@ -168,6 +216,8 @@ PYBIND11_MODULE(_planner, m) {
         py::arg("cap_mem"), py::arg("seed") = 42, py::arg("n_tries") = 4, py::arg("fixed") = std::vector<int>(),
         py::arg("initial") = std::vector<int>());
   m.def("connectivity_minus_one", &py_km1);
+  m.def("build_fwd_tables", &py_build_fwd_tables, py::arg("rows"), py::arg("block_size"), py::arg("tile_m"));
+  m.def("build_bwd_tables", &py_build_bwd_tables, py::arg("rows"), py::arg("block_size"), py::arg("hq"));
   m.def("pack_multicast_trees", &py_pack_trees, py::arg("requests"), py::arg("n_nodes"), py::arg("n_stages"),
         py::arg("exact") = true, py::arg("search_budget") = 50000);
   m.def("slice_mask_pairs", &py_slice_mask_pairs, py::arg("rng"), py::arg("q_lo"), py::arg("q_hi"), py::arg("n_blk"),

@@ -70,7 +70,34 @@ def _pair_count(ranges: np.ndarray) -> float:
     return float(np.maximum(r[:, 1] - r[:, 0], 0).sum() + np.maximum(r[:, 3] - r[:, 2], 0).sum())
 
 
+def _native_planner():
+    """The C++ table builders (csrc/planner/kernel_tables.cpp), or None when DCP_B200_PY_TABLES=1
+    asks for the Python implementations below (their twins and oracle)."""
+    import os
+    if os.environ.get("DCP_B200_PY_TABLES", "0") == "1":
+        return None
+    from .. import _planner
+    return _planner
+
+
+def _row_tuples(rows: Sequence[AttnRow]):
+    return [(int(r.q_row), int(r.n_tokens), [int(h) for h in r.heads], [(int(a), int(b)) for a, b in r.kv],
+             np.ascontiguousarray(r.ranges, dtype=np.int32).reshape(-1, 4), int(r.out_dev), int(r.out_row), int(r.dq_dev),
+             int(r.dq_row), [(int(a), int(b)) for a, b in r.dkv]) for r in rows]
+
+
 def build_fwd_tables(rows: Sequence[AttnRow], block_size: int, device, tile_m: int = TILE_M_PAIR) -> FwdTables:
+    """Forward kernel tables (see ``build_fwd_tables_py`` for the layout); built by the C++ planner module."""
+    native = _native_planner()
+    if native is None:
+        return build_fwd_tables_py(rows, block_size, device, tile_m)
+    assert tile_m in (TILE_M, TILE_M_PAIR)
+    t_np, e_np, m_np, pairs = native.build_fwd_tables(_row_tuples(rows), int(block_size), int(tile_m))
+    to = lambda a: torch.from_numpy(a).to(device, non_blocking=True)
+    return FwdTables(to(t_np), to(e_np), to(m_np), int(t_np.shape[0]), block_size, flops=4.0 * pairs * HEAD_DIM, tile_m=tile_m)
+
+
+def build_fwd_tables_py(rows: Sequence[AttnRow], block_size: int, device, tile_m: int = TILE_M_PAIR) -> FwdTables:
     """Flatten Q blocks into CTA tiles of ``tile_m`` query rows.
 
     tile_m = 128: one tile per CTA (attn_fwd.cu, attn_fwd_split.cu); ``kv_entries`` lists the KV blocks
@@ -307,6 +334,16 @@ def _tile_bounds(rng: np.ndarray, tile: int):
 
 
 def build_bwd_tables(rows: Sequence[AttnRow], block_size: int, hq: int, hkv: int, device) -> BwdTables:
+    """Backward kernel tables (see ``build_bwd_tables_py`` for the layout); built by the C++ planner module."""
+    native = _native_planner()
+    if native is None:
+        return build_bwd_tables_py(rows, block_size, hq, hkv, device)
+    c_np, i_np, m_np, pairs = native.build_bwd_tables(_row_tuples(rows), int(block_size), int(hq))
+    to = lambda a: torch.from_numpy(a).to(device, non_blocking=True)
+    return BwdTables(to(c_np), to(i_np), to(m_np), int(c_np.shape[0]), int(i_np.shape[0]), flops=10.0 * pairs * HEAD_DIM)
+
+
+def build_bwd_tables_py(rows: Sequence[AttnRow], block_size: int, hq: int, hkv: int, device) -> BwdTables:
     """KV-major work lists for the backward kernel: one table entry per key tile (the kernel runs
     it once per KV head) listing the 64-query tiles that see it; heads are not materialised."""
     masks, mask_row = [], 0

@@ -33,10 +33,11 @@ def test_self_check_cases_are_valid_at_every_world_size(world):
     size the driver uses, their kernel tables validate and the emulated programs equal dense attention."""
     from dcp_b200.runtime.selfcheck import DEFAULT_CASES
     for raw, bs, H, Hkv, mask_name, hbs, n_stages in DEFAULT_CASES:
-        _check_emulated_case(world, list(raw), bs, H, Hkv, mask_name, n_stages, hbs)
+        # the long batch is only validated statically (its dense fp64 attention takes a minute on a CPU)
+        _check_emulated_case(world, list(raw), bs, H, Hkv, mask_name, n_stages, hbs, numerics=sum(raw) < 8000)
 
 
-def _check_emulated_case(world, raw, bs, H, Hkv, mask_name, n_stages, hbs):
+def _check_emulated_case(world, raw, bs, H, Hkv, mask_name, n_stages, hbs, numerics=True):
     d = 32
     ctx = get_default_execution_context(world, 1)
     pad = pad_seqlens(raw, bs)
@@ -47,6 +48,8 @@ def _check_emulated_case(world, raw, bs, H, Hkv, mask_name, n_stages, hbs):
     progs = lower_all(ctx, fw_wl)
     counts = validate_programs(progs)                     # static cross-rank consistency of the tables
     assert counts["tiles"] > 0 and counts["items"] > 0
+    if not numerics:
+        return
     devs = ctx.devices()
     T = sum(raw)
     g = torch.Generator().manual_seed(11)
@@ -241,3 +244,37 @@ def test_copy_jobs_move_exactly_the_pulled_rows():
     for peer, s_row, d_row, n in pulls.tolist():
         ref_s[:, d_row:d_row + n] = stats[peer][:, s_row:s_row + n]
     assert (dst_s == ref_s).all()
+
+
+def test_native_table_builders_equal_their_python_twins():
+    """csrc/planner/kernel_tables.cpp against the Python builders on random attention rows (ragged
+    blocks, empty and reversed ranges, rows without keys, peer destinations): identical arrays."""
+    import numpy as np
+    from dcp_b200.ops import attention as A
+    rng = np.random.default_rng(7)
+    for trial in range(60):
+        bs = int(rng.choice([128, 256, 512]))
+        hq = int(rng.choice([2, 4]))
+        rows, q_row = [], 0
+        for _ in range(int(rng.integers(1, 6))):
+            n_tok = int(rng.integers(1, bs + 1))
+            n_kv = int(rng.integers(0, 5))
+            kv = [(int(rng.integers(0, 50)) * bs, int(rng.integers(1, bs + 1))) for _ in range(n_kv)]
+            span = max(1, n_kv * bs)
+            r = np.sort(rng.integers(0, span + 1, size=(n_tok, 4)), axis=1).astype(np.int32)
+            kind = rng.integers(0, 4, size=n_tok)
+            r[kind == 0, 2:] = 0                                  # single range
+            r[kind == 1] = r[kind == 1][:, [1, 0, 3, 2]]          # reversed (empty) ranges
+            if trial % 3 == 0:                                    # causal-like: whole tiles fully visible
+                r[:, 0], r[:, 1], r[:, 2], r[:, 3] = 0, span, 0, 0
+            rows.append(A.AttnRow(q_row, n_tok, list(range(hq)), kv, r, int(rng.integers(0, 3)), int(rng.integers(0, 9)) * bs,
+                                  int(rng.integers(0, 3)), int(rng.integers(0, 9)) * bs,
+                                  [(int(rng.integers(0, 3)), int(rng.integers(0, 9)) * bs) for _ in kv] if trial % 2 else []))
+            q_row += bs
+        for tile_m in (A.TILE_M, A.TILE_M_PAIR):
+            a, b = A.build_fwd_tables(rows, bs, "cpu", tile_m), A.build_fwd_tables_py(rows, bs, "cpu", tile_m)
+            assert torch.equal(a.tiles, b.tiles) and torch.equal(a.kv_entries, b.kv_entries) and torch.equal(a.masks, b.masks)
+            assert (a.n_tiles, a.flops, a.tile_m, a.kv_entries.shape) == (b.n_tiles, b.flops, b.tile_m, b.kv_entries.shape)
+        a, b = A.build_bwd_tables(rows, bs, hq, 1, "cpu"), A.build_bwd_tables_py(rows, bs, hq, 1, "cpu")
+        assert torch.equal(a.ctas, b.ctas) and torch.equal(a.items, b.items) and torch.equal(a.masks, b.masks)
+        assert (a.n_ctas, a.n_items, a.flops) == (b.n_ctas, b.n_items, b.flops)
