@@ -70,3 +70,26 @@ def visualize_workload_spec_figure(workload: WorkloadSpec, path: Optional[str] =
         with open(path, "w") as f:
             json.dump(graph, f)
     return graph
+
+
+def merge_chrome_traces(modelled: list, measured_by_rank: dict, path: str = None) -> dict:
+    """One chrome trace with the planner's modelled stage timeline (``planner.stages.pipeline_chrome_trace``)
+    above the measured phases of every rank (``FusedAttentionExecutor.profile_chrome_trace``).  The
+    modelled events keep their per-device lanes under process ids 0 .. n_nodes-1 named
+    "modelled node n"; rank r's measured phases go to process id 1000 + r named "measured rank r",
+    so both open side by side in a trace viewer."""
+    events = []
+    nodes = sorted({e["pid"] for e in modelled})
+    for n in nodes:
+        events.append({"name": "process_name", "ph": "M", "pid": n, "args": {"name": f"modelled node {n}"}})
+    events.extend(dict(e) for e in modelled)
+    for rank in sorted(measured_by_rank):
+        pid = 1000 + int(rank)
+        events.append({"name": "process_name", "ph": "M", "pid": pid, "args": {"name": f"measured rank {rank}"}})
+        events.extend({**e, "pid": pid} for e in measured_by_rank[rank])
+    trace = {"traceEvents": events, "displayTimeUnit": "ms"}
+    if path:
+        import json
+        with open(path, "w") as f:
+            json.dump(trace, f)
+    return trace

@@ -364,3 +364,27 @@ def test_native_mask_slicing_matches_array_version(mask):
             assert list(a[0]) == list(b[0]) and list(a[1]) == list(b[1])
             assert np.array_equal(np.asarray(a[2]), np.asarray(b[2]))
         off += n_pad
+
+
+def test_modelled_and_measured_traces_merge_into_one_file(tmp_path):
+    """The planner's modelled stage timeline and per-rank measured phases end up in one chrome trace
+    with named processes; events keep their lanes and durations."""
+    import json
+    from dcp_b200.planner.stages import pipeline_chrome_trace
+    from dcp_b200.utils.visualization import merge_chrome_traces
+    ctx = get_default_execution_context(4, 1)
+    wl, _, _ = _workload([1500, 700, 400], 128, hbs=4, mask="causal", ctx=ctx)
+    construct_and_partition_graph_multiconstraint(ctx, wl)
+    work, comm, _ = generate_pipelines_n_stages(3, ctx.devices(), wl.workloads, wl.work_unit_input_map,
+                                                wl.block_mapping.input_id_to_meta, wl.input_sizes, wl.work_to_device_map,
+                                                wl.input_to_device_map, False)
+    modelled = pipeline_chrome_trace(work, comm, wl.workloads, wl.input_sizes, ctx.comm_cost_model)
+    measured = {r: [{"name": "fwd:kernels (with operand fetch)", "ph": "X", "pid": r, "tid": 0, "ts": 10.0, "dur": 500.0 + r}]
+                for r in range(4)}
+    trace = merge_chrome_traces(modelled, measured, str(tmp_path / "t.json"))
+    loaded = json.load(open(tmp_path / "t.json"))
+    assert loaded == trace
+    names = {e["args"]["name"] for e in trace["traceEvents"] if e["ph"] == "M"}
+    assert names == {"modelled node 0"} | {f"measured rank {r}" for r in range(4)}
+    xs = [e for e in trace["traceEvents"] if e["ph"] == "X"]
+    assert len(xs) == len(modelled) + 4 and {e["pid"] for e in xs if e["name"].startswith("fwd:")} == {1000, 1001, 1002, 1003}
