@@ -11,15 +11,19 @@ from ..ops import model_ops
 from .llama import LlamaConfig
 
 
-def reference_loss(cfg: LlamaConfig, p: Dict[str, torch.Tensor], tokens: torch.Tensor, labels: torch.Tensor,
-                   positions: torch.Tensor, seqlens: Sequence[int], grad_scale: float) -> torch.Tensor:
-    """Tokens are packed sequence after sequence; returns sum(token losses) * grad_scale."""
+def reference_embed(p: Dict[str, torch.Tensor], tokens: torch.Tensor) -> torch.Tensor:
+    return F.embedding(tokens, p["embed"])
+
+
+def reference_layers(cfg: LlamaConfig, p: Dict[str, torch.Tensor], x: torch.Tensor, positions: torch.Tensor,
+                     seqlens: Sequence[int], first: int, last: int) -> torch.Tensor:
+    """Decoder layers ``first`` .. ``last - 1`` on the packed hidden states ``x`` (dense causal attention
+    per sequence).  The unit a pipeline stage owns."""
     cos, sin = model_ops.rope_tables(positions, cfg.rope_theta, cfg.head_dim)
     hq, hkv, d = cfg.n_heads, cfg.n_kv_heads, cfg.head_dim
     g = hq // hkv
-    x = F.embedding(tokens, p["embed"])
     norm = lambda t, w: t * torch.rsqrt(t.pow(2).mean(-1, keepdim=True) + cfg.eps) * w
-    for l in range(cfg.n_layers):
+    for l in range(first, last):
         h = norm(x, p[f"l{l}.norm1"])
         qkv = F.linear(h, p[f"l{l}.wqkv"]).view(-1, hq + 2 * hkv, d)
         q = model_ops.rope_reference(qkv[:, :hq], cos, sin)
@@ -38,7 +42,26 @@ def reference_loss(cfg: LlamaConfig, p: Dict[str, torch.Tensor], tokens: torch.T
         h = norm(x, p[f"l{l}.norm2"])
         gate, up = F.linear(h, p[f"l{l}.wgu"]).chunk(2, dim=-1)
         x = x + F.linear(F.silu(gate) * up, p[f"l{l}.wd"])
-    h = norm(x, p["norm_f"])
+    return x
+
+
+def reference_head_loss(cfg: LlamaConfig, p: Dict[str, torch.Tensor], x: torch.Tensor, labels: torch.Tensor,
+                        grad_scale: float) -> torch.Tensor:
+    h = x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + cfg.eps) * p["norm_f"]
     logits = F.linear(h, p["lm_head"])
     loss = F.cross_entropy(logits, labels.clamp(min=0), reduction="none")
     return torch.where(labels >= 0, loss, torch.zeros_like(loss)).sum() * grad_scale
+
+
+def stage_layer_range(n_layers: int, stage: int, n_stages: int) -> range:
+    """Consecutive layers of pipeline stage ``stage`` (earlier stages take the remainder)."""
+    per, extra = divmod(n_layers, n_stages)
+    first = stage * per + min(stage, extra)
+    return range(first, first + per + (1 if stage < extra else 0))
+
+
+def reference_loss(cfg: LlamaConfig, p: Dict[str, torch.Tensor], tokens: torch.Tensor, labels: torch.Tensor,
+                   positions: torch.Tensor, seqlens: Sequence[int], grad_scale: float) -> torch.Tensor:
+    """Tokens are packed sequence after sequence; returns sum(token losses) * grad_scale."""
+    x = reference_layers(cfg, p, reference_embed(p, tokens), positions, seqlens, 0, cfg.n_layers)
+    return reference_head_loss(cfg, p, x, labels, grad_scale)

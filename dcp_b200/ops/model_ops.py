@@ -27,10 +27,11 @@ def swiglu_reference(gu: torch.Tensor) -> torch.Tensor:
 
 
 def rope_reference(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
-    """x [T, H, 128], cos/sin [T, 64]; rotate-half convention."""
-    xf = x.float()
-    x1, x2 = xf[..., :64], xf[..., 64:]
-    c, s = cos[:, None, :].float(), sin[:, None, :].float()
+    """x [T, H, d], cos/sin [T, d/2]; rotate-half convention.  Computed in fp32, or in fp64 for fp64 input."""
+    xf = x.double() if x.dtype == torch.float64 else x.float()
+    half = x.shape[-1] // 2
+    x1, x2 = xf[..., :half], xf[..., half:]
+    c, s = cos[:, None, :].to(xf.dtype), sin[:, None, :].to(xf.dtype)
     return torch.cat([x1 * c - x2 * s, x2 * c + x1 * s], dim=-1).to(x.dtype)
 
 
