@@ -3,8 +3,11 @@
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \\
         -m dcp_b200.bench.attention --framework dcp --mask causal --tokens 131072 --batches 5
 
-Frameworks: ``dcp`` (fused sm_100a executor), ``ulysses`` (NCCL all-to-all + library attention),
-``nccl-plan`` (the same DCP plans interpreted with NCCL point-to-point and torch ops).  Timing
+Frameworks (``--framework`` takes one or several, run one after the other on the same batches):
+``dcp`` (fused sm_100a executor), ``ulysses`` (NCCL all-to-all + library attention), ``ring`` /
+``zigzag`` / ``double-ring`` (NCCL point-to-point rings + library attention per chunk), ``a2a+p2p``
+(head all-to-all inside small groups x ring between them), ``nccl-plan`` (the same DCP plans
+interpreted with NCCL point-to-point and torch ops).  Timing
 follows the reference's harness (benchmark/microbenchmark/utils.py:144-225,
 benchmark_attention.py:1457-1472): warm-up iterations, CUDA events, per-rank times gathered and the
 MAX over ranks reported, summed over batches; the line ``<Name>: total time X ms`` keeps the
