@@ -81,22 +81,28 @@ class ClockSampler:
         except subprocess.TimeoutExpired:
             self.proc.kill()
         self.f.close()
-        sm, mx, reasons = [], [], set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for line in open(self.path):
-            parts = [p.strip() for p in line.split(",")]
-            if len(parts) < 9:
-                continue
-            try:
-                sm.append(float(parts[1])); mx.append(float(parts[2]))
-            except ValueError:
-                continue
-            for n, v in zip(names, parts[5:9]):
-                if v.lower().startswith("active"):
-                    reasons.add(n)
-        sm.sort()
-        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": sorted(reasons), "samples": len(sm), "gpus_sampled": len(self.gpu_ids) or "all"}
+        return {**parse_clock_log(self.path), "gpus_sampled": len(self.gpu_ids) or "all"}
+
+
+def parse_clock_log(path: str) -> dict:
+    """Median SM clock, maximum SM clock and the throttle reasons seen in a log of ``QUERY`` rows
+    (csv, no header, no units; rows that do not parse - e.g. "[N/A]" - are skipped)."""
+    sm, mx, reasons = [], [], set()
+    names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+    for line in open(path):
+        parts = [p.strip() for p in line.split(",")]
+        if len(parts) < 9:
+            continue
+        try:
+            sm.append(float(parts[1])); mx.append(float(parts[2]))
+        except ValueError:
+            continue
+        for n, v in zip(names, parts[5:9]):
+            if v.lower().startswith("active"):
+                reasons.add(n)
+    sm.sort()
+    return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+            "reasons": sorted(reasons), "samples": len(sm)}
 
 
 def parse_args(argv=None):

@@ -89,3 +89,24 @@ def test_parallel_layout_groups_partition_the_world():
             assert all(r % tp == t for r in og)
         for tg in lay["tp_groups"]:
             assert tg == list(range(tg[0], tg[0] + tp))               # tensor-parallel ranks are adjacent
+
+
+def test_bench_clock_log_parsing(tmp_path):
+    """The bench line's clock record: median SM clock over the sampled rows of the job's own GPUs,
+    maximum clock, and every throttle reason that was active in any row; unparsable rows are skipped."""
+    import importlib.util
+    import os
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    spec = importlib.util.spec_from_file_location("bench_main", os.path.join(root, "bench.py"))
+    bench = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bench)
+    log = tmp_path / "clocks.csv"
+    log.write_text("0, 1530, 1965, 950.1, 0x0000000000000004, Not Active, Not Active, Not Active, Active\n"
+                   "0, 1695, 1965, 990.0, 0x0000000000000004, Not Active, Not Active, Not Active, Active\n"
+                   "0, [N/A], 1965, 10.0, 0x0, Not Active, Not Active, Not Active, Not Active\n"
+                   "0, 1920, 1965, 400.0, 0x0, Not Active, Not Active, Active, Not Active\n"
+                   "garbage\n")
+    rec = bench.parse_clock_log(str(log))
+    assert rec == {"sm_mhz": 1695.0, "sm_max_mhz": 1965.0, "reasons": ["sw_power_cap", "sw_thermal_slowdown"], "samples": 3}
+    sampler = bench.ClockSampler(str(tmp_path / "x.csv"), ["GPU-abc", "GPU-def"])
+    assert sampler.stop()["reasons"] == ["nvidia-smi unavailable"]          # never started: no process to read
