@@ -57,6 +57,7 @@ class PlanSpec:
     use_block_size_heuristic: bool = False
     cost_model: Optional[dict] = None       # intra/inter node latency + bandwidth, max_tflops, max_mem_bw
     cache_dir: Optional[str] = None         # plans are stored here by batch signature and reused (e.g. after a resume)
+    qkv_dtype: str = "bfloat16"             # dtype of the attention buffers in the instruction plans (plan interpreter)
 
 
 @dataclass
@@ -213,7 +214,7 @@ def _plan_group(spec: PlanSpec, iteration: int, group_id: int, seqlens: Sequence
     hbs = spec.head_block_size or spec.n_heads
     d = spec.head_dim
     wl = generate_workload((sum(pad), spec.n_heads, d), (sum(pad), 2, spec.n_kv_heads, d), raw, pad, bs, hbs,
-                           ctx.comp_cost_model, mask, torch.bfloat16)
+                           ctx.comp_cost_model, mask, getattr(torch, spec.qkv_dtype))
     ccfg = CompilerConfig(n_stages=spec.n_stages)
     for name in ("mem_imbalance_epsilon", "comp_imbalance_epsilon", "inter_node_comp_imbalance_factor"):
         if getattr(spec, name) is not None:
