@@ -40,15 +40,26 @@ def init_params(cfg: LlamaConfig, seed: int = 0, dtype=torch.float32, device="cp
 
 class InterpreterEngine:
     """One rank of a context-parallel training job on the plan interpreter.  ``group``: the ranks that
-    share every batch (None = single process)."""
+    share every batch (None = single process).
+
+    With ``pp_group`` (the ranks that hold the other pipeline stages of this rank's tokens; group rank
+    = stage index) the model is cut into stages of consecutive layers: ``group`` then links the
+    context-parallel ranks of ONE stage, every stage of a context-parallel rank plans the same
+    batches, a step runs ``n_micro`` planned batches in one-forward-one-backward order
+    (``parallel.pipeline.run_stage_1f1b``) and a stage only ever touches its own parameters."""
 
     def __init__(self, cfg: LlamaConfig, tokens_per_step: int, block_size: int = 256, mask: str = "causal",
                  length_dist: Optional[synth.LengthDist] = None, group=None, seed: int = 0, lr: float = 1e-3,
-                 device: str = "cpu", n_stages: Optional[int] = None):
+                 device: str = "cpu", n_stages: Optional[int] = None, pp_group=None, n_micro: int = 1):
         import torch.distributed as dist
+        from .models.reference import stage_layer_range
         self.cfg, self.group, self.device = cfg, group, torch.device(device)
         self.world = dist.get_world_size(group) if group is not None else 1
         self.rank = dist.get_rank(group) if group is not None else 0
+        self.pp_group, self.n_micro = pp_group, n_micro
+        self.stage = dist.get_rank(pp_group) if pp_group is not None else 0
+        self.n_pp = dist.get_world_size(pp_group) if pp_group is not None else 1
+        self.layers = stage_layer_range(cfg.n_layers, self.stage, self.n_pp)
         self.ctx = get_default_execution_context(self.world, 1)
         self.spec = PlanSpec(self.world, self.world, tokens_per_step, cfg.n_heads, cfg.n_kv_heads, cfg.head_dim, block_size,
                              0, mask, length_dist or synth.LengthDist("lognormal", 400.0, 0.6, 32, tokens_per_step),
@@ -61,18 +72,24 @@ class InterpreterEngine:
     def plan(self, iteration: Optional[int] = None) -> RankPlan:
         return plan_iteration(self.spec, self.iteration if iteration is None else iteration, self.rank)
 
-    def local_loss(self, plan: RankPlan) -> torch.Tensor:
-        """Sum of this rank's token losses / global token count (the ranks' values add up to the batch loss)."""
-        cfg, p, dev = self.cfg, self.p, self.device
+    def _executor(self, plan: RankPlan):
+        cfg = self.cfg
+        return get_executor(cfg.n_heads, cfg.head_dim, self.ctx, plan.fw_plan, plan.fw_workload, plan.bw_plan,
+                            plan.bw_workload, executor_impl="python", process_group=self.group, device=self.device)
+
+    def _norm(self, t, w):
+        return t * torch.rsqrt(t.pow(2).mean(-1, keepdim=True) + self.cfg.eps) * w
+
+    def embed(self, plan: RankPlan) -> torch.Tensor:
+        return F.embedding(plan.tokens.to(self.device), self.p["embed"])
+
+    def run_layers(self, plan: RankPlan, ex, x: torch.Tensor, layers) -> torch.Tensor:
+        """Decoder layers ``layers`` on this rank's tokens of ``plan`` (attention through ``ex``)."""
+        cfg, p = self.cfg, self.p
         hq, hkv, d = cfg.n_heads, cfg.n_kv_heads, cfg.head_dim
-        ex = get_executor(hq, d, self.ctx, plan.fw_plan, plan.fw_workload, plan.bw_plan, plan.bw_workload,
-                          executor_impl="python", process_group=self.group, device=dev)
-        toks, labels, pos = plan.tokens.to(dev), plan.labels.to(dev), plan.positions.to(dev)
-        cos, sin = model_ops.rope_tables(pos, cfg.rope_theta, d)
-        norm = lambda t, w: t * torch.rsqrt(t.pow(2).mean(-1, keepdim=True) + cfg.eps) * w
-        x = F.embedding(toks, p["embed"])
-        for l in range(cfg.n_layers):
-            qkv = F.linear(norm(x, p[f"l{l}.norm1"]), p[f"l{l}.wqkv"]).view(-1, hq + 2 * hkv, d)
+        cos, sin = model_ops.rope_tables(plan.positions.to(self.device), cfg.rope_theta, d)
+        for l in layers:
+            qkv = F.linear(self._norm(x, p[f"l{l}.norm1"]), p[f"l{l}.wqkv"]).view(-1, hq + 2 * hkv, d)
             q = model_ops.rope_reference(qkv[:, :hq], cos, sin)
             k = model_ops.rope_reference(qkv[:, hq:hq + hkv], cos, sin)
             kv = torch.stack([k, qkv[:, hq + hkv:]], dim=1)                   # [tokens, 2, hkv, d]
@@ -80,11 +97,61 @@ class InterpreterEngine:
             # fetch blocks from it and wait for its messages
             a = DCPAttention.apply(ex, False, False, q.contiguous(), kv.contiguous())
             x = x + F.linear(a.reshape(-1, hq * d), p[f"l{l}.wo"])
-            gate, up = F.linear(norm(x, p[f"l{l}.norm2"]), p[f"l{l}.wgu"]).chunk(2, dim=-1)
+            gate, up = F.linear(self._norm(x, p[f"l{l}.norm2"]), p[f"l{l}.wgu"]).chunk(2, dim=-1)
             x = x + F.linear(F.silu(gate) * up, p[f"l{l}.wd"])
-        logits = F.linear(norm(x, p["norm_f"]), p["lm_head"])
+        return x
+
+    def head_loss(self, plan: RankPlan, x: torch.Tensor) -> torch.Tensor:
+        labels = plan.labels.to(self.device)
+        logits = F.linear(self._norm(x, self.p["norm_f"]), self.p["lm_head"])
         loss = F.cross_entropy(logits, labels.clamp(min=0), reduction="none")
         return torch.where(labels >= 0, loss, torch.zeros_like(loss)).sum() / max(plan.n_global_tokens, 1)
+
+    def local_loss(self, plan: RankPlan) -> torch.Tensor:
+        """Sum of this rank's token losses / global token count (the ranks' values add up to the batch loss)."""
+        x = self.run_layers(plan, self._executor(plan), self.embed(plan), range(self.cfg.n_layers))
+        return self.head_loss(plan, x)
+
+    def pipeline_loss_and_grads(self, first_iteration: Optional[int] = None):
+        """One pipelined step over ``n_micro`` planned batches (iterations ``first_iteration`` ...):
+        gradients of this stage's parameters summed over the micro-batches and over the stage's
+        context-parallel ranks.  Returns the micro-batch losses on the last stage (summed over its
+        ranks), an empty list elsewhere."""
+        import torch.distributed as dist
+        from .parallel.pipeline import PipelineComm, run_stage_1f1b
+        it0 = self.iteration * self.n_micro if first_iteration is None else first_iteration
+        plans = [self.plan(it0 + mb) for mb in range(self.n_micro)]
+        execs = [self._executor(pl) for pl in plans]          # plans differ per micro-batch, so do the executors
+        for t in self.p.values():
+            t.grad = None
+        comm = PipelineComm(self.pp_group, lambda mb: (plans[mb].tokens.numel(), self.cfg.hidden), torch.float32, self.device)
+        losses = run_stage_1f1b(
+            comm, self.n_micro,
+            lambda mb, x: self.run_layers(plans[mb], execs[mb], self.embed(plans[mb]) if x is None else x, self.layers),
+            lambda mb, y: self.head_loss(plans[mb], y))
+        mine = self.stage_parameters()
+        for name in mine:
+            t = self.p[name]
+            if t.grad is None:
+                t.grad = torch.zeros_like(t)
+            if self.group is not None:
+                dist.all_reduce(t.grad, group=self.group)
+        out = []
+        for l in losses:
+            l = l.clone()
+            if self.group is not None:
+                dist.all_reduce(l, group=self.group)
+            out.append(float(l.item()))
+        return out
+
+    def stage_parameters(self):
+        """Names of the parameters this pipeline stage owns."""
+        names = [k for k in self.p if any(k.startswith(f"l{l}.") for l in self.layers)]
+        if self.stage == 0:
+            names.append("embed")
+        if self.stage == self.n_pp - 1:
+            names += ["norm_f", "lm_head"]
+        return names
 
     def loss_and_grads(self, plan: RankPlan) -> float:
         """Backward through the distributed attention, gradients summed over the ranks; returns the

@@ -104,6 +104,17 @@ def test_interpreter_training_matches_unsplit_model(world):
     assert res.returncode == 0 and "INTERP_OK" in res.stdout, res.stdout[-3000:]
 
 
+def test_interpreter_pipeline_times_context_parallel():
+    """Pipeline parallelism together with DCP: 2 stages x 2 context-parallel ranks (4 gloo ranks), every
+    stage of a context-parallel rank plans the same batches, three micro-batches in one-forward-one-
+    backward order; losses and every stage's gradients equal the unsplit fp32 model's."""
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=4", "--master-addr",
+           "127.0.0.1", "--master-port", "29627", os.path.join(ROOT, "tests", "interp_pp_worker.py")]
+    env = dict(os.environ, PYTHONPATH=ROOT, OMP_NUM_THREADS="1")
+    res = subprocess.run(cmd, env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=600)
+    assert res.returncode == 0 and "INTERP_PP_OK" in res.stdout, res.stdout[-3000:]
+
+
 def test_rank_failure_surfaces_as_exception():
     torch.manual_seed(0)
     raw = [256, 256]
