@@ -77,7 +77,8 @@ def _native_planner():
     if os.environ.get("DCP_B200_PY_TABLES", "0") == "1":
         return None
     from .. import _planner
-    return _planner
+    # a planner library built before the table builders were added has no such entry points
+    return _planner if hasattr(_planner, "build_fwd_tables") and hasattr(_planner, "build_bwd_tables") else None
 
 
 def _row_tuples(rows: Sequence[AttnRow]):
