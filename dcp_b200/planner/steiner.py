@@ -159,6 +159,8 @@ def pack_multicast_trees(requests: Sequence[Request], n_nodes: int, n_stages: in
     requests = [(b, s, set(d), float(z)) for b, s, d, z in requests]
     if native:
         from .. import _planner
+        native = hasattr(_planner, "pack_multicast_trees")      # a library built before the packer was added
+    if native:
         packed = []
         for b, s, dsts, z in requests:
             ds = sorted(dsts)
