@@ -66,29 +66,64 @@ def default_args(**over) -> argparse.Namespace:
     return argparse.Namespace(**d)
 
 
+def bench_plan_spec(args, world: int) -> PlanSpec:
+    """The planner settings of a benchmark run (optional arguments default to the planner's own)."""
+    dists = {"lognormal8k": synth.LOGNORMAL_8K, "lognormal16k": synth.LOGNORMAL_16K, "mixture": synth.MIXTURE}
+    return PlanSpec(world, world, args.tokens, args.n_heads, args.n_kv_heads, 128, args.block_size,
+                    getattr(args, "head_block_size", 0) or 0, args.mask, dists[args.length_dist], seed=args.seed,
+                    n_stages=args.stages, build_instruction_plans=args.framework == "nccl-plan",
+                    mem_imbalance_epsilon=getattr(args, "mem_epsilon", None),
+                    comp_imbalance_epsilon=getattr(args, "comp_epsilon", None),
+                    use_block_size_heuristic=bool(getattr(args, "use_block_size_heuristic", False)))
+
+
+def explicit_batches(args):
+    """Sequence lengths given on the command line: ``--seqlens 4096,512,...`` (one batch) or
+    ``--seqlens-config file.json`` ({"batches": [[...], ...]} as written by ``bench.preprocessing``, or a
+    plain list of lists / one list); None when the lengths are to be drawn from ``--length-dist``."""
+    if getattr(args, "seqlens", None):
+        return [[int(x) for x in str(args.seqlens).split(",") if x]]
+    path = getattr(args, "seqlens_config", None)
+    if not path:
+        return None
+    data = json.load(open(path))
+    if isinstance(data, dict):
+        data = data["batches"]
+    return [list(map(int, b)) for b in data] if data and isinstance(data[0], (list, tuple)) else [list(map(int, data))]
+
+
+def plan_for_batch(args, spec: PlanSpec, b: int, rank: int):
+    """Rank ``rank``'s plan of benchmark batch ``b``: drawn from the length distribution, or the b-th
+    explicit batch (cycled) with seeded token ids."""
+    batches = explicit_batches(args)
+    if batches is None:
+        return plan_iteration(spec, b, rank)
+    from ..data.plan_service import plan_batch
+    seqlens = batches[b % len(batches)]
+    return plan_batch(spec, b, rank, seqlens, synth.make_token_batch(seqlens, spec.vocab, spec.seed * 1000003 + b))
+
+
 def run_batches(args, group, dev, rank: int, world: int, verbose: bool = True) -> dict:
     """Time ``args.batches`` packed batches with ``args.framework`` on an initialised process group
     (or one GPU when ``group`` is None) and return the summary (max over ranks per batch)."""
-    dists = {"lognormal8k": synth.LOGNORMAL_8K, "lognormal16k": synth.LOGNORMAL_16K, "mixture": synth.MIXTURE}
-    spec = PlanSpec(world, world, args.tokens, args.n_heads, args.n_kv_heads, 128, args.block_size, 0, args.mask,
-                    dists[args.length_dist], seed=args.seed, n_stages=args.stages,
-                    build_instruction_plans=args.framework == "nccl-plan")
+    spec = bench_plan_spec(args, world)
     hbm, tf_peak, src = measured_peaks()
     total_max_ms, total_flops, total_roof = 0.0, 0.0, 0.0
     ex = None
     for b in range(args.batches):
-        plan = plan_iteration(spec, b, rank)
+        plan = plan_for_batch(args, spec, b, rank)
         p = plan.program
         H, Hkv = args.n_heads, args.n_kv_heads
         g = torch.Generator(device=dev).manual_seed(1000 + b * 17 + rank)
         if args.framework == "dcp":
             cap = int(args.tokens // world * 1.5) + 4 * args.block_size
+            hl, hkvl = p.heads_q, p.heads_kv       # heads per block (all heads unless --head-block-size is given)
             if ex is None:
-                ex = FusedAttentionExecutor(H, Hkv, cap, cap, cap, dev, group)
+                ex = FusedAttentionExecutor(hl, hkvl, cap * (H // hl), cap * (H // hl), cap * (H // hl), dev, group)
             ex.prepare(p)
-            lq = torch.randn(p.q_local_rows, H, 128, device=dev, generator=g).bfloat16()
-            lkv = torch.randn(p.kv_local_rows, 2, Hkv, 128, device=dev, generator=g).bfloat16()
-            ldo = torch.randn(p.q_local_rows, H, 128, device=dev, generator=g).bfloat16()
+            lq = torch.randn(p.q_local_rows, hl, 128, device=dev, generator=g).bfloat16()
+            lkv = torch.randn(p.kv_local_rows, 2, hkvl, 128, device=dev, generator=g).bfloat16()
+            ldo = torch.randn(p.q_local_rows, hl, 128, device=dev, generator=g).bfloat16()
 
             def step():
                 ex.q_local().copy_(lq)
@@ -100,7 +135,8 @@ def run_batches(args, group, dev, rank: int, world: int, verbose: bool = True) -
         elif args.framework in ("ulysses", "ring", "zigzag", "double-ring", "a2a+p2p"):
             from .baselines import make_baseline
             assert args.mask == "causal", "the library attention kernel only knows causal masks"
-            attn, n = make_baseline(args.framework, group, plan.seqlens, H, Hkv, rank, world)
+            attn, n = make_baseline(args.framework, group, plan.seqlens, H, Hkv, rank, world,
+                                    window=getattr(args, "lt_window_size", None), a2a=getattr(args, "a2a_degree", None))
             q = torch.randn(n, H, 128, device=dev, generator=g).bfloat16().requires_grad_(True)
             k = torch.randn(n, Hkv, 128, device=dev, generator=g).bfloat16().requires_grad_(True)
             v = torch.randn(n, Hkv, 128, device=dev, generator=g).bfloat16().requires_grad_(True)
@@ -175,6 +211,16 @@ def main(argv=None):
     ap.add_argument("--stages", type=int, default=None)
     ap.add_argument("--mode", default="fwdbwd", choices=["fwd", "fwdbwd"])
     ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--seqlens", default=None, help="comma separated sequence lengths of one batch (overrides --length-dist)")
+    ap.add_argument("--seqlens-config", default=None, help="json with explicit batches (see bench.preprocessing)")
+    ap.add_argument("--head-block-size", type=int, default=0, help="heads per block (0 = all heads in one block)")
+    ap.add_argument("-me", "--mem-epsilon", type=float, default=None, help="token (memory) balance tolerance of the placement")
+    ap.add_argument("-ce", "--comp-epsilon", type=float, default=None, help="attention-work balance tolerance of the placement")
+    ap.add_argument("--use-block-size-heuristic", action="store_true")
+    ap.add_argument("--lt-window-size", type=int, default=None, help="double ring: ranks per inner ring")
+    ap.add_argument("--a2a-degree", type=int, default=None, help="a2a+p2p: ranks per head all-to-all group")
+    ap.add_argument("--check-correctness", action="store_true",
+                    help="dcp on 2 or more GPUs: first compare the fused path with dense fp64 attention on small batches")
     args = ap.parse_args(argv)
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -185,6 +231,11 @@ def main(argv=None):
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
         group = dist.group.WORLD
+    if args.check_correctness and world > 1 and "dcp" in args.framework:
+        from ..runtime.selfcheck import fused_self_check
+        check = fused_self_check(rank, world, group)
+        if rank == 0:
+            print(json.dumps({"check_correctness": check}), flush=True)
     for framework in args.framework:
         one = argparse.Namespace(**{**vars(args), "framework": framework})
         try:

@@ -23,7 +23,7 @@ torch SDPA per sequence otherwise.
 """
 from __future__ import annotations
 
-from typing import List, Sequence
+from typing import List, Optional, Sequence
 
 import torch
 import torch.distributed as dist
@@ -411,8 +411,11 @@ class HierarchicalA2AP2P:
         return _SeqAllToAll.apply(out, self.a2a_group, False, self.counts)
 
 
-def make_baseline(framework: str, group, seqlens: Sequence[int], n_heads: int, n_kv_heads: int, rank: int, world: int):
-    """-> (attention callable (q, k, v) -> out, number of local tokens) for a baseline framework."""
+def make_baseline(framework: str, group, seqlens: Sequence[int], n_heads: int, n_kv_heads: int, rank: int, world: int,
+                  window: Optional[int] = None, a2a: Optional[int] = None):
+    """-> (attention callable (q, k, v) -> out, number of local tokens) for a baseline framework.
+    ``window``: ranks per inner ring of the double ring; ``a2a``: ranks per head all-to-all group of
+    a2a+p2p (defaults: 2, and the largest power of two the KV heads and the world size allow)."""
     if framework == "ulysses":
         ua = UlyssesAttention(group, seqlens, n_heads, n_kv_heads)
         return ua, ua.counts[rank]
@@ -423,14 +426,18 @@ def make_baseline(framework: str, group, seqlens: Sequence[int], n_heads: int, n
         return ra, ra.cu[-1]
     if framework == "double-ring":
         assert group is not None, "ring attention needs at least two ranks"
-        window = 2 if world % 2 == 0 and world > 2 else world       # inner rings of two ranks (four rings on 8 GPUs)
+        if window is None:
+            window = 2 if world % 2 == 0 and world > 2 else world   # inner rings of two ranks (four rings on 8 GPUs)
+        assert world % window == 0, "the inner ring size must divide the number of ranks"
         ra = RingAttention(group, RingAttention.adjust_seqlens(seqlens, world), zigzag=True, window=window)
         return ra, ra.cu[-1]
     if framework == "a2a+p2p":
         assert group is not None, "needs at least two ranks"
-        a2a = 2 if world % 2 == 0 else 1
-        while a2a * 2 <= min(n_kv_heads, 4) and world % (a2a * 2) == 0 and world // (a2a * 2) >= 2:
-            a2a *= 2                                                 # 4 x 2 on 8 GPUs, 2 x 2 on 4
+        if a2a is None:
+            a2a = 2 if world % 2 == 0 else 1
+            while a2a * 2 <= min(n_kv_heads, 4) and world % (a2a * 2) == 0 and world // (a2a * 2) >= 2:
+                a2a *= 2                                             # 4 x 2 on 8 GPUs, 2 x 2 on 4
+        assert world % a2a == 0 and n_kv_heads % a2a == 0, "the all-to-all group must divide ranks and KV heads"
         ha = HierarchicalA2AP2P(group, HierarchicalA2AP2P.adjust_seqlens(seqlens, world, a2a), n_heads, n_kv_heads, a2a)
         return ha, ha.n_local
     raise ValueError(f"unknown baseline framework {framework!r}")

@@ -172,3 +172,27 @@ def test_pipeline_stage_boundary():
         res = subprocess.run(cmd, env=dict(os.environ, PYTHONPATH=root, OMP_NUM_THREADS="1"), stdout=subprocess.PIPE,
                              stderr=subprocess.STDOUT, text=True, timeout=300)
         assert res.returncode == 0 and "PP_OK" in res.stdout, res.stdout[-3000:]
+
+
+def test_attention_benchmark_planning_arguments(tmp_path):
+    """The microbenchmark's planner-side arguments: default settings leave the planner's own defaults,
+    explicit sequence lengths (command line or the preprocessing json, cycled over batches) replace the
+    length distribution, tolerances / head block size reach the plan specification."""
+    import argparse
+    from dcp_b200.bench import attention as A
+    args = A.default_args(tokens=8192, block_size=512)
+    spec = A.bench_plan_spec(args, 2)
+    assert (spec.head_block_size, spec.mem_imbalance_epsilon, spec.comp_imbalance_epsilon) == (0, None, None)
+    assert sum(A.plan_for_batch(args, spec, 0, 1).seqlens) <= 8192
+    args.seqlens = "3000,1000,2500"
+    plans = [A.plan_for_batch(args, spec, 0, r) for r in range(2)]
+    assert plans[0].seqlens == [3000, 1000, 2500] and sum(p.tokens.numel() for p in plans) == 6500
+    args.seqlens = None
+    json.dump({"batches": [[2000, 500], [4096]], "max_dp_degree": 1}, open(tmp_path / "b.json", "w"))
+    args.seqlens_config = str(tmp_path / "b.json")
+    assert [A.plan_for_batch(args, spec, b, 0).seqlens for b in range(3)] == [[2000, 500], [4096], [2000, 500]]
+    tuned = argparse.Namespace(**{**vars(args), "mem_epsilon": 0.1, "comp_epsilon": 0.05, "head_block_size": 8,
+                                  "use_block_size_heuristic": True})
+    spec = A.bench_plan_spec(tuned, 4)
+    assert (spec.head_block_size, spec.mem_imbalance_epsilon, spec.comp_imbalance_epsilon, spec.use_block_size_heuristic) == \
+        (8, 0.1, 0.05, True)
