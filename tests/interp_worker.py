@@ -11,7 +11,9 @@ sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
 from dcp_b200.data import synth  # noqa: E402
 from dcp_b200.models.llama import LlamaConfig  # noqa: E402
-from dcp_b200.models.reference import reference_loss  # noqa: E402
+from dcp_b200.models.reference import reference_loss, sequence_masks  # noqa: E402
+from dcp_b200.planner import masks  # noqa: E402
+from dcp_b200.planner.workload import pad_seqlens  # noqa: E402
 from dcp_b200.train_interp import InterpreterEngine, init_params  # noqa: E402
 
 
@@ -35,8 +37,12 @@ def main():
         batch = synth.make_token_batch(seqlens, cfg.vocab, seed)
         for t in ref_p.values():
             t.grad = None
+        allow = None
+        if mask != "causal":
+            pad = pad_seqlens(seqlens, eng.spec.block_size)
+            allow = sequence_masks(seqlens, masks.get_mask_fn(mask)(seqlens, pad, torch.int32), pad)
         ref = reference_loss(cfg, ref_p, torch.from_numpy(batch["tokens"]), torch.from_numpy(batch["labels"]),
-                             torch.from_numpy(batch["positions"]), seqlens, 1.0 / sum(seqlens))
+                             torch.from_numpy(batch["positions"]), seqlens, 1.0 / sum(seqlens), allow)
         ref.backward()
         ok &= abs(loss - ref.item()) < 1e-5 * abs(ref.item())
         for name in ref_p:
