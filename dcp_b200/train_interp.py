@@ -46,11 +46,16 @@ class InterpreterEngine:
     = stage index) the model is cut into stages of consecutive layers: ``group`` then links the
     context-parallel ranks of ONE stage, every stage of a context-parallel rank plans the same
     batches, a step runs ``n_micro`` planned batches in one-forward-one-backward order
-    (``parallel.pipeline.run_stage_1f1b``) and a stage only ever touches its own parameters."""
+    (``parallel.pipeline.run_stage_1f1b``) and a stage only ever touches its own parameters.
+
+    With ``replica_group`` (all ranks that hold the same parameters) ``group`` is one of several
+    context-parallel groups inside it (CP x DP): the batch is dealt over the groups, attention stays
+    inside a group and gradients are summed over the whole replica group."""
 
     def __init__(self, cfg: LlamaConfig, tokens_per_step: int, block_size: int = 256, mask: str = "causal",
                  length_dist: Optional[synth.LengthDist] = None, group=None, seed: int = 0, lr: float = 1e-3,
-                 device: str = "cpu", n_stages: Optional[int] = None, pp_group=None, n_micro: int = 1):
+                 device: str = "cpu", n_stages: Optional[int] = None, pp_group=None, n_micro: int = 1,
+                 replica_group=None):
         import torch.distributed as dist
         from .models.reference import stage_layer_range
         self.cfg, self.group, self.device = cfg, group, torch.device(device)
@@ -60,8 +65,13 @@ class InterpreterEngine:
         self.stage = dist.get_rank(pp_group) if pp_group is not None else 0
         self.n_pp = dist.get_world_size(pp_group) if pp_group is not None else 1
         self.layers = stage_layer_range(cfg.n_layers, self.stage, self.n_pp)
+        self.replica_group = replica_group if replica_group is not None else group
+        n_all = dist.get_world_size(self.replica_group) if self.replica_group is not None else 1
+        self.plan_rank = dist.get_rank(self.replica_group) if self.replica_group is not None else 0
+        assert n_all % self.world == 0 and self.plan_rank % self.world == self.rank, \
+            "context-parallel groups must be runs of consecutive ranks of the replica group"
         self.ctx = get_default_execution_context(self.world, 1)
-        self.spec = PlanSpec(self.world, self.world, tokens_per_step, cfg.n_heads, cfg.n_kv_heads, cfg.head_dim, block_size,
+        self.spec = PlanSpec(n_all, self.world, tokens_per_step, cfg.n_heads, cfg.n_kv_heads, cfg.head_dim, block_size,
                              0, mask, length_dist or synth.LengthDist("lognormal", 400.0, 0.6, 32, tokens_per_step),
                              vocab=cfg.vocab, seed=seed, n_stages=n_stages, build_instruction_plans=True,
                              qkv_dtype="float32")
@@ -70,7 +80,7 @@ class InterpreterEngine:
         self.iteration = 0
 
     def plan(self, iteration: Optional[int] = None) -> RankPlan:
-        return plan_iteration(self.spec, self.iteration if iteration is None else iteration, self.rank)
+        return plan_iteration(self.spec, self.iteration if iteration is None else iteration, self.plan_rank)
 
     def _executor(self, plan: RankPlan):
         cfg = self.cfg
@@ -162,12 +172,12 @@ class InterpreterEngine:
         loss = self.local_loss(plan)
         loss.backward()
         total = loss.detach().clone()
-        if self.group is not None:
-            dist.all_reduce(total, group=self.group)
+        if self.replica_group is not None:
+            dist.all_reduce(total, group=self.replica_group)
             for t in self.p.values():
                 if t.grad is None:                       # a rank without tokens still takes part in the sum
                     t.grad = torch.zeros_like(t)
-                dist.all_reduce(t.grad, group=self.group)
+                dist.all_reduce(t.grad, group=self.replica_group)
         return float(total.item())
 
     def train_step(self) -> float:

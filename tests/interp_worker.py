@@ -22,18 +22,29 @@ def main():
     rank, world = dist.get_rank(), dist.get_world_size()
     torch.set_num_threads(2)
     mask = sys.argv[1] if len(sys.argv) > 1 else "causal"
+    dcp_size = int(sys.argv[2]) if len(sys.argv) > 2 else world          # < world: CP x DP
     cfg = LlamaConfig(2, 64, 4, 2, 16, 96, 101)
-    eng = InterpreterEngine(cfg, 1500, block_size=128, mask=mask, group=dist.group.WORLD, seed=3, lr=1e-2)
+    group = dist.group.WORLD
+    if dcp_size < world:
+        groups = [dist.new_group(list(range(g * dcp_size, (g + 1) * dcp_size))) for g in range(world // dcp_size)]
+        group = groups[rank // dcp_size]
+    eng = InterpreterEngine(cfg, 1500, block_size=128, mask=mask, group=group, seed=3, lr=1e-2,
+                            replica_group=dist.group.WORLD)
     ref_p = init_params(cfg, 3)
     ref_opt = torch.optim.AdamW(list(ref_p.values()), lr=1e-2, betas=(0.9, 0.95), weight_decay=0.1)
     ok = True
     for it in range(3):
         plan = eng.plan()
-        assert plan.tokens.numel() > 0 and sum(plan.seqlens) > plan.tokens.numel()     # the batch really is split
+        assert plan.tokens.numel() > 0 and plan.n_global_tokens > plan.tokens.numel()   # the batch really is split
         loss = eng.loss_and_grads(plan)
         # the unsplit model on the whole batch (every rank computes it: same seeds)
         seed = eng.spec.seed * 1000003 + it
-        seqlens = synth.sample_seqlens(eng.spec.tokens_per_step, eng.spec.length_dist, seed)
+        n_groups = world // dcp_size
+        if n_groups > 1:        # every context-parallel group draws its own sub-batch; the job's batch is their union
+            seqlens = [n for g in range(n_groups)
+                       for n in synth.sample_seqlens(eng.spec.tokens_per_step // n_groups, eng.spec.length_dist, seed * 64 + g + 1)]
+        else:
+            seqlens = synth.sample_seqlens(eng.spec.tokens_per_step, eng.spec.length_dist, seed)
         batch = synth.make_token_batch(seqlens, cfg.vocab, seed)
         for t in ref_p.values():
             t.grad = None

@@ -92,14 +92,17 @@ def test_gloo_world2_reference_config():
     assert "GLOO_OK" in res.stdout, res.stdout[-3000:]
 
 
-@pytest.mark.parametrize("world,mask", [(2, "causal"), (3, "causal"), (2, "shared_question"), (2, "causal_blockwise")])
-def test_interpreter_training_matches_unsplit_model(world, mask):
+@pytest.mark.parametrize("world,mask,dcp_size", [(2, "causal", 2), (3, "causal", 3), (2, "shared_question", 2),
+                                                 (2, "causal_blockwise", 2), (4, "causal", 2)])
+def test_interpreter_training_matches_unsplit_model(world, mask, dcp_size):
     """End-to-end DCP training without a GPU: synthetic batch -> placement -> plans -> two-layer Llama
     with distributed attention on the plan interpreter over gloo ranks -> gradient sum -> AdamW; loss,
     gradients and the parameters after three steps equal those of the unsplit fp32 model, for causal
-    and for structured masks (the unsplit model applies the same per-query key ranges densely)."""
+    and for structured masks (the unsplit model applies the same per-query key ranges densely), and for
+    two context-parallel groups of two ranks each (CP x DP: the batch dealt over the groups)."""
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr",
-           "127.0.0.1", "--master-port", str(29620 + world), os.path.join(ROOT, "tests", "interp_worker.py"), mask]
+           "127.0.0.1", "--master-port", str(29620 + world), os.path.join(ROOT, "tests", "interp_worker.py"), mask,
+           str(dcp_size)]
     env = dict(os.environ, PYTHONPATH=ROOT, OMP_NUM_THREADS="2")
     res = subprocess.run(cmd, env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=600)
     assert res.returncode == 0 and "INTERP_OK" in res.stdout, res.stdout[-3000:]
