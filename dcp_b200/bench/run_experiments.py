@@ -99,7 +99,8 @@ def command(cell: Dict, port: int, args) -> List[str]:
     if cell["kind"] == "attention":
         return launch + ["-m", "dcp_b200.bench.attention", "--framework", cell["framework"], "--mask", cell["mask"],
                          "--length-dist", cell["length_dist"], "--block-size", str(cell["block_size"]), "--tokens",
-                         str(args.tokens), "--batches", str(args.batches)]
+                         str(args.tokens), "--batches", str(args.batches)] + \
+            (["--seqlens-config", args.seqlens_config] if getattr(args, "seqlens_config", None) else [])
     return launch + ["-m", "dcp_b200.train", "--iters", str(args.iters), "--tokens-per-step", str(args.tokens),
                      "--dcp-mask-type", cell["mask"], "--length-dist", cell["length_dist"], "--dcp-block-size",
                      str(cell["block_size"]), "--model", args.model]
@@ -176,6 +177,8 @@ def main(argv=None):
     ap.add_argument("--block-sizes", nargs="+", type=int, default=[1024, 2048, 4096])
     ap.add_argument("--tokens", type=int, default=131072)
     ap.add_argument("--batches", type=int, default=5)
+    ap.add_argument("--seqlens-config", default=None,
+                    help="json of explicit batches for the attention cells (written by dcp_b200.bench.preprocessing)")
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--model", default="llama3-8b")
     ap.add_argument("--no-progress-s", type=float, default=180.0)
