@@ -116,8 +116,9 @@ class InstrCompiler:
             out_dir = os.environ.get("DCP_DEBUG_VISUALIZE_WORKLOAD_SPEC_DIR",
                                      os.environ.get("DCP_LOGGING_DEBUG_DIR", "./debug"))
             os.makedirs(out_dir, exist_ok=True)
-            visualize_workload_spec_figure(workload, os.path.join(out_dir, f"workload_iter{self.iteration_idx}.json"),
-                                           self.context.n_devices_per_node)
+            for ext in ("json", "svg"):         # graph description and the drawn figure
+                visualize_workload_spec_figure(workload, os.path.join(out_dir, f"workload_iter{self.iteration_idx}.{ext}"),
+                                               self.context.n_devices_per_node)
 
     def compile(self, workload: WorkloadSpec, generate_backward: bool = True) -> Tuple[
             WorkloadSpec, Optional[WorkloadSpec], Dict[Device, ExecutionPlan], Optional[Dict[Device, ExecutionPlan]]]:

@@ -388,3 +388,22 @@ def test_modelled_and_measured_traces_merge_into_one_file(tmp_path):
     assert names == {"modelled node 0"} | {f"measured rank {r}" for r in range(4)}
     xs = [e for e in trace["traceEvents"] if e["ph"] == "X"]
     assert len(xs) == len(modelled) + 4 and {e["pid"] for e in xs if e["name"].startswith("fwd:")} == {1000, 1001, 1002, 1003}
+
+
+def test_placement_figure_svg(tmp_path):
+    """The placement drawn as SVG: one owner cell per token block and one work cell per (q block, kv
+    block) unit of head block 0, coloured by device."""
+    import xml.etree.ElementTree as ET
+    from dcp_b200.utils.visualization import visualize_workload_spec_figure
+    ctx = get_default_execution_context(4, 1)
+    wl, _, _ = _workload([1500, 700, 400], 128, hbs=4, mask="causal", ctx=ctx)
+    construct_and_partition_graph_multiconstraint(ctx, wl)
+    graph = visualize_workload_spec_figure(wl, str(tmp_path / "p.svg"), 4)
+    root = ET.parse(tmp_path / "p.svg").getroot()
+    ns = {"s": "http://www.w3.org/2000/svg"}
+    im, wm = wl.block_mapping.input_id_to_meta, wl.block_mapping.work_id_to_meta
+    n_blocks = sum(1 for m in im.values() if m.type == BlockType.Q and m.head_id == 0)
+    n_work = sum(1 for u in wm.values() if u.head_id == 0)
+    assert len(root.findall(".//s:rect[@class='owner']", ns)) == n_blocks
+    assert len(root.findall(".//s:rect[@class='work']", ns)) == n_work
+    assert len(graph["nodes"]) > 0 and not (tmp_path / "p.json").exists()
