@@ -38,6 +38,60 @@ def init_params(cfg: LlamaConfig, seed: int = 0, dtype=torch.float32, device="cp
     return p
 
 
+def shard_params(cfg: LlamaConfig, full: Dict[str, torch.Tensor], tp: int, t: int) -> Dict[str, torch.Tensor]:
+    """Tensor-parallel rank ``t``'s slice of full parameters: its query heads, KV heads and FFN channels
+    (rows of the QKV and gate/up matrices, columns of the output and down projections); embeddings,
+    norms and the LM head are held in full.  Same cut as ``LlamaConfig.shard``."""
+    d, hq, hkv, f = cfg.head_dim, cfg.n_heads // tp, cfg.n_kv_heads // tp, cfg.ffn // tp
+    out = {}
+    for name, w in full.items():
+        w = w.detach()
+        if name.endswith("wqkv"):
+            q, k, v = w[:cfg.n_heads * d], w[cfg.n_heads * d:(cfg.n_heads + cfg.n_kv_heads) * d], w[(cfg.n_heads + cfg.n_kv_heads) * d:]
+            w = torch.cat([q[t * hq * d:(t + 1) * hq * d], k[t * hkv * d:(t + 1) * hkv * d], v[t * hkv * d:(t + 1) * hkv * d]])
+        elif name.endswith("wgu"):
+            w = torch.cat([w[t * f:(t + 1) * f], w[cfg.ffn + t * f:cfg.ffn + (t + 1) * f]])
+        elif name.endswith(".wo"):
+            w = w[:, t * hq * d:(t + 1) * hq * d]
+        elif name.endswith(".wd"):
+            w = w[:, t * f:(t + 1) * f]
+        out[name] = w.clone().contiguous().requires_grad_(True)
+    return out
+
+
+class _SumForward(torch.autograd.Function):
+    """Row-parallel output: partial products of the tensor-parallel ranks are summed; the gradient
+    passes through unchanged."""
+
+    @staticmethod
+    def forward(ctx, x, group):
+        import torch.distributed as dist
+        x = x.clone()
+        dist.all_reduce(x, group=group)
+        return x
+
+    @staticmethod
+    def backward(ctx, g):
+        return g, None
+
+
+class _SumBackward(torch.autograd.Function):
+    """Input of a column-parallel layer: identity forward; every tensor-parallel rank contributes a
+    part of the input gradient, summed in the backward."""
+
+    @staticmethod
+    def forward(ctx, x, group):
+        ctx.group = group
+        return x.view_as(x)
+
+    @staticmethod
+    def backward(ctx, g):
+        import torch.distributed as dist
+        g = g.clone()
+        dist.all_reduce(g, group=ctx.group)
+        return g, None
+
+
 class InterpreterEngine:
     """One rank of a context-parallel training job on the plan interpreter.  ``group``: the ranks that
     share every batch (None = single process).
@@ -50,12 +104,16 @@ class InterpreterEngine:
 
     With ``replica_group`` (all ranks that hold the same parameters) ``group`` is one of several
     context-parallel groups inside it (CP x DP): the batch is dealt over the groups, attention stays
-    inside a group and gradients are summed over the whole replica group."""
+    inside a group and gradients are summed over the whole replica group.
+
+    With ``tp_group`` (the ranks that hold the other shards of this rank's model replica; they see the
+    same tokens) every rank holds 1/tp of the heads and FFN channels, the planner plans for the
+    per-shard head counts, and ``group`` / ``replica_group`` link ranks of equal shard index."""
 
     def __init__(self, cfg: LlamaConfig, tokens_per_step: int, block_size: int = 256, mask: str = "causal",
                  length_dist: Optional[synth.LengthDist] = None, group=None, seed: int = 0, lr: float = 1e-3,
                  device: str = "cpu", n_stages: Optional[int] = None, pp_group=None, n_micro: int = 1,
-                 replica_group=None):
+                 replica_group=None, tp_group=None):
         import torch.distributed as dist
         from .models.reference import stage_layer_range
         self.cfg, self.group, self.device = cfg, group, torch.device(device)
@@ -65,6 +123,12 @@ class InterpreterEngine:
         self.stage = dist.get_rank(pp_group) if pp_group is not None else 0
         self.n_pp = dist.get_world_size(pp_group) if pp_group is not None else 1
         self.layers = stage_layer_range(cfg.n_layers, self.stage, self.n_pp)
+        self.tp_group = tp_group
+        self.tp = dist.get_world_size(tp_group) if tp_group is not None else 1
+        self.tp_rank = dist.get_rank(tp_group) if tp_group is not None else 0
+        self.full_cfg = cfg
+        if self.tp > 1:
+            cfg = self.cfg = cfg.shard(self.tp)
         self.replica_group = replica_group if replica_group is not None else group
         n_all = dist.get_world_size(self.replica_group) if self.replica_group is not None else 1
         self.plan_rank = dist.get_rank(self.replica_group) if self.replica_group is not None else 0
@@ -75,7 +139,9 @@ class InterpreterEngine:
                              0, mask, length_dist or synth.LengthDist("lognormal", 400.0, 0.6, 32, tokens_per_step),
                              vocab=cfg.vocab, seed=seed, n_stages=n_stages, build_instruction_plans=True,
                              qkv_dtype="float32")
-        self.p = init_params(cfg, seed, torch.float32, self.device)
+        self.p = init_params(self.full_cfg, seed, torch.float32, self.device)
+        if self.tp > 1:
+            self.p = shard_params(self.full_cfg, self.p, self.tp, self.tp_rank)
         self.opt = torch.optim.AdamW(list(self.p.values()), lr=lr, betas=(0.9, 0.95), weight_decay=0.1)
         self.iteration = 0
 
@@ -98,17 +164,19 @@ class InterpreterEngine:
         cfg, p = self.cfg, self.p
         hq, hkv, d = cfg.n_heads, cfg.n_kv_heads, cfg.head_dim
         cos, sin = model_ops.rope_tables(plan.positions.to(self.device), cfg.rope_theta, d)
+        tp_in = (lambda t: _SumBackward.apply(t, self.tp_group)) if self.tp > 1 else (lambda t: t)
+        tp_out = (lambda t: _SumForward.apply(t, self.tp_group)) if self.tp > 1 else (lambda t: t)
         for l in layers:
-            qkv = F.linear(self._norm(x, p[f"l{l}.norm1"]), p[f"l{l}.wqkv"]).view(-1, hq + 2 * hkv, d)
+            qkv = F.linear(tp_in(self._norm(x, p[f"l{l}.norm1"])), p[f"l{l}.wqkv"]).view(-1, hq + 2 * hkv, d)
             q = model_ops.rope_reference(qkv[:, :hq], cos, sin)
             k = model_ops.rope_reference(qkv[:, hq:hq + hkv], cos, sin)
             kv = torch.stack([k, qkv[:, hq + hkv:]], dim=1)                   # [tokens, 2, hkv, d]
             # every rank calls the executor in every layer, also with zero local tokens: its peers
             # fetch blocks from it and wait for its messages
             a = DCPAttention.apply(ex, False, False, q.contiguous(), kv.contiguous())
-            x = x + F.linear(a.reshape(-1, hq * d), p[f"l{l}.wo"])
-            gate, up = F.linear(self._norm(x, p[f"l{l}.norm2"]), p[f"l{l}.wgu"]).chunk(2, dim=-1)
-            x = x + F.linear(F.silu(gate) * up, p[f"l{l}.wd"])
+            x = x + tp_out(F.linear(a.reshape(-1, hq * d), p[f"l{l}.wo"]))
+            gate, up = F.linear(tp_in(self._norm(x, p[f"l{l}.norm2"])), p[f"l{l}.wgu"]).chunk(2, dim=-1)
+            x = x + tp_out(F.linear(F.silu(gate) * up, p[f"l{l}.wd"]))
         return x
 
     def head_loss(self, plan: RankPlan, x: torch.Tensor) -> torch.Tensor:

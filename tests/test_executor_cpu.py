@@ -119,6 +119,17 @@ def test_interpreter_pipeline_times_context_parallel():
     assert res.returncode == 0 and "INTERP_PP_OK" in res.stdout, res.stdout[-3000:]
 
 
+def test_interpreter_tensor_times_context_parallel():
+    """Tensor parallelism together with DCP: heads and FFN channels split over 2 adjacent ranks, 2
+    context-parallel ranks per shard (4 gloo ranks); the planner plans for the per-shard head counts;
+    loss and every shard's gradients equal the unsplit model's, replicated parameters stay identical."""
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=4", "--master-addr",
+           "127.0.0.1", "--master-port", "29628", os.path.join(ROOT, "tests", "interp_tp_worker.py")]
+    env = dict(os.environ, PYTHONPATH=ROOT, OMP_NUM_THREADS="1")
+    res = subprocess.run(cmd, env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=600)
+    assert res.returncode == 0 and "INTERP_TP_OK" in res.stdout, res.stdout[-3000:]
+
+
 def test_rank_failure_surfaces_as_exception():
     torch.manual_seed(0)
     raw = [256, 256]
